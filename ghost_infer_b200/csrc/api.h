@@ -1,0 +1,45 @@
+// C entry points of the kernel library.  Every function takes device pointers and a CUDA stream,
+// launches on that stream without synchronising, and returns 0 or an error code whose text
+// gi_last_error() gives.  Nothing here allocates device memory: callers pass outputs and scratch.
+#pragma once
+
+#define GI_ABI_VERSION 1
+
+#define GI_GEMM_STORE 0      // out = A * W^T, stored in out_dtype
+#define GI_GEMM_ACCUM_F32 1  // out (float) += A * W^T
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* gi_last_error(void);
+int gi_abi_version(void);
+
+int gi_embed(float* out, const void* table, int table_dtype, const int* tokens, int n_tokens, int d, int vocab,
+             void* stream);
+int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows, int n_rows,
+               int d, float eps, void* stream);
+int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, void* stream);
+
+int gi_gemm_generic(void* out, int out_dtype, int mode, const void* A, int a_dtype, const void* W, int w_dtype, int M,
+                    int N, int K, long lda, long ldw, long ldo, void* stream);
+
+int gi_rope_cache_write(void* qkv, int dtype, long ld, const int* positions, const int* slots, const int* block_table,
+                        int max_pages, void* kcache, void* vcache, const float* inv_freq, int n_tokens, int n_heads,
+                        int n_kv, int hd, int rot, int adjacent, int write_cache, void* stream);
+
+int gi_attn_prefill_generic(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
+                            const void* vcache, const int* block_table, int max_pages, const int* cu_seqlens,
+                            const int* seq_slots, const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv,
+                            int hd, float scale, int window, void* stream);
+int gi_attn_decode_generic(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, int dtype,
+                           const void* kcache, const void* vcache, const int* block_table, int max_pages,
+                           const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
+                           float scale, int window, int n_splits, void* stream);
+
+int gi_sample(int* out_tokens, const float* logits, long ld, int n_rows, int vocab, float temperature, int top_k,
+              float top_p, unsigned long long* rng_state, const int* state_index, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,70 @@
+// Shared device helpers for every kernel file: element load/store for the two activation and
+// weight types (float, bfloat16), reductions with a fixed order, and the host-side error record.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define GI_OK 0
+#define GI_ERR_ARG 1
+#define GI_ERR_CUDA 2
+#define GI_ERR_UNSUPPORTED 3
+
+// dtype codes shared with the Python side
+#define GI_F32 0
+#define GI_BF16 1
+
+#define PAGE_TOKENS 64
+
+namespace gi {
+
+int fail(int code, const char* fmt, ...);          // records the message for gi_last_error(), returns code
+int check_launch(const char* what);                // cudaGetLastError() -> GI_OK or a recorded failure
+
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block (blockDim.x a multiple of 32, at most 1024); every thread gets the result.
+// The order of additions depends only on blockDim.x, so a row gives the same sum in any batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarp ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+template <typename T> struct DType;
+template <> struct DType<float> { static constexpr int code = GI_F32; };
+template <> struct DType<__nv_bfloat16> { static constexpr int code = GI_BF16; };
+
+}  // namespace gi
+
+// Calls `body` with `T` bound to the element type named by a dtype code.
+#define GI_DISPATCH_DTYPE(code, T, ...)                         \
+  do {                                                          \
+    if ((code) == GI_F32) { using T = float; __VA_ARGS__; }     \
+    else if ((code) == GI_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else return gi::fail(GI_ERR_ARG, "unknown dtype code %d", (int)(code)); \
+  } while (0)

@@ -1,0 +1,79 @@
+// Row kernels that move no matrix: embedding lookup, RMSNorm, SwiGLU's elementwise half.
+// All arithmetic is 32-bit; inputs and outputs may be float or bfloat16.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+// x[t, :] = table[tokens[t], :] as float (the reference's embed: src/cuda.rs:418-432, no scaling).
+template <typename TW>
+__global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table, const int* __restrict__ tokens,
+                             int d, int vocab) {
+  const int t = blockIdx.x;
+  int id = tokens[t];
+  if (id < 0 || id >= vocab) id = 0;  // the host validates ids; padding rows may carry anything
+  const TW* row = table + (size_t)id * d;
+  float* o = out + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = gi::ldf(row + i);
+}
+
+// y = x * (1 / sqrt(mean(x^2) + eps)) * w, one block per row (src/model.rs:919-928, src/cuda.rs:505-515).
+// `rows` (optional) picks which rows of x are normed; output row r is then x[rows[r]].
+template <typename TO, typename TW>
+__global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
+                               const int* __restrict__ rows, int d, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = gi::block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+  TO* o = out + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) gi::stf(o + i, xr[i] * scale * gi::ldf(w + i));
+}
+
+// h = silu(gate) * up from packed rows [gate | up] (src/cuda.rs:3573-3579; silu(g) = g / (1 + exp(-g)),
+// src/quant.rs:1135-1154).
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int f, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t m = i / f, c = i % f;
+  const float g = gi::ldf(gu + m * 2 * (size_t)f + c);
+  const float u = gi::ldf(gu + m * 2 * (size_t)f + f + c);
+  gi::stf(out + i, g / (1.0f + expf(-g)) * u);
+}
+
+}  // namespace
+
+extern "C" int gi_embed(float* out, const void* table, int table_dtype, const int* tokens, int n_tokens, int d,
+                        int vocab, void* stream) {
+  if (n_tokens <= 0) return GI_OK;
+  if (d <= 0 || vocab <= 0) return gi::fail(GI_ERR_ARG, "embed: bad sizes d=%d vocab=%d", d, vocab);
+  GI_DISPATCH_DTYPE(table_dtype, TW,
+                    embed_kernel<TW><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(out, (const TW*)table, tokens, d, vocab));
+  return gi::check_launch("embed");
+}
+
+extern "C" int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows,
+                          int n_rows, int d, float eps, void* stream) {
+  if (n_rows <= 0) return GI_OK;
+  if (d <= 0) return gi::fail(GI_ERR_ARG, "rmsnorm: bad width %d", d);
+  const int threads = d >= 2048 ? 512 : 256;
+  GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW,
+      (rmsnorm_kernel<TO, TW><<<n_rows, threads, 0, (cudaStream_t)stream>>>((TO*)out, x, (const TW*)w, rows, d, eps))));
+  return gi::check_launch("rmsnorm");
+}
+
+extern "C" int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, void* stream) {
+  if (n_rows <= 0) return GI_OK;
+  if (f <= 0) return gi::fail(GI_ERR_ARG, "silu_mul: bad width %d", f);
+  const size_t total = (size_t)n_rows * f;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  GI_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)gate_up, f, total));
+  return gi::check_launch("silu_mul");
+}

@@ -1,0 +1,311 @@
+// Next-token selection on the device: greedy, or temperature + top-k + top-p.
+//
+// Rule (src/sampler.rs:205-218, :259-291): temperature <= 0 picks the highest logit, the first one on
+// ties.  Otherwise the candidates are the top_k highest logits (0 = all), in descending order;
+// w_i = exp((l_i - l_max) / T); the list is cut after the first place where the running share of the
+// total reaches top_p; then r = u * (kept mass) is walked down the list and the first candidate at
+// which the running sum reaches r is taken.  u comes from xorshift64*, top 24 bits (src/sampler.rs:185-191).
+//
+// No sort is done.  "The first place in descending order where a running sum reaches a target" is
+// found by descending the bits of an order-preserving integer key, eight at a time: one sweep builds
+// a 256-bin histogram of weights for the keys that share the prefix found so far, a scan of the bins
+// picks the next byte.  Weights are 41-bit fixed point and summed as integers, so the result does not
+// depend on the order in which threads add.  Equal logits are ordered by token id (lower first), with
+// a second descent over the ids.  One block per row.
+#include <math.h>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+typedef unsigned long long u64;
+
+constexpr int THREADS = 1024;
+constexpr float FIXED_ONE = 1099511627776.0f;  // 2^40
+
+__device__ __forceinline__ unsigned order_key(float v) {
+  if (v != v) return 0u;  // NaN never wins (src/cuda.rs:3540-3570)
+  const unsigned f = __float_as_uint(v);
+  return (f & 0x80000000u) ? ~f : (f | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(unsigned k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ u64 fixed_weight(float logit, float lmax, float temperature) {
+  if (logit != logit) return 0;
+  return __float2ull_rn(expf((logit - lmax) / temperature) * FIXED_ONE);
+}
+
+struct Shared {
+  u64 hist[256];
+  u64 red64[32];
+  float redv[32];
+  int redi[32];
+  unsigned prefix;
+  u64 before, equal;
+  float bestv;
+  int besti;
+  u64 total;
+  float u;
+};
+
+// Descends the bytes of `val` from `start_shift` down.  elem(i, val, wt) says whether element i takes
+// part and gives its ordering value and weight.  On return: `val_out` is the value at which the running
+// sum (in descending order if DESC, else ascending) first reaches `target`; `before` is the weight
+// ordered strictly before it; `equal` the weight of the elements equal to it.
+template <bool DESC, typename F>
+__device__ void radix_descend(Shared& sh, int n, int start_shift, u64 target, F elem, unsigned& val_out, u64& before_out,
+                              u64& equal_out) {
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    sh.prefix = 0;
+    sh.before = 0;
+    sh.equal = 0;
+  }
+  for (int shift = start_shift; shift >= 0; shift -= 8) {
+    for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0;
+    __syncthreads();
+    const unsigned prefix = sh.prefix;
+    const bool check = shift != start_shift;
+    int cur = -1;
+    u64 run = 0;
+    for (int i = tid; i < n; i += blockDim.x) {
+      unsigned val;
+      u64 wt;
+      if (!elem(i, val, wt)) continue;
+      if (check && (val >> (shift + 8)) != prefix) continue;
+      const int bin = (int)((val >> shift) & 255u);
+      if (bin != cur) {
+        if (run) atomicAdd(&sh.hist[cur], run);
+        cur = bin;
+        run = 0;
+      }
+      run += wt;
+    }
+    if (run) atomicAdd(&sh.hist[cur], run);
+    __syncthreads();
+    if (tid == 0) {
+      u64 acc = sh.before;
+      int chosen = -1, last = -1;
+      for (int s = 0; s < 256; ++s) {
+        const int b = DESC ? 255 - s : s;
+        const u64 hb = sh.hist[b];
+        if (hb == 0) continue;
+        last = b;
+        if (acc + hb >= target) {
+          chosen = b;
+          break;
+        }
+        acc += hb;
+      }
+      if (chosen < 0) {  // the target lies beyond the total: the last element in order
+        chosen = last < 0 ? 0 : last;
+        acc -= sh.hist[chosen];
+      }
+      sh.prefix = (sh.prefix << 8) | (unsigned)chosen;
+      sh.before = acc;
+      sh.equal = sh.hist[chosen];
+    }
+    __syncthreads();
+  }
+  val_out = sh.prefix;
+  before_out = sh.before;
+  equal_out = sh.equal;
+  __syncthreads();
+}
+
+__device__ __forceinline__ int index_start_shift(int n) { return n <= (1 << 8) ? 0 : n <= (1 << 16) ? 8 : n <= (1 << 24) ? 16 : 24; }
+
+__device__ u64 block_sum_u64(Shared& sh, u64 v) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) sh.red64[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    u64 t = lane < (int)(blockDim.x >> 5) ? sh.red64[lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) sh.total = t;
+  }
+  __syncthreads();
+  return sh.total;
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, int n, float temperature, int top_k,
+              float top_p, u64* __restrict__ rng_state, const int* __restrict__ state_index) {
+  __shared__ Shared sh;
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* row = logits + (size_t)r * ld;
+
+  // ---- highest logit, first index on ties
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = tid; i < n; i += blockDim.x) {
+    const float v = row[i];
+    if (v > bv) {  // strictly greater keeps the first; NaN never enters
+      bv = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if (lane == 0) {
+    sh.redv[warp] = bv;
+    sh.redi[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    bv = lane < (int)(blockDim.x >> 5) ? sh.redv[lane] : -INFINITY;
+    bi = lane < (int)(blockDim.x >> 5) ? sh.redi[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      sh.bestv = bv;
+      sh.besti = bi == 0x7fffffff ? 0 : bi;
+    }
+  }
+  __syncthreads();
+  const float lmax = sh.bestv;
+  if (!(temperature > 0.f) || rng_state == nullptr) {
+    if (tid == 0) out[r] = sh.besti;
+    return;
+  }
+
+  // ---- one draw from this row's xorshift64* stream
+  if (tid == 0) {
+    const int si = state_index ? state_index[r] : r;
+    u64 s = rng_state[si];
+    if (s == 0) s = 1;
+    s ^= s >> 12;
+    s ^= s << 25;
+    s ^= s >> 27;
+    rng_state[si] = s;
+    sh.u = (float)((s * 0x2545F4914F6CDD1DULL) >> 40) / 16777216.0f;
+  }
+
+  const int ishift = index_start_shift(n);
+  unsigned val;
+  u64 before, equal;
+
+  // ---- top-k: the k-th highest key, and up to which token id keys equal to it still count
+  unsigned kth = 0;
+  int kth_last = n;  // ids <= kth_last with key == kth are candidates
+  if (top_k > 0 && top_k < n) {
+    radix_descend<true>(sh, n, 24, (u64)top_k,
+                        [&](int i, unsigned& v, u64& w) { v = order_key(row[i]); w = 1; return true; }, val, before, equal);
+    kth = val;
+    const u64 need = (u64)top_k - before;
+    if (need < equal) {
+      radix_descend<false>(sh, n, ishift, need,
+                           [&](int i, unsigned& v, u64& w) { v = (unsigned)i; w = 1; return order_key(row[i]) == kth; }, val,
+                           before, equal);
+      kth_last = (int)val;
+    }
+  }
+  auto candidate = [&](int i, unsigned key) { return key > kth || (key == kth && i <= kth_last); };
+
+  // ---- total weight of the candidates
+  u64 mine = 0;
+  for (int i = tid; i < n; i += blockDim.x) {
+    const float v = row[i];
+    if (candidate(i, order_key(v))) mine += fixed_weight(v, lmax, temperature);
+  }
+  const u64 total = block_sum_u64(sh, mine);
+
+  // ---- top-p: where the running share first reaches top_p
+  unsigned cut = 0;
+  int cut_last = n;
+  u64 mass = total;
+  if (top_p < 1.0f && total > 0) {
+    u64 target = (u64)ceil((double)top_p * (double)total);
+    target = target < 1 ? 1 : (target > total ? total : target);
+    radix_descend<true>(sh, n, 24, target,
+                        [&](int i, unsigned& v, u64& w) {
+                          const float x = row[i];
+                          v = order_key(x);
+                          w = fixed_weight(x, lmax, temperature);
+                          return candidate(i, v);
+                        },
+                        val, before, equal);
+    cut = val;
+    const u64 wc = fixed_weight(key_value(cut), lmax, temperature);
+    if (wc > 0) {
+      const u64 n_eq = equal / wc;
+      u64 j = (target - before + wc - 1) / wc;
+      j = j < 1 ? 1 : (j > n_eq ? n_eq : j);
+      mass = before + j * wc;
+      if (j < n_eq) {
+        radix_descend<false>(sh, n, ishift, j,
+                             [&](int i, unsigned& v, u64& w) {
+                               v = (unsigned)i;
+                               w = 1;
+                               return order_key(row[i]) == cut && candidate(i, cut);
+                             },
+                             val, before, equal);
+        cut_last = (int)val;
+      }
+    } else {
+      mass = before + equal;
+    }
+  }
+  auto kept = [&](int i, unsigned key) { return candidate(i, key) && (key > cut || (key == cut && i <= cut_last)); };
+
+  // ---- the draw: the first kept candidate, in descending order, at which the running sum reaches u * mass
+  u64 target = (u64)ceil((double)sh.u * (double)mass);
+  target = target < 1 ? 1 : (target > mass ? mass : target);
+  radix_descend<true>(sh, n, 24, target,
+                      [&](int i, unsigned& v, u64& w) {
+                        const float x = row[i];
+                        v = order_key(x);
+                        w = fixed_weight(x, lmax, temperature);
+                        return kept(i, v);
+                      },
+                      val, before, equal);
+  const unsigned sel = val;
+  const u64 ws = fixed_weight(key_value(sel), lmax, temperature);
+  u64 jj = 1;
+  if (ws > 0) {
+    const u64 n_eq = equal / ws;
+    jj = (target - before + ws - 1) / ws;
+    jj = jj < 1 ? 1 : (jj > n_eq ? n_eq : jj);
+  }
+  radix_descend<false>(sh, n, ishift, jj,
+                       [&](int i, unsigned& v, u64& w) {
+                         v = (unsigned)i;
+                         w = 1;
+                         return order_key(row[i]) == sel && kept(i, sel);
+                       },
+                       val, before, equal);
+  if (tid == 0) out[r] = equal > 0 ? (int)val : sh.besti;
+}
+
+}  // namespace
+
+extern "C" int gi_sample(int* out_tokens, const float* logits, long ld, int n_rows, int vocab, float temperature,
+                         int top_k, float top_p, unsigned long long* rng_state, const int* state_index, void* stream) {
+  if (n_rows <= 0) return GI_OK;
+  if (vocab <= 0) return gi::fail(GI_ERR_ARG, "sample: empty vocabulary");
+  if (temperature > 0.f && !rng_state) return gi::fail(GI_ERR_ARG, "sample: temperature sampling needs generator states");
+  if (top_k < 0) return gi::fail(GI_ERR_ARG, "sample: top_k must not be negative");
+  sample_kernel<<<n_rows, THREADS, 0, (cudaStream_t)stream>>>(out_tokens, logits, ld, vocab, temperature, top_k, top_p,
+                                                             rng_state, state_index);
+  return gi::check_launch("sample");
+}

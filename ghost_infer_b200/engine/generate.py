@@ -1,0 +1,138 @@
+"""The generation loop above the step function.
+
+One sequence in the reference (src/main.rs:702-786): the prompt must be non-empty and leave room; it is
+read in one go; then, while fewer than max_new tokens were generated and the context has room: sample
+from the current logits, count the token, stop if it is a stop token (which is neither kept nor fed),
+else keep it and feed it.  Here the same happens for batches: requests are taken in order, as many as
+`batch_size` and the cache allow; all prompts of a batch run in one step; each following step carries
+one token for every sequence still alive; a sequence that ends leaves the batch at once and its slot
+goes back when the batch ends, to be used by the next batch.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..cache.pages import PAGE_TOKENS, CacheFullError, pages_for
+from .step import StepEntry
+
+
+@dataclass
+class GenerationResult:
+    prompt_tokens: int
+    tokens: List[int] = field(default_factory=list)
+    finish_reason: str = ""            # "stop", "length" or "capacity"
+    stopped_on: Optional[int] = None
+
+
+@dataclass
+class GenerationStats:
+    """The reference's Stats (src/main.rs:587-598), summed over batches."""
+    prompt_tokens: int = 0
+    prompt_secs: float = 0.0
+    gen_tokens: int = 0
+    gen_secs: float = 0.0
+    batches: int = 0
+    steps: int = 0
+
+
+class GenerationLoop:
+    """`engine` needs `.cache` (open_slot, close_slot, length, free_pages, max_seq_len) and
+    `.step(entries) -> logits`; `sampler` needs `.start(n)` and `.pick(logits, request_ids) -> tokens`."""
+
+    def __init__(self, engine, sampler, stop_token_ids: Sequence[int] = (), batch_size: int = 8,
+                 on_token: Optional[Callable[[int, int], None]] = None):
+        if batch_size < 1:
+            raise ValueError("batch_size must be at least 1")
+        self.engine = engine
+        self.sampler = sampler
+        self.stop = frozenset(int(t) for t in stop_token_ids)
+        self.batch_size = batch_size
+        self.on_token = on_token
+        self.stats = GenerationStats()
+
+    # ---- which requests form the next batch -------------------------------------------------------
+    def _admit(self, prompts: Sequence[Sequence[int]], first: int) -> int:
+        """How many requests starting at `first` go into the next batch."""
+        cache = self.engine.cache
+        free = cache.free_pages
+        free_slots = cache.slots.free_slots
+        n = 0
+        for i in range(first, min(len(prompts), first + self.batch_size)):
+            need = pages_for(len(prompts[i]) + 1)
+            if need > free or n >= free_slots:
+                break
+            free -= need
+            n += 1
+        if n == 0:
+            raise CacheFullError(
+                f"request {first} does not fit: its prompt of {len(prompts[first])} tokens needs "
+                f"{pages_for(len(prompts[first]) + 1)} pages of {PAGE_TOKENS} tokens, {cache.free_pages} are free")
+        return n
+
+    def run(self, prompts: Sequence[Sequence[int]], max_new: int) -> List[GenerationResult]:
+        cache = self.engine.cache
+        for i, p in enumerate(prompts):
+            if len(p) == 0:
+                raise ValueError(f"request {i}: empty prompt")          # src/main.rs:703
+            if len(p) >= cache.max_seq_len:
+                raise ValueError(f"request {i}: prompt does not fit: {len(p)} tokens >= context {cache.max_seq_len}")  # :706
+        results = [GenerationResult(prompt_tokens=len(p)) for p in prompts]
+        self.sampler.start(len(prompts))
+        first = 0
+        while first < len(prompts):
+            n = self._admit(prompts, first)
+            self._run_batch(prompts, results, list(range(first, first + n)), max_new)
+            first += n
+        return results
+
+    def _run_batch(self, prompts, results, ids: List[int], max_new: int) -> None:
+        cache = self.engine.cache
+        slots = {i: cache.open_slot() for i in ids}
+        self.stats.batches += 1
+        try:
+            t0 = time.perf_counter()
+            live = list(ids)
+            if max_new <= 0:
+                for i in live:
+                    results[i].finish_reason = "length"
+                return
+            logits = self.engine.step([StepEntry(slots[i], prompts[i], [len(prompts[i]) - 1]) for i in live])
+            self.stats.steps += 1
+            picked = self.sampler.pick(logits, live)
+            self.stats.prompt_tokens += sum(len(prompts[i]) for i in live)
+            t1 = time.perf_counter()
+            self.stats.prompt_secs += t1 - t0
+            while True:
+                feed = []
+                for i, tok in zip(live, picked):
+                    res = results[i]
+                    self.stats.gen_tokens += 1
+                    if tok in self.stop:                      # counted, not kept, not fed (src/main.rs:772-776)
+                        res.finish_reason, res.stopped_on = "stop", tok
+                        continue
+                    res.tokens.append(tok)
+                    if self.on_token is not None:
+                        self.on_token(i, tok)
+                    if len(res.tokens) >= max_new:
+                        res.finish_reason = "length"
+                    elif cache.length(slots[i]) + 1 > cache.max_seq_len:
+                        res.finish_reason = "capacity"        # the reference's `pos < ctx` (src/main.rs:770)
+                    else:
+                        feed.append((i, tok))
+                if not feed:
+                    break
+                try:
+                    logits = self.engine.step([StepEntry(slots[i], [tok], [0]) for i, tok in feed])
+                except CacheFullError:
+                    for i, _ in feed:
+                        results[i].finish_reason = "capacity"
+                    break
+                self.stats.steps += 1
+                live = [i for i, _ in feed]
+                picked = self.sampler.pick(logits, live)
+            self.stats.gen_secs += time.perf_counter() - t1
+        finally:
+            for s in slots.values():
+                cache.close_slot(s)

@@ -1,0 +1,267 @@
+"""Typed Python wrappers over the kernel library's C entry points.
+
+Each wrapper checks shapes, dtypes, devices and contiguity on the host (the reference validates
+token ids, capacity and sizes before any launch: src/model.rs:974-982, src/cuda.rs:8644-8652), then
+launches on torch's current stream.  Tensors are torch tensors on a CUDA device; nothing here runs on
+the CPU and nothing falls back to library code.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+from typing import Optional
+
+import torch
+
+from .library import KernelError, last_error, load
+
+F32, BF16 = 0, 1
+GEMM_STORE, GEMM_ACCUM_F32 = 0, 1
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_bound = None
+
+
+def _bind():
+    global _bound
+    if _bound is not None:
+        return _bound
+    lib = load()
+    P, I, L, F = c_void_p, c_int, c_long, c_float
+    sigs = {
+        "gi_embed": [P, P, I, P, I, I, I, P],
+        "gi_rmsnorm": [P, I, P, P, I, P, I, I, F, P],
+        "gi_silu_mul": [P, P, I, I, I, P],
+        "gi_gemm_generic": [P, I, I, P, I, P, I, I, I, I, L, L, L, P],
+        "gi_rope_cache_write": [P, I, L, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P],
+        "gi_attn_prefill_generic": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
+        "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
+        "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
+    }
+    for name, argtypes in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    _bound = lib
+    return lib
+
+
+def _check(lib, rc: int) -> None:
+    if rc != 0:
+        raise KernelError(last_error(lib) or f"kernel entry point failed with code {rc}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor, what: str) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what} must live on a CUDA device; there is no CPU path")
+
+
+def _rows(t: torch.Tensor, what: str) -> int:
+    """Leading dimension (in elements) of a 2-D tensor whose rows are contiguous."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what} must be 2-D with contiguous rows, got shape {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0)
+
+
+def _i32(t: Optional[torch.Tensor], what: str):
+    if t is None:
+        return None
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{what} must be a contiguous int32 tensor")
+    _cuda(t, what)
+    return t.data_ptr()
+
+
+# ------------------------------------------------------------------------------------------------
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _bind()
+    _cuda(table, "embedding table")
+    if table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("the embedding table must be a contiguous [vocab, width] matrix")
+    n, (vocab, d) = tokens.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, d), dtype=torch.float32, device=table.device)
+    _check(lib, lib.gi_embed(out.data_ptr(), table.data_ptr(), _dt(table, "embedding table"), _i32(tokens, "tokens"),
+                             n, d, vocab, _stream()))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _bind()
+    _cuda(x, "rmsnorm input")
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("rmsnorm input must be a contiguous float32 [rows, width] matrix")
+    d = x.shape[1]
+    if weight.numel() != d or not weight.is_contiguous():
+        raise KernelError(f"rmsnorm weight has {weight.numel()} values, the rows are {d} wide")
+    n = x.shape[0] if rows is None else rows.numel()
+    if out is None:
+        out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    _check(lib, lib.gi_rmsnorm(out.data_ptr(), _dt(out, "rmsnorm output"), x.data_ptr(), weight.data_ptr(),
+                               _dt(weight, "rmsnorm weight"), _i32(rows, "rows"), n, d, float(eps), _stream()))
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _bind()
+    _cuda(gate_up, "gate/up rows")
+    if gate_up.dim() != 2 or not gate_up.is_contiguous() or gate_up.shape[1] % 2:
+        raise KernelError("gate/up rows must be a contiguous [rows, 2 * width] matrix")
+    n, f = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((n, f), dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib, lib.gi_silu_mul(out.data_ptr(), gate_up.data_ptr(), _dt(gate_up, "gate/up rows"), n, f, _stream()))
+    return out
+
+
+def gemm_generic(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
+    """out[M, N] (+)= a[M, K] @ w[N, K]^T with 32-bit accumulation on CUDA cores."""
+    lib = _bind()
+    _cuda(a, "activations")
+    _cuda(w, "weights")
+    lda, ldw = _rows(a, "activations"), _rows(w, "weights")
+    m, k = a.shape
+    n, kw = w.shape
+    if k != kw:
+        raise KernelError(f"matrix product: activations are {k} wide, the weights take {kw}")
+    if out is None:
+        if accumulate:
+            raise KernelError("matrix product: accumulation needs an output to add to")
+        out = torch.empty((m, n), dtype=out_dtype or a.dtype, device=a.device)
+    ldo = _rows(out, "output")
+    if out.shape != (m, n):
+        raise KernelError(f"matrix product: output is {tuple(out.shape)}, wanted {(m, n)}")
+    mode = GEMM_ACCUM_F32 if accumulate else GEMM_STORE
+    _check(lib, lib.gi_gemm_generic(out.data_ptr(), _dt(out, "output"), mode, a.data_ptr(), _dt(a, "activations"),
+                                    w.data_ptr(), _dt(w, "weights"), m, n, k, lda, ldw, ldo, _stream()))
+    return out
+
+
+def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                     block_table: Optional[torch.Tensor], kcache: Optional[torch.Tensor],
+                     vcache: Optional[torch.Tensor], inv_freq: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                     rotary_dim: int, adjacent: bool, write_cache: bool) -> None:
+    lib = _bind()
+    _cuda(qkv, "q/k/v rows")
+    ld = _rows(qkv, "q/k/v rows")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError(f"q/k/v rows are {qkv.shape[1]} wide, wanted {(n_heads + 2 * n_kv) * head_dim}")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2:
+        raise KernelError("the rotary frequency table must hold rotary_dim / 2 float32 values")
+    if write_cache:
+        if kcache is None or vcache is None or block_table is None:
+            raise KernelError("cache write without a cache")
+        if kcache.dtype != qkv.dtype or vcache.dtype != qkv.dtype:
+            raise KernelError(f"the cache is {kcache.dtype}, the step runs in {qkv.dtype}")
+        if tuple(kcache.shape[1:]) != (n_kv, 64, head_dim) or not kcache.is_contiguous() or not vcache.is_contiguous():
+            raise KernelError(f"cache pages must be contiguous [pages, {n_kv}, 64, {head_dim}], got {tuple(kcache.shape)}")
+    max_pages = block_table.shape[1] if block_table is not None else 0
+    _check(lib, lib.gi_rope_cache_write(
+        qkv.data_ptr(), _dt(qkv, "q/k/v rows"), ld, _i32(positions, "positions"), _i32(slots, "slots"),
+        _i32(block_table, "block table"), max_pages,
+        kcache.data_ptr() if kcache is not None else None, vcache.data_ptr() if vcache is not None else None,
+        inv_freq.data_ptr(), n, n_heads, n_kv, head_dim, rotary_dim, int(adjacent), int(write_cache), _stream()))
+
+
+def attn_prefill_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                         cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
+                         max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                         window: Optional[int], out: torch.Tensor) -> torch.Tensor:
+    lib = _bind()
+    _cuda(q, "queries")
+    ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
+    if kcache.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("queries, cache and attention output must share a dtype")
+    _check(lib, lib.gi_attn_prefill_generic(
+        out.data_ptr(), ldo, q.data_ptr(), ldq, _dt(q, "queries"), kcache.data_ptr(), vcache.data_ptr(),
+        _i32(block_table, "block table"), block_table.shape[1], _i32(cu_seqlens, "cu_seqlens"),
+        _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"), n_seqs, max_q_len, n_heads, n_kv, head_dim,
+        float(scale), int(window or 0), _stream()))
+    return out
+
+
+def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                        seq_slots: torch.Tensor, seq_lens: torch.Tensor, n_seqs: int, n_heads: int, n_kv: int,
+                        head_dim: int, scale: float, window: Optional[int], n_splits: int, out: torch.Tensor,
+                        part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _bind()
+    _cuda(q, "queries")
+    ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
+    if kcache.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("queries, cache and attention output must share a dtype")
+    if n_splits > 1:
+        if part_o is None or part_ml is None:
+            raise KernelError("attention slices need scratch memory")
+        if part_o.dtype != torch.float32 or part_o.numel() < n_seqs * n_heads * n_splits * head_dim:
+            raise KernelError("attention scratch for outputs is too small")
+        if part_ml.dtype != torch.float32 or part_ml.numel() < n_seqs * n_heads * n_splits * 2:
+            raise KernelError("attention scratch for maxima and sums is too small")
+    _check(lib, lib.gi_attn_decode_generic(
+        out.data_ptr(), ldo, part_o.data_ptr() if part_o is not None else None,
+        part_ml.data_ptr() if part_ml is not None else None, q.data_ptr(), ldq, _dt(q, "queries"),
+        kcache.data_ptr(), vcache.data_ptr(), _i32(block_table, "block table"), block_table.shape[1],
+        _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"), n_seqs, n_heads, n_kv, head_dim, float(scale),
+        int(window or 0), int(n_splits), _stream()))
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
+           rng_state: Optional[torch.Tensor] = None, state_index: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of `logits` (float32).  temperature <= 0: the highest logit, first on ties."""
+    lib = _bind()
+    _cuda(logits, "logits")
+    if logits.dtype != torch.float32:
+        raise KernelError("logits must be float32")
+    ld = _rows(logits, "logits")
+    n, vocab = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    if rng_state is not None:
+        if rng_state.dtype != torch.int64 or not rng_state.is_contiguous():
+            raise KernelError("generator states must be a contiguous int64 tensor")
+        _cuda(rng_state, "generator states")
+    _check(lib, lib.gi_sample(out.data_ptr(), logits.data_ptr(), ld, n, vocab, float(temperature), int(top_k),
+                              float(top_p), rng_state.data_ptr() if rng_state is not None else None,
+                              _i32(state_index, "state index"), _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Dispatchers: the one place where a kernel is chosen for an operation.
+def linear(h: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
+    return gemm_generic(h, w, out=out, out_dtype=out_dtype, accumulate=accumulate)
+
+
+def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim: int, scale: float,
+              window: Optional[int], out: torch.Tensor) -> torch.Tensor:
+    """Attention of a step's tokens over the cache (which already holds the step's own keys and values).
+    The queries are the first n_heads * head_dim columns of the packed rows `qkv`."""
+    if memory.k is None:
+        raise KernelError("attention needs a cache to read from")
+    if step.is_decode:
+        n_splits = step.decode_splits(n_kv, n_heads // n_kv)
+        part_o = part_ml = None
+        if n_splits > 1:
+            part_o = torch.empty((step.n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
+        return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
+                                   step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
+    return attn_prefill_generic(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots,
+                                step.seq_pos0, step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out)

@@ -1,0 +1,71 @@
+"""Causal grouped-query attention as a mixer.
+
+Order of operations (src/model.rs:1000-1101): q, k, v = Wq h, Wk h, Wv h (one product over the three
+matrices stacked by rows, as the reference's GPU path merges them: src/cuda.rs:7908-7909); position
+encoding on q and k; k and v appended to the cache; head h attends with kv head h / (H / KV) over every
+cached position up to its own (src/model.rs:1320-1419), scores scaled by `scale` (1/sqrt(head_dim) for
+Llama, src/model.rs:271); residual += Wo att.  With `window` = w a query sees only the last w positions.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..cache.sequence_cache import CacheRequest
+from ..kernels import ops
+from .base import Mixer, WeightSpec
+from .linear import linear
+from .registry import lookup, register
+
+
+@register("mixer", "gqa_attention")
+class GqaAttention(Mixer):
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden_size"])
+        self.n_heads = int(params["num_heads"])
+        self.n_kv = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.scale = float(params["scale"])
+        self.window = params.get("window")
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"{self.n_heads} heads do not divide into {self.n_kv} kv heads")
+        pos = params["position"]
+        self.position = lookup("position", pos.kind)(pos.params, prefix) if pos is not None else None
+        self.q_dim = self.n_heads * self.head_dim
+        self.kv_dim = self.n_kv * self.head_dim
+        self.names = {k: f"{prefix}self_attn.{k}_proj.weight" for k in ("q", "k", "v", "o")}
+
+    def weights(self) -> List[WeightSpec]:
+        n = self.names
+        return [WeightSpec(n["q"], (self.q_dim, self.hidden)), WeightSpec(n["k"], (self.kv_dim, self.hidden)),
+                WeightSpec(n["v"], (self.kv_dim, self.hidden)), WeightSpec(n["o"], (self.hidden, self.q_dim))]
+
+    def cache_request(self) -> Optional[CacheRequest]:
+        if self.window:
+            return CacheRequest("window", self.n_kv, self.head_dim, int(self.window))
+        return CacheRequest("full", self.n_kv, self.head_dim)
+
+    def bind(self, tensors, rt) -> None:
+        super().bind(tensors, rt)
+        q, k, v = (rt.place(tensors[self.names[x]]) for x in ("q", "k", "v"))
+        if not (q.dtype == k.dtype == v.dtype):
+            q, k, v = (t.to(torch.float32) for t in (q, k, v))
+        self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
+        del q, k, v
+        self.w_o = rt.place(tensors[self.names["o"]])
+        if self.position is not None:
+            self.position.bind(tensors, rt)
+
+    def forward(self, h, residual, step, memory) -> None:
+        qkv = linear(h, self.w_qkv, out_dtype=self.rt.dtype)
+        if self.position is not None:
+            self.position.encode_and_store(qkv, step, memory, self.n_heads, self.n_kv, self.head_dim)
+        else:
+            ops.rope_cache_write(qkv, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
+                                 step.empty_f32, self.n_heads, self.n_kv, self.head_dim, 0, False,
+                                 memory.writes and memory.k is not None)
+        att = torch.empty((h.shape[0], self.q_dim), dtype=self.rt.dtype, device=h.device)
+        ops.attention(qkv, memory, step, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, att)
+        linear(att, self.w_o, out=residual, accumulate=True)

@@ -1,0 +1,43 @@
+"""SwiGLU feed-forward: residual += Wdown (silu(Wgate h) * (Wup h)), silu(g) = g / (1 + exp(-g)).
+
+No biases; gate and up are one product over the two matrices stacked by rows, as the reference's GPU
+path packs them (src/quant.rs:1135-1154, src/model.rs:1133-1147, src/cuda.rs:9238-9256).
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, WeightSpec
+from .linear import linear
+from .registry import register
+
+
+@register("feed_forward", "swiglu")
+class SwiGlu(FeedForward):
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.names = {k: f"{prefix}mlp.{k}_proj.weight" for k in ("gate", "up", "down")}
+
+    def weights(self) -> List[WeightSpec]:
+        n = self.names
+        return [WeightSpec(n["gate"], (self.inter, self.hidden)), WeightSpec(n["up"], (self.inter, self.hidden)),
+                WeightSpec(n["down"], (self.hidden, self.inter))]
+
+    def bind(self, tensors, rt) -> None:
+        super().bind(tensors, rt)
+        g, u = rt.place(tensors[self.names["gate"]]), rt.place(tensors[self.names["up"]])
+        if g.dtype != u.dtype:
+            g, u = g.to(torch.float32), u.to(torch.float32)
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        del g, u
+        self.w_down = rt.place(tensors[self.names["down"]])
+
+    def forward(self, h, residual, step) -> None:
+        gu = linear(h, self.w_gate_up, out_dtype=self.rt.dtype)
+        act = ops.silu_mul(gu)
+        linear(act, self.w_down, out=residual, accumulate=True)
