@@ -11,7 +11,9 @@ from .config.llama_spec import build_llama_spec
 register_architecture("LlamaForCausalLM", LlamaConfig.from_dict, build_llama_spec, replace=True)
 
 from .engine import Engine, Model, StepEntry  # noqa: E402
+from .api import LLM  # noqa: E402
+from .sampling import SamplingParams  # noqa: E402
 
 __all__ = ["ConfigError", "LlamaConfig", "UnknownArchitectureError", "load_config", "register_architecture",
-           "registered_architectures", "Engine", "Model", "StepEntry"]
+           "registered_architectures", "Engine", "Model", "StepEntry", "LLM", "SamplingParams"]
 __version__ = "0.1.0"

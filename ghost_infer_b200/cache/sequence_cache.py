@@ -67,7 +67,7 @@ class _Group:
         self.first_live: Dict[int, int] = {}           # slot -> first page index still held
         self.table_host = np.zeros((max_slots, max_pages_per_seq), dtype=np.int32)
         self.table_dev: Optional[torch.Tensor] = None
-        self.dirty = True
+        self.dirty: Dict[int, Tuple[int, int]] = {}    # slot -> [first, end) page indices not yet on the device
         self.k: Optional[torch.Tensor] = None
         self.v: Optional[torch.Tensor] = None
         self.dtype = dtype
@@ -161,7 +161,7 @@ class SequenceCache:
             g.pool.give_back(held)
             g.first_live.pop(slot, None)
             g.table_host[slot, :] = 0
-            g.dirty = True
+            g.dirty.pop(slot, None)      # a closed slot's row is never read; it is rewritten when pages come
         self.lengths[slot] = 0
         self.slots.give_back(slot)
 
@@ -188,7 +188,8 @@ class SequenceCache:
                     new = g.pool.take(more)
                     g.pages[s].extend(new)
                     g.table_host[s, have:have + more] = new
-                    g.dirty = True
+                    lo, hi = g.dirty.get(s, (have, have))
+                    g.dirty[s] = (min(lo, have), max(hi, have + more))
 
     def commit(self, slot: int, new_len: int) -> None:
         """The slot now holds `new_len` tokens.  Window groups give back pages no later query can see."""
@@ -204,9 +205,8 @@ class SequenceCache:
                 g.pool.give_back([pages[i] for i in range(first, dead_before)])
                 for i in range(first, dead_before):
                     pages[i] = PagePool.TRASH_PAGE
-                g.table_host[slot, first:dead_before] = 0
+                g.table_host[slot, first:dead_before] = 0    # never read again: the device copy may keep them
                 g.first_live[slot] = dead_before
-                g.dirty = True
 
     def truncate(self, slot: int, pos: int) -> int:
         """Rewinds a slot to `pos` tokens (src/model.rs:799-821: lowering the position is enough for
@@ -224,18 +224,19 @@ class SequenceCache:
                 g.pool.give_back(pages[keep:])
                 g.table_host[slot, keep:len(pages)] = 0
                 del pages[keep:]
-                g.dirty = True
         self.lengths[slot] = pos
         return pos
 
     # ---- device side ------------------------------------------------------------------------
     def sync_tables(self) -> None:
-        """Copies changed page tables to the device (same stream as the kernels that read them)."""
+        """Copies the changed stretches of the page tables to the device, on the stream of the kernels
+        that read them.  Only rows that gained pages since the last call are touched."""
         for g in self._groups:
-            if g.dirty:
-                src = torch.from_numpy(g.table_host)
-                g.table_dev.copy_(src, non_blocking=False)
-                g.dirty = False
+            if not g.dirty:
+                continue
+            for slot, (lo, hi) in g.dirty.items():
+                g.table_dev[slot, lo:hi].copy_(torch.from_numpy(g.table_host[slot, lo:hi]))
+            g.dirty.clear()
 
     def memory(self, entry: int) -> LayerMemory:
         src = self._reads_from.get(entry, entry)

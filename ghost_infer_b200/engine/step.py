@@ -46,6 +46,10 @@ class StepContext:
         self.empty_f32: torch.Tensor = None
         self.fixed_splits: Optional[int] = None
         self.sm_count = 148
+        # the same facts on the host, for parts that plan their work there
+        self.host_q_lens: List[int] = []
+        self.host_slots: List[int] = []
+        self.host_pos0: List[int] = []
 
     def decode_splits(self, n_kv: int, group: int) -> int:
         """Into how many slices of its context a decode block family cuts a sequence."""
@@ -167,6 +171,7 @@ class Engine:
         ctx.logit_rows = dev[o:o + R] if R else None
         ctx.empty_f32 = self._empty_f32
         ctx.sm_count = self._sm_count
+        ctx.host_q_lens, ctx.host_slots, ctx.host_pos0 = lens, [e.slot for e in entries], pos0
         return ctx
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:

@@ -1,0 +1,281 @@
+"""Each kernel alone against a plain float64/float32 PyTorch statement of the same operation, at sizes
+other than the tiny models': odd widths, head sizes 16..256, several group sizes, long contexts."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from ghost_infer_b200.kernels import ops
+from gpu_helpers import paged_from_dense
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("wdtype", DTYPES)
+def test_embed(wdtype):
+    table = rnd(301, 70, dtype=wdtype)
+    toks = torch.tensor([0, 300, 5, 5, 299], dtype=torch.int32, device=DEV)
+    out = ops.embed(table, toks)
+    assert out.dtype == torch.float32 and torch.equal(out, table[toks.long()].float())
+
+
+@pytest.mark.parametrize("odtype", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("d", [70, 1000, 4096])
+def test_rmsnorm(odtype, wdtype, d):
+    x = rnd(9, d, seed=1, scale=3.0)
+    w = (1 + 0.2 * rnd(d, seed=2)).to(wdtype)
+    ref = (x.double() * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-3) * w.double())
+    out = ops.rmsnorm(x, w, 1e-3, odtype)
+    torch.testing.assert_close(out.double(), ref, **tol(odtype))
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    out = ops.rmsnorm(x, w, 1e-3, odtype, rows=rows)
+    torch.testing.assert_close(out.double(), ref[rows.long()], **tol(odtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    gu = rnd(5, 2 * 301, dtype=dtype, seed=3, scale=2.0)
+    g, u = gu[:, :301].double(), gu[:, 301:].double()
+    ref = g / (1 + torch.exp(-g)) * u
+    torch.testing.assert_close(ops.silu_mul(gu).double(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("adtype", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(7, 96, 37), (1, 301, 80), (130, 65, 129), (64, 64, 16)])
+def test_gemm_generic(adtype, wdtype, m, n, k):
+    """Odd sizes, as the reference's own matmul test uses (37 x 96 x 7, src/quant.rs:1437-1461); the
+    tolerance scales with the size of the terms, not of the sum."""
+    a, w = rnd(m, k, dtype=adtype, seed=4), rnd(n, k, dtype=wdtype, seed=5)
+    ref = a.double() @ w.double().T
+    terms = (a.double().abs() @ w.double().abs().T)
+    out = ops.gemm_generic(a, w, out_dtype=torch.float32)
+    assert ((out.double() - ref).abs() <= 1e-6 * terms + 1e-7).all()
+    out16 = ops.gemm_generic(a, w, out_dtype=torch.bfloat16)
+    assert ((out16.double() - ref).abs() <= 2 ** -8 * ref.abs() + 1e-6 * terms + 1e-7).all()
+    acc = rnd(m, n, seed=6)
+    before = acc.clone()
+    ops.gemm_generic(a, w, out=acc, accumulate=True)
+    assert ((acc.double() - (before.double() + ref)).abs() <= 1e-6 * (terms + before.abs().double()) + 1e-6).all()
+
+
+def test_gemm_strided_rows():
+    a_full, w = rnd(10, 100, seed=7), rnd(33, 40, seed=8)
+    a = a_full[:, 20:60]                       # rows 100 apart, 40 wide
+    out_full = torch.zeros(10, 50, device=DEV)
+    ops.gemm_generic(a, w, out=out_full[:, 5:38])
+    torch.testing.assert_close(out_full[:, 5:38], a @ w.T, rtol=1e-5, atol=1e-5)
+    assert float(out_full[:, :5].abs().sum()) == 0 and float(out_full[:, 38:].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,rot,adjacent", [(16, 16, False), (48, 48, False), (128, 128, False), (64, 32, False), (32, 32, True)])
+def test_rope_and_cache_write(dtype, hd, rot, adjacent):
+    H, KV, T = 5, 2, 6
+    qkv = rnd(T, (H + 2 * KV) * hd, dtype=dtype, seed=9)
+    orig = qkv.clone()
+    positions = torch.tensor([0, 1, 63, 64, 200, 77], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([0, 0, 0, 0, 1, 1], dtype=torch.int32, device=DEV)
+    bt = torch.tensor([[3, 1, 0, 0], [2, 5, 6, 4]], dtype=torch.int32, device=DEV)
+    kc = torch.zeros(7, KV, 64, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    inv = torch.from_numpy(pl.rotary_inv_freq(rot, 10000.0, None)).to(DEV)
+    ops.rope_cache_write(qkv, positions, slots, bt, kc, vc, inv, H, KV, hd, rot, adjacent, True)
+    pairing = "adjacent" if adjacent else "half"
+    o = orig.double().cpu().numpy()
+    pos = positions.cpu().numpy()
+
+    def rot_ref(x, heads):
+        x = x.reshape(T, heads, hd)
+        y = x.copy()
+        y[:, :, :rot] = pl.rope(x[:, :, :rot].reshape(T, heads * rot), pos, inv.cpu().numpy(), rot, pairing).reshape(T, heads, rot)
+        return y.reshape(T, heads * hd)
+
+    q_ref = rot_ref(o[:, :H * hd], H)
+    k_ref = rot_ref(o[:, H * hd:(H + KV) * hd], KV)
+    v_ref = o[:, (H + KV) * hd:]
+    t = tol(dtype)
+    np.testing.assert_allclose(qkv[:, :H * hd].double().cpu().numpy(), q_ref, rtol=t["rtol"], atol=t["atol"])
+    assert torch.equal(qkv[:, H * hd:], orig[:, H * hd:])          # k and v rows are left as they were
+    for i in range(T):
+        page = int(bt[int(slots[i]), int(pos[i]) // 64])
+        got_k = kc[page, :, int(pos[i]) % 64].double().cpu().numpy().reshape(-1)
+        got_v = vc[page, :, int(pos[i]) % 64].double().cpu().numpy().reshape(-1)
+        np.testing.assert_allclose(got_k, k_ref[i], rtol=t["rtol"], atol=t["atol"])
+        np.testing.assert_array_equal(got_v, v_ref[i])
+    assert float(kc[0].abs().sum()) == 0                            # nobody wrote to the trash page
+
+
+def attention_ref(q, k, v, lens_q, pos0, H, KV, hd, scale, window):
+    """q [B, Q, H*hd] at positions pos0[b]..; k, v dense [B, S, KV, hd].  float64."""
+    out = torch.zeros_like(q, dtype=torch.float64)
+    g = H // KV
+    for b in range(q.shape[0]):
+        for i in range(lens_q[b]):
+            p = pos0[b] + i
+            lo = max(0, p - window + 1) if window else 0
+            for h in range(H):
+                kk = k[b, lo:p + 1, h // g].double()
+                vv = v[b, lo:p + 1, h // g].double()
+                s = (kk @ q[b, i, h * hd:(h + 1) * hd].double()) * scale
+                out[b, i, h * hd:(h + 1) * hd] = torch.softmax(s, 0) @ vv
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,hd", [(4, 2, 16), (5, 1, 48), (8, 8, 64), (6, 2, 128), (2, 1, 256), (16, 2, 80)])
+@pytest.mark.parametrize("window", [None, 37])
+def test_attention_prefill(dtype, H, KV, hd, window):
+    """Ragged batch: sequences that start at position 0 and one that goes on after 70 cached positions."""
+    lens_q, pos0 = [1, 45, 100, 33], [0, 0, 0, 70]
+    B, S = 4, 128
+    k = rnd(B, S, KV, hd, dtype=dtype, seed=10)
+    v = rnd(B, S, KV, hd, dtype=dtype, seed=11)
+    q = rnd(B, max(lens_q), H * hd, dtype=dtype, seed=12)
+    lens_kv = [p + n for p, n in zip(pos0, lens_q)]
+    kc, vc, bt = paged_from_dense(k, v, lens_kv, seed=3)
+    flat = torch.cat([q[b, :lens_q[b]] for b in range(B)])
+    cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    out = torch.full_like(flat, float("nan"))
+    ops.attn_prefill_generic(flat, kc, vc, bt, cu, slots, torch.tensor(pos0, dtype=torch.int32, device=DEV), B,
+                             max(lens_q), H, KV, hd, 0.21, window, out)
+    ref = attention_ref(q, k, v, lens_q, pos0, H, KV, hd, 0.21, window)
+    ref = torch.cat([ref[b, :lens_q[b]] for b in range(B)])
+    torch.testing.assert_close(out.double(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,hd", [(4, 2, 16), (5, 1, 48), (8, 8, 64), (32, 8, 128), (2, 1, 256), (24, 2, 80)])
+@pytest.mark.parametrize("window,splits", [(None, 1), (None, 5), (100, 1), (100, 3)])
+def test_attention_decode(dtype, H, KV, hd, window, splits):
+    lens = [1, 64, 65, 700, 333]
+    B, S = len(lens), 704
+    k = rnd(B, S, KV, hd, dtype=dtype, seed=13)
+    v = rnd(B, S, KV, hd, dtype=dtype, seed=14)
+    q = rnd(B, 1, H * hd, dtype=dtype, seed=15)
+    kc, vc, bt = paged_from_dense(k, v, lens, seed=4)
+    out = torch.full((B, H * hd), float("nan"), dtype=dtype, device=DEV)
+    part_o = torch.full((B * H * splits * hd,), float("nan"), device=DEV)
+    part_ml = torch.full((B * H * splits * 2,), float("nan"), device=DEV)
+    ops.attn_decode_generic(q[:, 0], kc, vc, bt, torch.arange(B, dtype=torch.int32, device=DEV),
+                            torch.tensor(lens, dtype=torch.int32, device=DEV), B, H, KV, hd, 0.17, window, splits, out,
+                            part_o, part_ml)
+    ref = attention_ref(q, k, v, [1] * B, [n - 1 for n in lens], H, KV, hd, 0.17, window)[:, 0]
+    torch.testing.assert_close(out.double(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("decode", [False, True])
+@pytest.mark.parametrize("window", [None, 50])
+def test_attention_finds_one_far_key(decode, window):
+    """Random keys would hide a missed row among hundreds.  Here one key, far back (or exactly at the
+    window's edge), is made to dominate the softmax, and its value is unlike every other."""
+    H, KV, hd, n = 4, 2, 32, 600
+    k = 0.01 * rnd(1, n, KV, hd, seed=16)
+    v = 0.01 * rnd(1, n, KV, hd, seed=17)
+    q = rnd(1, 1, H * hd, seed=18)
+    pos = n - 1
+    for kvh, target in ((0, 3), (1, pos - (window - 1) if window else 130)):
+        # the key that matches the query of the group's first head, scaled up
+        k[0, target, kvh] = 4.0 * q[0, 0, (kvh * 2) * hd:(kvh * 2 + 1) * hd]
+        v[0, target, kvh] = 100.0 + kvh
+        if window:
+            k[0, pos - window, kvh] = 40.0 * q[0, 0, (kvh * 2) * hd:(kvh * 2 + 1) * hd]   # just outside: must not count
+            v[0, pos - window, kvh] = -500.0
+    kc, vc, bt = paged_from_dense(k, v, [n], seed=5)
+    ref = attention_ref(q, k, v, [1], [pos], H, KV, hd, 1.0, window)[:, 0]
+    if window:
+        assert float(ref[0, 2 * hd]) > 90                    # the edge key is inside and wins for head 2
+        assert float(ref.min()) > -1                         # the key just outside the window plays no part
+    else:
+        assert float(ref[0, 2 * hd]) > 90
+    out = torch.zeros((1, H * hd), device=DEV)
+    one = torch.ones(1, dtype=torch.int32, device=DEV)
+    if decode:
+        po, pml = torch.zeros(H * 4 * hd, device=DEV), torch.zeros(H * 4 * 2, device=DEV)
+        ops.attn_decode_generic(q[:, 0], kc, vc, bt, 0 * one, n * one, 1, H, KV, hd, 1.0, window, 4, out, po, pml)
+    else:
+        # the last position as a one-token chunk after n - 1 cached ones
+        ops.attn_prefill_generic(q[:, 0], kc, vc, bt, torch.tensor([0, 1], dtype=torch.int32, device=DEV), 0 * one,
+                                 pos * one, 1, 1, H, KV, hd, 1.0, window, out)
+    torch.testing.assert_close(out.double(), ref, rtol=1e-4, atol=1e-4)
+
+
+def test_argmax_first_on_ties_and_nan():
+    logits = torch.zeros(4, 1000, device=DEV)
+    logits[0, 17] = 3.0
+    logits[0, 800] = 3.0                 # the first of the highest wins (src/sampler.rs:136-142)
+    logits[1, 999] = 1.0
+    logits[2, :] = -5.0
+    logits[2, 500] = float("nan")        # NaN never wins (src/cuda.rs:3540-3570)
+    logits[2, 501] = -4.0
+    logits[3, :] = float("-inf")
+    out = ops.sample(logits, 0.0, 0, 1.0).cpu().tolist()
+    assert out == [17, 999, 501, 0]
+
+
+@pytest.mark.parametrize("vocab", [301, 5000, 128256])
+@pytest.mark.parametrize("temp,top_k,top_p", [(0.8, 0, 1.0), (0.7, 40, 0.9), (1.5, 0, 0.9), (0.3, 5, 1.0), (1.0, 1000, 0.5), (2.0, 3, 0.2)])
+def test_sampler_matches_the_plain_sampler(vocab, temp, top_k, top_p):
+    """Same logits, same generator stream: the device picks what the plain walk over the sorted list picks.
+    Several draws per row advance the state as the plain generator does."""
+    rows = 6
+    g = torch.Generator().manual_seed(vocab)
+    logits = (torch.randn(rows, vocab, generator=g) * 2.0)
+    logits[1, :50] = logits[1, 0]                       # ties, ordered by token id
+    logits[2] = torch.round(logits[2])                  # many ties
+    dev = logits.to(DEV)
+    seeds = [1, 2, 3, 99, 2 ** 40 + 7, 12345]
+    state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    gens = [pl.XorShift64Star(s) for s in seeds]
+    for draw in range(3):
+        got = ops.sample(dev, temp, top_k, top_p, state).cpu().tolist()
+        for r in range(rows):
+            want = pl.sample(logits[r].numpy(), temp, top_k, top_p, gens[r])
+            assert got[r] == want, f"row {r} draw {draw}: device {got[r]}, plain {want}"
+    assert [int(s) & (2 ** 64 - 1) for s in state.cpu().tolist()] == [g_.s for g_ in gens]
+
+
+def test_sampler_frequencies_and_state_index():
+    logits = torch.tensor([[0.0, 1.0, 2.0, 0.5, -1.0]] * 512, device=DEV)
+    state = torch.arange(1, 1025, dtype=torch.int64, device=DEV)
+    idx = torch.arange(512, 1024, dtype=torch.int32, device=DEV)      # rows use states 512..1023
+    counts = np.zeros(5)
+    for _ in range(40):
+        got = ops.sample(logits, 0.8, 0, 1.0, state, idx).cpu().numpy()
+        counts += np.bincount(got, minlength=5)
+    assert torch.equal(state[:512].cpu(), torch.arange(1, 513, dtype=torch.int64))   # the other states are untouched
+    p = np.exp(np.array([0.0, 1.0, 2.0, 0.5, -1.0]) / 0.8)
+    p /= p.sum()
+    assert np.abs(counts / counts.sum() - p).max() < 0.012
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from ghost_infer_b200.kernels import KernelError
+    with pytest.raises(KernelError):
+        ops.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-5, torch.float32)          # no CPU path
+    with pytest.raises(KernelError):
+        ops.gemm_generic(rnd(2, 8), rnd(3, 9))                                       # widths that do not meet
+    with pytest.raises(KernelError):
+        ops.gemm_generic(rnd(2, 8).half(), rnd(3, 8).half())                         # a dtype nobody wrote
+    H, KV, hd = 2, 1, 272
+    q = rnd(1, H * hd)
+    kc = torch.zeros(2, KV, 64, hd, device=DEV)
+    one = torch.ones(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError) as e:
+        ops.attn_decode_generic(q, kc, kc, one.reshape(1, 1), 0 * one, one, 1, H, KV, hd, 1.0, None, 1, torch.zeros_like(q))
+    assert "272" in str(e.value)
