@@ -1,0 +1,232 @@
+#!/usr/bin/env python3
+"""Benchmark: Llama-3.1-8B-shaped random bf16 weights on one B200.
+
+Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 from 2,048-token contexts (device
+time over `--steps` decode steps, sampling included); `e2e` is the same through the Python entry point
+with host tokens in and out; `prefill` is one 2,048-token prompt; `points` holds decode at batch 1 and 64;
+`roofline` relates the decode step's bytes (every weight once, plus the cache of the live requests) to the
+measured copy bandwidth.  With --gpus N > 1 it says that this library runs on one GPU and exits with 2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIG_8B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": 32, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256,
+    "max_position_embeddings": 131072, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+CONTEXT = 8192
+PROMPT = 2048
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = max((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), default=None)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+
+
+def model_numbers(cfg, layers):
+    d, H, KV, hd = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    F, V = cfg["intermediate_size"], cfg["vocab_size"]
+    per_layer = (H + 2 * KV) * hd * d + d * H * hd + 3 * F * d
+    return {"linear_params_per_layer": per_layer, "head_params": V * d, "norm_params": (2 * layers + 1) * d,
+            "kv_bytes_per_token": 2 * layers * KV * hd * 2}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (recorded in config)")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust program for Windows that reads GGUF "
+                          "files; it is no Python package, and cargo/rustc are not installed, so it cannot be built or installed here"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    W = max(3, args.warmup)
+    K = max(1, args.steps)
+
+    import numpy as np
+    import torch
+    import ghost_infer_b200 as gi
+    from ghost_infer_b200.kernels import ops
+
+    dev = "cuda:0"
+    cfg = dict(CONFIG_8B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    layers = cfg["num_hidden_layers"]
+    pk = peaks()
+    nums = model_numbers(cfg, layers)
+    t0 = time.time()
+    llm = gi.LLM(cfg, dtype="bfloat16", device=dev, max_tokens=64 * CONTEXT, max_slots=64, max_seq_len=CONTEXT, seed=0)
+    eng, cache = llm.engine, llm.cache
+    for g in cache.groups:            # contexts stand in for prompts already read: random keys and values
+        g.k.normal_(0.0, 0.5)
+        g.v.normal_(0.0, 0.5)
+    torch.cuda.synchronize()
+    load_s = time.time() - t0
+    rng = np.random.default_rng(0)
+    V = cfg["vocab_size"]
+    clocks = ClockSampler()
+
+    def decode_run(batch, steps, warmup):
+        """`steps` timed decode steps of `batch` sequences that each hold PROMPT tokens; device time."""
+        slots = [cache.open_slot() for _ in range(batch)]
+        cache.reserve([(s, PROMPT) for s in slots])
+        for s in slots:
+            cache.commit(s, PROMPT)
+        toks = rng.integers(0, V, size=batch).tolist()
+        runner = eng.decoder(slots)
+        picked = torch.zeros(batch, dtype=torch.int32, device=dev)
+        logits = runner.forward(tokens=toks)
+        for _ in range(warmup):
+            ops.sample(logits, 0.0, 0, 1.0, out=picked)
+            logits = runner.forward(dev_tokens=picked)
+        torch.cuda.synchronize()
+        l0 = ops.launches
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):                       # a decode step: pick the token, run it
+            ops.sample(logits, 0.0, 0, 1.0, out=picked)
+            logits = runner.forward(dev_tokens=picked)
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / steps
+        launched = ops.launches - l0
+        ctx_tokens = sum(cache.length(s) for s in slots)
+        for s in slots:
+            cache.close_slot(s)
+        return ms, launched, ctx_tokens
+
+    clocks.start()
+    ms8, launches8, ctx8 = decode_run(8, K, W)
+    value = 8 * 1000.0 / ms8
+    weight_bytes = 2 * (layers * nums["linear_params_per_layer"] + nums["head_params"] + nums["norm_params"])
+    step_bytes = weight_bytes + ctx8 * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms8 * 1e-3) / 1e9
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            ms, _, _ = decode_run(b, max(8, K // 2), W)
+            points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+
+    # prefill: one prompt of 2,048 tokens, logits for its last place
+    prompt = rng.integers(0, V, size=PROMPT).tolist()
+    reps = 3
+
+    def prefill_once():
+        s = cache.open_slot()
+        out = eng.step([gi.StepEntry(s, prompt, [PROMPT - 1])])
+        cache.close_slot(s)
+        return out
+
+    for _ in range(3):
+        prefill_once()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        prefill_once()
+    stop.record()
+    torch.cuda.synchronize()
+    pre_ms = start.elapsed_time(stop) / reps
+    H, hd = cfg["num_attention_heads"], cfg["head_dim"]
+    flops = 2.0 * PROMPT * layers * nums["linear_params_per_layer"] + 2.0 * nums["head_params"] \
+        + layers * 4.0 * H * hd * (PROMPT * (PROMPT + 1) / 2)
+    pre_frac = flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+
+    # end to end through the Python entry point: host token ids in, host token ids out, every step
+    prompts = [rng.integers(0, V, size=PROMPT).tolist() for _ in range(8)]
+    e2e_new = max(8, min(K, 64))
+    llm.generate(prompts, max_new=3, temperature=0.0, stop_token_ids=(), batch_size=8)     # warm-up
+    llm.generate(prompts, max_new=e2e_new, temperature=0.0, stop_token_ids=(), batch_size=8)
+    st = llm.last_stats
+    e2e_steps = max(1, st.steps - 1)
+    e2e = {"value": round((st.gen_tokens - 8) / st.gen_secs, 1) if st.gen_secs > 0 else None, "unit": "tokens/s",
+           "h2d_bytes_per_step": int(eng.bytes_h2d), "d2h_bytes_per_step": 8 * 4,
+           "note": f"LLM.generate, batch 8, {PROMPT}-token prompts, {e2e_new} new tokens each; wall clock of the decode loop"}
+    clk = clocks.stop()
+
+    line = {
+        "metric": "Llama-3.1-8B bf16 decode tok/s @ batch 8 (2,048-token contexts)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms8, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random N(0, 0.02) weights, uniform random token ids, random keys/values as contexts for the device-timed points",
+        "impl": "ours",
+        "config": {"model": "Llama-3.1-8B shape", "layers": layers, "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": V, "global_batch": 8, "seq_len": CONTEXT,
+                   "prompt_len": PROMPT, "parallelism": "1 gpu", "l2": "inputs larger than L2 (weights read once per step)",
+                   "peaks": pk["source"], "load_s": round(load_s, 1)},
+        "e2e": e2e,
+        "gpu_launches": int(launches8),
+        "prefill": {"value": round(PROMPT * 1000.0 / pre_ms, 1), "tokens": PROMPT, "ms": round(pre_ms, 3), "frac": round(pre_frac, 4),
+                    "peak_tflops": pk["bf16_tflops"]},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+        "points": points,
+        "clocks": clk,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -94,6 +94,7 @@ class GenerationLoop:
         try:
             t0 = time.perf_counter()
             live = list(ids)
+            runner = None
             if max_new <= 0:
                 for i in live:
                     results[i].finish_reason = "length"
@@ -124,7 +125,13 @@ class GenerationLoop:
                 if not feed:
                     break
                 try:
-                    logits = self.engine.step([StepEntry(slots[i], [tok], [0]) for i, tok in feed])
+                    if hasattr(self.engine, "decoder"):
+                        want = [slots[i] for i, _ in feed]
+                        if runner is None or runner.slots != want:
+                            runner = self.engine.decoder(want)
+                        logits = runner.forward(tokens=[tok for _, tok in feed])
+                    else:
+                        logits = self.engine.step([StepEntry(slots[i], [tok], [0]) for i, tok in feed])
                 except CacheFullError:
                     for i, _ in feed:
                         results[i].finish_reason = "capacity"

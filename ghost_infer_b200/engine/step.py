@@ -102,6 +102,9 @@ class Engine:
         self._empty_f32 = torch.empty((0,), dtype=torch.float32, device=self.device)
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 148
         self.bytes_h2d = 0
+        self._decode_graphs = {}
+        mixers = [layer.block.mixer for layer in getattr(model, "layers", [])]
+        self._attn_shapes = sorted({(m.n_kv, m.n_heads // m.n_kv) for m in mixers if hasattr(m, "n_kv")})
 
     # ---- host-side checks, before anything is launched (src/model.rs:974-982) -------------------
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -185,6 +188,17 @@ class Engine:
             return None
         h = model.final_norm.forward(x, rows=ctx.logit_rows)
         return model.head.forward(h)
+
+    def decode_splits_for(self, ctx: StepContext) -> int:
+        """One slice count for a captured decode step: what the model's attention layers would choose."""
+        if not self._attn_shapes:
+            return 1
+        return max(ctx.decode_splits(kv, group) for kv, group in self._attn_shapes)
+
+    def decoder(self, slots: Sequence[int], use_graph: bool = True):
+        """A runner of one-token steps for these slots (see engine.decode.DecodeRunner)."""
+        from .decode import DecodeRunner
+        return DecodeRunner(self, slots, use_graph=use_graph)
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs the entries' tokens after what their slots hold.  Returns float32 logits

@@ -47,9 +47,14 @@ def _bind():
     return lib
 
 
-def _check(lib, rc: int) -> None:
+launches = 0   # kernels launched through this module since import (benchmarks report the difference)
+
+
+def _check(lib, rc: int, n: int = 1) -> None:
+    global launches
     if rc != 0:
         raise KernelError(last_error(lib) or f"kernel entry point failed with code {rc}")
+    launches += n
 
 
 def _stream() -> int:
@@ -216,7 +221,7 @@ def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Ten
         part_ml.data_ptr() if part_ml is not None else None, q.data_ptr(), ldq, _dt(q, "queries"),
         kcache.data_ptr(), vcache.data_ptr(), _i32(block_table, "block table"), block_table.shape[1],
         _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"), n_seqs, n_heads, n_kv, head_dim, float(scale),
-        int(window or 0), int(n_splits), _stream()))
+        int(window or 0), int(n_splits), _stream()), 2 if n_splits > 1 else 1)
     return out
 
 
