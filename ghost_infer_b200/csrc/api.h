@@ -19,10 +19,18 @@ int gi_embed(float* out, const void* table, int table_dtype, const int* tokens, 
              void* stream);
 int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows, int n_rows,
                int d, float eps, void* stream);
-int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, void* stream);
+int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, int interleaved, void* stream);
 
 int gi_gemm_generic(void* out, int out_dtype, int mode, const void* A, int a_dtype, const void* W, int w_dtype, int M,
                     int N, int K, long lda, long ldw, long ldo, void* stream);
+
+// mode of gi_gemm_skinny_bf16
+#define GI_SKINNY_STORE_BF16 0
+#define GI_SKINNY_STORE_F32 1
+#define GI_SKINNY_ACCUM_F32 2   // out (float) += product
+#define GI_SKINNY_SWIGLU 3      // W rows interleaved [8 gate | 8 up]; out[M, N/2] bfloat16 = silu(gate) * up
+int gi_gemm_skinny_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
+                        long ldo, void* stream);
 
 int gi_rope_cache_write(void* qkv, int dtype, long ld, const int* positions, const int* slots, const int* block_table,
                         int max_pages, void* kcache, void* vcache, const float* inv_freq, int n_tokens, int n_heads,

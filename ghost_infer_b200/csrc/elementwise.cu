@@ -38,13 +38,16 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
 
 // h = silu(gate) * up from packed rows [gate | up] (src/cuda.rs:3573-3579; silu(g) = g / (1 + exp(-g)),
 // src/quant.rs:1135-1154).
+// `interleaved`: the row holds blocks of 16 values [gate j..j+7 | up j..j+7] instead of [all gates | all ups].
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int f, size_t total) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int f, size_t total, int interleaved) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t m = i / f, c = i % f;
-  const float g = gi::ldf(gu + m * 2 * (size_t)f + c);
-  const float u = gi::ldf(gu + m * 2 * (size_t)f + f + c);
+  const size_t gate_at = interleaved ? (c / 8) * 16 + c % 8 : c;
+  const size_t up_at = interleaved ? gate_at + 8 : (size_t)f + c;
+  const float g = gi::ldf(gu + m * 2 * (size_t)f + gate_at);
+  const float u = gi::ldf(gu + m * 2 * (size_t)f + up_at);
   gi::stf(out + i, g / (1.0f + expf(-g)) * u);
 }
 
@@ -69,11 +72,12 @@ extern "C" int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* 
   return gi::check_launch("rmsnorm");
 }
 
-extern "C" int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, void* stream) {
+extern "C" int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, int interleaved, void* stream) {
   if (n_rows <= 0) return GI_OK;
   if (f <= 0) return gi::fail(GI_ERR_ARG, "silu_mul: bad width %d", f);
+  if (interleaved && f % 8 != 0) return gi::fail(GI_ERR_ARG, "silu_mul: interleaved rows need a width that is a multiple of 8, got %d", f);
   const size_t total = (size_t)n_rows * f;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  GI_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)gate_up, f, total));
+  GI_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)gate_up, f, total, interleaved));
   return gi::check_launch("silu_mul");
 }

@@ -32,7 +32,8 @@ def _bind():
     sigs = {
         "gi_embed": [P, P, I, P, I, I, I, P],
         "gi_rmsnorm": [P, I, P, P, I, P, I, I, F, P],
-        "gi_silu_mul": [P, P, I, I, I, P],
+        "gi_silu_mul": [P, P, I, I, I, I, P],
+        "gi_gemm_skinny_bf16": [P, I, P, P, I, I, I, L, L, L, P],
         "gi_gemm_generic": [P, I, I, P, I, P, I, I, I, I, L, L, L, P],
         "gi_rope_cache_write": [P, I, L, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P],
         "gi_attn_prefill_generic": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
@@ -120,7 +121,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
+    """silu(gate) * up over rows [gate | up], or, `interleaved`, rows of blocks [8 gate | 8 up]."""
     lib = _bind()
     _cuda(gate_up, "gate/up rows")
     if gate_up.dim() != 2 or not gate_up.is_contiguous() or gate_up.shape[1] % 2:
@@ -128,7 +130,8 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch
     n, f = gate_up.shape[0], gate_up.shape[1] // 2
     if out is None:
         out = torch.empty((n, f), dtype=gate_up.dtype, device=gate_up.device)
-    _check(lib, lib.gi_silu_mul(out.data_ptr(), gate_up.data_ptr(), _dt(gate_up, "gate/up rows"), n, f, _stream()))
+    _check(lib, lib.gi_silu_mul(out.data_ptr(), gate_up.data_ptr(), _dt(gate_up, "gate/up rows"), n, f, int(interleaved),
+                                _stream()))
     return out
 
 
@@ -153,6 +156,43 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor
     mode = GEMM_ACCUM_F32 if accumulate else GEMM_STORE
     _check(lib, lib.gi_gemm_generic(out.data_ptr(), _dt(out, "output"), mode, a.data_ptr(), _dt(a, "activations"),
                                     w.data_ptr(), _dt(w, "weights"), m, n, k, lda, ldw, ldo, _stream()))
+    return out
+
+
+SKINNY_STORE_BF16, SKINNY_STORE_F32, SKINNY_ACCUM_F32, SKINNY_SWIGLU = 0, 1, 2, 3
+SKINNY_MAX_ROWS = 64
+
+
+def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the decode product kernel takes these operands: bfloat16, at most 64 rows, 16-byte rows."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 2
+            and 0 < a.shape[0] <= SKINNY_MAX_ROWS and a.shape[1] % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] (op)= a[M, K] @ w[N, K]^T for M <= 64, bfloat16 operands, tensor cores, bound by the bytes of w.
+    mode SKINNY_SWIGLU: w's rows are interleaved [8 gate | 8 up] and out is [M, N / 2] = silu(gate) * up."""
+    lib = _bind()
+    _cuda(a, "activations")
+    _cuda(w, "weights")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the decode product kernel takes bfloat16 operands")
+    lda, ldw = _rows(a, "activations"), _rows(w, "weights")
+    m, k = a.shape
+    n, kw = w.shape
+    if k != kw:
+        raise KernelError(f"matrix product: activations are {k} wide, the weights take {kw}")
+    cols = n // 2 if mode == SKINNY_SWIGLU else n
+    want = {SKINNY_STORE_BF16: torch.bfloat16, SKINNY_SWIGLU: torch.bfloat16}.get(mode, torch.float32)
+    if out is None:
+        if mode == SKINNY_ACCUM_F32:
+            raise KernelError("matrix product: accumulation needs an output to add to")
+        out = torch.empty((m, cols), dtype=want, device=a.device)
+    if out.shape != (m, cols) or out.dtype != want:
+        raise KernelError(f"matrix product: output is {tuple(out.shape)} {out.dtype}, wanted {(m, cols)} {want}")
+    ldo = _rows(out, "output")
+    _check(lib, lib.gi_gemm_skinny_bf16(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), m, n, k, lda, ldw, ldo, _stream()))
     return out
 
 
@@ -251,7 +291,23 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
 # Dispatchers: the one place where a kernel is chosen for an operation.
 def linear(h: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
+    if skinny_ok(h, w):
+        if accumulate:
+            return gemm_skinny(h, w, SKINNY_ACCUM_F32, out)
+        want = out.dtype if out is not None else (out_dtype or h.dtype)
+        if want == torch.bfloat16:
+            return gemm_skinny(h, w, SKINNY_STORE_BF16, out)
+        if want == torch.float32:
+            return gemm_skinny(h, w, SKINNY_STORE_F32, out)
     return gemm_generic(h, w, out=out, out_dtype=out_dtype, accumulate=accumulate)
+
+
+def swiglu_interleaved(h: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+    """silu(Wgate h) * (Wup h) where `w_interleaved` holds gate and up rows in blocks [8 gate | 8 up]."""
+    if skinny_ok(h, w_interleaved):
+        return gemm_skinny(h, w_interleaved, SKINNY_SWIGLU)
+    gu = linear(h, w_interleaved, out_dtype=h.dtype)
+    return silu_mul(gu, interleaved=True)
 
 
 def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim: int, scale: float,

@@ -33,11 +33,23 @@ class SwiGlu(FeedForward):
         g, u = rt.place(tensors[self.names["gate"]]), rt.place(tensors[self.names["up"]])
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        # 16-bit path: gate and up rows interleaved in blocks of 8, so that one block of the decode kernel
+        # holds both halves of an activation and applies SwiGLU before anything is written
+        self.interleaved = (rt.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and self.inter % 8 == 0
+                            and rt.device.type == "cuda")
+        if self.interleaved:
+            blocks = self.inter // 8
+            self.w_gate_up = torch.stack([g.view(blocks, 8, self.hidden), u.view(blocks, 8, self.hidden)], dim=1) \
+                .reshape(2 * self.inter, self.hidden).contiguous()
+        else:
+            self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         del g, u
         self.w_down = rt.place(tensors[self.names["down"]])
 
     def forward(self, h, residual, step) -> None:
-        gu = linear(h, self.w_gate_up, out_dtype=self.rt.dtype)
-        act = ops.silu_mul(gu)
+        if self.interleaved:
+            act = ops.swiglu_interleaved(h, self.w_gate_up)
+        else:
+            gu = linear(h, self.w_gate_up, out_dtype=self.rt.dtype)
+            act = ops.silu_mul(gu)
         linear(act, self.w_down, out=residual, accumulate=True)

@@ -279,3 +279,43 @@ def test_kernels_refuse_what_they_cannot_do():
     with pytest.raises(KernelError) as e:
         ops.attn_decode_generic(q, kc, kc, one.reshape(1, 1), 0 * one, one, 1, H, KV, hd, 1.0, None, 1, torch.zeros_like(q))
     assert "272" in str(e.value)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 40, 64])
+@pytest.mark.parametrize("n,k", [(100, 72), (96, 4096), (33, 264), (6144, 512)])
+def test_gemm_skinny(m, n, k):
+    """The decode product: few rows of activations, W rows that are no multiple of the block's 32, a K that is
+    a multiple of 8 but not of 32; store, float store and accumulation."""
+    a, w = rnd(m, k, dtype=torch.bfloat16, seed=20), rnd(n, k, dtype=torch.bfloat16, seed=21)
+    assert ops.skinny_ok(a, w)
+    ref = a.double() @ w.double().T
+    terms = a.double().abs() @ w.double().abs().T
+    out = ops.gemm_skinny(a, w, ops.SKINNY_STORE_F32)
+    assert ((out.double() - ref).abs() <= 2e-6 * terms + 1e-7).all()
+    out16 = ops.gemm_skinny(a, w, ops.SKINNY_STORE_BF16)
+    assert ((out16.double() - ref).abs() <= 2 ** -8 * ref.abs() + 2e-6 * terms + 1e-7).all()
+    acc = rnd(m, n, seed=22)
+    before = acc.clone()
+    ops.gemm_skinny(a, w, ops.SKINNY_ACCUM_F32, acc)
+    assert ((acc.double() - (before.double() + ref)).abs() <= 2e-6 * (terms + before.abs().double()) + 1e-6).all()
+    # a row gives the same bits alone and inside a batch (fixed summation order, src/cuda.rs:748-766)
+    alone = ops.gemm_skinny(a[m - 1:m].contiguous(), w, ops.SKINNY_STORE_F32)
+    assert torch.equal(alone[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m", [1, 8, 13, 64])
+@pytest.mark.parametrize("f,k", [(176, 64), (24, 4096), (14336 // 8, 128)])
+def test_gemm_skinny_swiglu(m, f, k):
+    a = rnd(m, k, dtype=torch.bfloat16, seed=23)
+    g, u = rnd(f, k, dtype=torch.bfloat16, seed=24, scale=0.3), rnd(f, k, dtype=torch.bfloat16, seed=25, scale=0.3)
+    w = torch.stack([g.view(f // 8, 8, k), u.view(f // 8, 8, k)], dim=1).reshape(2 * f, k).contiguous()
+    gd, ud = a.double() @ g.double().T, a.double() @ u.double().T
+    ref = gd / (1 + torch.exp(-gd)) * ud
+    out = ops.swiglu_interleaved(a, w)
+    assert out.shape == (m, f) and out.dtype == torch.bfloat16
+    torch.testing.assert_close(out.double(), ref, rtol=1e-2, atol=1e-3 * float(ref.abs().max()))
+    # more rows than the decode kernel takes: the product, then the interleaved elementwise kernel
+    big = rnd(70, k, dtype=torch.bfloat16, seed=26)
+    gd, ud = big.double() @ g.double().T, big.double() @ u.double().T
+    torch.testing.assert_close(ops.swiglu_interleaved(big, w).double(), gd / (1 + torch.exp(-gd)) * ud, rtol=2e-2,
+                               atol=1e-2 * float((gd * ud).abs().max()))
