@@ -45,6 +45,14 @@ int gi_attn_decode_generic(void* out, long ldo, float* part_o, float* part_ml, c
                            const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
                            float scale, int window, int n_splits, void* stream);
 
+// bfloat16, head size 64 or 128: the same operation as gi_attn_decode_generic, on tensor cores
+int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, const void* kcache,
+                      const void* vcache, const int* block_table, int max_pages, const int* seq_slots,
+                      const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd, float scale, int window,
+                      int n_splits, void* stream);
+int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const float* part_ml, int n_seqs, int n_heads,
+                    int hd, int n_splits, void* stream);
+
 int gi_sample(int* out_tokens, const float* logits, long ld, int n_rows, int vocab, float temperature, int top_k,
               float top_p, unsigned long long* rng_state, const int* state_index, void* stream);
 

@@ -1,0 +1,298 @@
+// Decode attention over the paged cache on tensor cores: one token per sequence, bfloat16, head size 64 or 128.
+//
+// Same formula as the plain kernel (src/model.rs:1320-1419) and the same cut of the work as the
+// reference's attention_partial_gqa + attention_combine (src/cuda.rs:1684-1865, :2806-2839): a block takes
+// one kv head of one sequence and one slice of its context, and all query heads of the group share every
+// key and value row that is read.  Here the group's heads (up to 16) are the rows of an m16n8k16 tile:
+// scores S = Q K^T and outputs O += P V are mma.sync products with 32-bit accumulators, softmax statistics
+// and the running rescale are 32-bit.  Each of the 4 warps walks its own tiles of 32 keys; keys and values
+// arrive by cp.async into a per-warp ring of shared-memory stages (16-byte chunks, XOR-swizzled for
+// ldmatrix), so the next tiles are in flight while one is used.  Warps are merged through shared memory in
+// warp order; slices are merged by the combine kernel in slice order.
+#include <math.h>
+
+#include "api.h"
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace {
+
+constexpr int KT = 32;       // keys per tile
+constexpr int WARPS = 4;
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
+attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restrict__ part_o, float* __restrict__ part_ml,
+                      const __nv_bfloat16* __restrict__ q, long ldq, const __nv_bfloat16* __restrict__ kcache,
+                      const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_pages,
+                      const int* __restrict__ seq_slots, const int* __restrict__ seq_lens, int n_heads, int n_kv,
+                      float scale, int window, int n_splits) {
+  constexpr int CH = HD / 8;                     // 16-byte chunks per row
+  constexpr int TILE_BYTES = KT * HD * 2;        // one K or V tile
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;    // K then V
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* q_s = smem;                                       // [16][HD] bf16, swizzled
+  unsigned char* ring = smem + 16 * HD * 2;                        // [WARPS][STAGES][K tile | V tile]
+
+  const int group = n_heads / n_kv;
+  const int chunks = (group + 15) / 16;
+  const int b = blockIdx.z, kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks, sp = blockIdx.x;
+  const int g0 = chunk * 16, gcount = min(16, group - g0);
+  const int h0 = kvh * group + g0;
+  const int slot = seq_slots[b];
+  const int len = seq_lens[b];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  // queries of the group's heads as rows 0..gcount-1 of a 16-row tile (the others zero)
+  for (int idx = tid; idx < 16 * CH; idx += WARPS * 32) {
+    const int r = idx / CH, c = idx % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < gcount) v = *reinterpret_cast<const uint4*>(q + (size_t)b * ldq + (size_t)(h0 + r) * HD + c * 8);
+    *reinterpret_cast<uint4*>(q_s + gi::swz<CH>(r, c)) = v;
+  }
+  __syncthreads();
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+    // matrices: (rows 0-7, k lo), (rows 8-15, k lo), (rows 0-7, k hi), (rows 8-15, k hi) = a0..a3
+    const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = ks * 2 + (lane >> 4);
+    gi::ldmatrix_x4(qf[ks], gi::smem_u32(q_s + gi::swz<CH>(r, c)));
+  }
+
+  int t_first = 0;
+  if (window > 0) t_first = max(0, len - window);
+  const int t_base = (t_first / KT) * KT;
+  const int tiles = len > t_base ? (len - t_base + KT - 1) / KT : 0;
+  const int per = (tiles + n_splits - 1) / n_splits;
+  const int tile_lo = sp * per, tile_hi = min(tiles, tile_lo + per);
+
+  unsigned char* my_ring = ring + (size_t)warp * STAGES * STAGE_BYTES;
+  const float sl2 = scale * 1.4426950408889634f;
+
+  auto issue = [&](int tile, int stage) {
+    // 32 keys x CH chunks for K and for V, 16 bytes per lane and instruction
+    const int t0 = t_base + tile * KT;
+    const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + t0 / PAGE_TOKENS] : 0;
+    const size_t base = (((size_t)page * n_kv + kvh) * PAGE_TOKENS + (t0 % PAGE_TOKENS)) * HD;
+    unsigned char* ks = my_ring + (size_t)stage * STAGE_BYTES;
+    unsigned char* vs = ks + TILE_BYTES;
+#pragma unroll
+    for (int i = 0; i < KT * CH / 32; ++i) {
+      const int idx = i * 32 + lane;
+      const int r = idx / CH, c = idx % CH;
+      const int ok = (t0 + r < len && t0 + r >= t_first) ? 16 : 0;   // rows outside the visible span are zero-filled, not read
+      const size_t off = base + (size_t)(ok ? r : 0) * HD + c * 8;
+      gi::cp_async_16(gi::smem_u32(ks + gi::swz<CH>(r, c)), kcache + off, ok);
+      gi::cp_async_16(gi::smem_u32(vs + gi::swz<CH>(r, c)), vcache + off, ok);
+    }
+  };
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
+
+  // prologue: STAGES - 1 tiles in flight
+  int next = tile_lo + warp;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (next < tile_hi) issue(next, s);
+    gi::cp_async_commit();
+    next += WARPS;
+  }
+  int stage = 0;
+  for (int tile = tile_lo + warp; tile < tile_hi; tile += WARPS) {
+    // keep the ring full, then wait for the oldest tile
+    if (next < tile_hi) issue(next, (stage + STAGES - 1) % STAGES);
+    gi::cp_async_commit();
+    next += WARPS;
+    gi::cp_async_wait<STAGES - 1>();
+    __syncwarp();
+    const unsigned char* ks = my_ring + (size_t)stage * STAGE_BYTES;
+    const unsigned char* vs = ks + TILE_BYTES;
+    const int t0 = t_base + tile * KT;
+
+    // S = Q K^T : 4 key tiles of 8, HD/16 steps
+    float s[KT / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[nt][c] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < KT / 8; ++nt) {
+#pragma unroll
+      for (int kp = 0; kp < HD / 32; ++kp) {
+        // four 8x8 matrices: keys nt*8.., dims [kp*32, +8), [+8, +16), [+16, +24), [+24, +32)
+        uint32_t kb[4];
+        const int r = nt * 8 + (lane & 7), c = kp * 4 + (lane >> 3);
+        gi::ldmatrix_x4(kb, gi::smem_u32(ks + gi::swz<CH>(r, c)));
+        gi::mma_16816(s[nt], qf[kp * 2], kb[0], kb[1]);
+        gi::mma_16816(s[nt], qf[kp * 2 + 1], kb[2], kb[3]);
+      }
+    }
+    // mask and running softmax (rows g and g + 8)
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = t0 + nt * 8 + 2 * t + (c & 1);
+        const bool ok = key < len && key >= t_first;
+        s[nt][c] = ok ? s[nt][c] * sl2 : -INFINITY;
+        tmax[c >> 1] = fmaxf(tmax[c >> 1], s[nt][c]);
+      }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
+      tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
+      const float m_new = fmaxf(m_run[h], tmax[h]);       // finite: every tile holds at least one live key
+      alpha[h] = (m_run[h] == -INFINITY) ? 0.f : exp2f(m_run[h] - m_new);
+      m_run[h] = m_new;
+    }
+    float psum[2] = {0.f, 0.f};
+    uint32_t pf[KT / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < KT / 8; ++nt) {
+      const float p0 = exp2f(s[nt][0] - m_run[0]), p1 = exp2f(s[nt][1] - m_run[0]);
+      const float p2 = exp2f(s[nt][2] - m_run[1]), p3 = exp2f(s[nt][3] - m_run[1]);
+      psum[0] += p0 + p1;
+      psum[1] += p2 + p3;
+      pf[nt / 2][(nt & 1) * 2] = gi::pack_bf16(p0, p1);       // a0 / a2: row g
+      pf[nt / 2][(nt & 1) * 2 + 1] = gi::pack_bf16(p2, p3);   // a1 / a3: row g + 8
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 1);
+      psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 2);
+      l_run[h] = l_run[h] * alpha[h] + psum[h];
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      o[i][0] *= alpha[0];
+      o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1];
+      o[i][3] *= alpha[1];
+    }
+    // O += P V : 2 steps of 16 keys, HD/8 output tiles of 8 dims, two tiles per ldmatrix
+#pragma unroll
+    for (int kk = 0; kk < KT / 16; ++kk) {
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        // transposed 8x8 matrices: (keys kk*16.., dims dp*16..), (keys +8, same dims), (keys, dims +8), (keys +8, dims +8)
+        uint32_t vb[4];
+        const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = dp * 2 + (lane >> 4);
+        gi::ldmatrix_x4_trans(vb, gi::smem_u32(vs + gi::swz<CH>(r, c)));
+        gi::mma_16816(o[dp * 2], pf[kk], vb[0], vb[1]);
+        gi::mma_16816(o[dp * 2 + 1], pf[kk], vb[2], vb[3]);
+      }
+    }
+    __syncwarp();
+    stage = (stage + 1) % STAGES;
+  }
+  gi::cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the warps (reusing the ring): natural-log maxima so that the combine kernel can go on
+  float* Mo = reinterpret_cast<float*>(ring);            // [WARPS][16][HD]
+  float* Mm = Mo + WARPS * 16 * HD;                      // [WARPS][16]
+  float* Ml = Mm + WARPS * 16;                           // [WARPS][16]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + h * 8;
+    if (t == 0) {
+      Mm[warp * 16 + r] = m_run[h];
+      Ml[warp * 16 + r] = l_run[h];
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      Mo[(warp * 16 + r) * HD + i * 8 + 2 * t] = o[i][h * 2];
+      Mo[(warp * 16 + r) * HD + i * 8 + 2 * t + 1] = o[i][h * 2 + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < gcount * HD; idx += WARPS * 32) {
+    const int r = idx / HD, d = idx % HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, Mm[w * 16 + r]);
+    float tot = 0.f, val = 0.f;
+    if (mm != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float mw = Mm[w * 16 + r];
+        if (mw == -INFINITY) continue;
+        const float wgt = exp2f(mw - mm);
+        tot += Ml[w * 16 + r] * wgt;
+        val += Mo[(w * 16 + r) * HD + d] * wgt;
+      }
+    }
+    const int h = h0 + r;
+    if (n_splits == 1) {
+      out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(tot > 0.f ? val / tot : 0.f);
+    } else {
+      const size_t pi = ((size_t)b * n_heads + h) * n_splits + sp;
+      part_o[pi * HD + d] = val;
+      if (d == 0) {
+        part_ml[pi * 2] = mm * 0.6931471805599453f;      // back to natural-log units
+        part_ml[pi * 2 + 1] = tot;
+      }
+    }
+  }
+}
+
+template <int HD, int STAGES>
+int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, float* pml, const __nv_bfloat16* q, long ldq,
+           const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int max_pages, const int* slots, const int* lens,
+           int H, int KV, float scale, int window, int n_splits) {
+  constexpr size_t ring = (size_t)WARPS * STAGES * 2 * KT * HD * 2;
+  constexpr size_t merge = (size_t)(WARPS * 16 * HD + 2 * WARPS * 16) * sizeof(float);
+  constexpr size_t smem = 16 * HD * 2 + (ring > merge ? ring : merge);
+  auto kern = attn_decode_tc_kernel<HD, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention decode: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  kern<<<grid, WARPS * 32, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, scale, window, n_splits);
+  return gi::check_launch("attention decode (tensor cores)");
+}
+
+}  // namespace
+
+// The combine kernel lives in attention_generic.cu.
+extern "C" int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const float* part_ml, int n_seqs,
+                               int n_heads, int hd, int n_splits, void* stream);
+
+extern "C" int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq,
+                                 const void* kcache, const void* vcache, const int* block_table, int max_pages,
+                                 const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
+                                 float scale, int window, int n_splits, void* stream) {
+  if (n_seqs <= 0) return GI_OK;
+  if (hd != 64 && hd != 128) return gi::fail(GI_ERR_UNSUPPORTED, "attention decode (tensor cores): head size %d, only 64 and 128", hd);
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
+    return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
+  if (n_splits < 1) return gi::fail(GI_ERR_ARG, "attention: at least one slice");
+  if (n_splits > 1 && (!part_o || !part_ml)) return gi::fail(GI_ERR_ARG, "attention: slices need scratch memory");
+  if (ldq % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15))
+    return gi::fail(GI_ERR_UNSUPPORTED, "attention decode (tensor cores): queries and cache must be 16-byte aligned");
+  const int group = n_heads / n_kv;
+  const int chunks = (group + 15) / 16;
+  if ((long)n_kv * chunks > 65535 || n_seqs > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "attention: more than 65535 sequences or kv heads in one launch");
+  dim3 grid(n_splits, n_kv * chunks, n_seqs);
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc;
+  if (hd == 128)
+    rc = launch<128, 3>(grid, s, (__nv_bfloat16*)out, ldo, part_o, part_ml, (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kcache,
+                        (const __nv_bfloat16*)vcache, block_table, max_pages, seq_slots, seq_lens, n_heads, n_kv, scale, window, n_splits);
+  else
+    rc = launch<64, 4>(grid, s, (__nv_bfloat16*)out, ldo, part_o, part_ml, (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kcache,
+                       (const __nv_bfloat16*)vcache, block_table, max_pages, seq_slots, seq_lens, n_heads, n_kv, scale, window, n_splits);
+  if (rc != GI_OK) return rc;
+  if (n_splits > 1) return gi_attn_combine(out, ldo, GI_BF16, part_o, part_ml, n_seqs, n_heads, hd, n_splits, stream);
+  return GI_OK;
+}

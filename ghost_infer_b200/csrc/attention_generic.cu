@@ -49,9 +49,9 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
   const bool row_ok = row < rows_here;
   const int p_row = pos0 + q0 + row;               // this row's position
   const int p_last = pos0 + q0 + rows_here - 1;    // the block's last position
-  int t_begin = 0;
-  if (window > 0) t_begin = max(0, pos0 + q0 - window + 1);
-  t_begin = (t_begin / KT) * KT;
+  int t_first = 0;                                 // the first key any row of this block may see
+  if (window > 0) t_first = max(0, pos0 + q0 - window + 1);
+  const int t_begin = (t_first / KT) * KT;
 
   float m = -INFINITY, l = 0.f;
   float acc[DPT];
@@ -64,7 +64,7 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
     const size_t base = (((size_t)page * n_kv + kvh) * PAGE_TOKENS + (kt % PAGE_TOKENS)) * hd;
     for (int idx = tid; idx < KT * hd; idx += 128) {
       const int j = idx / hd, d = idx % hd;
-      const bool live = kt + j <= p_last;
+      const bool live = kt + j <= p_last && kt + j >= t_first;   // rows no query here sees are not read
       Ks[j * ldk + d] = live ? gi::ldf(kcache + base + (size_t)j * hd + d) : 0.f;
       Vs[j * ldk + d] = live ? gi::ldf(vcache + base + (size_t)j * hd + d) : 0.f;
     }
@@ -211,7 +211,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
 #pragma unroll
       for (int c = 0; c < DC; ++c) {
         const int d = lane + 32 * c;
-        v[c] = d < hd ? gi::ldf(vcache + base + (size_t)j * hd + d) : 0.f;
+        v[c] = (d < hd && t0 + j >= t_first) ? gi::ldf(vcache + base + (size_t)j * hd + d) : 0.f;
       }
 #pragma unroll
       for (int g = 0; g < GC; ++g) {
@@ -347,6 +347,14 @@ int pow2_at_least(int v) {
 }
 
 }  // namespace
+
+extern "C" int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const float* part_ml, int n_seqs,
+                               int n_heads, int hd, int n_splits, void* stream) {
+  dim3 cgrid(n_heads, n_seqs);
+  GI_DISPATCH_DTYPE(dtype, T,
+      (attn_combine_kernel<T><<<cgrid, 64, 0, (cudaStream_t)stream>>>((T*)out, ldo, part_o, part_ml, n_heads, hd, n_splits)));
+  return gi::check_launch("attention combine");
+}
 
 extern "C" int gi_attn_prefill_generic(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
                                        const void* vcache, const int* block_table, int max_pages,

@@ -38,6 +38,7 @@ def _bind():
         "gi_rope_cache_write": [P, I, L, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P],
         "gi_attn_prefill_generic": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
+        "gi_attn_decode_tc": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
     }
     for name, argtypes in sigs.items():
@@ -265,6 +266,37 @@ def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Ten
     return out
 
 
+def attn_decode_tc_ok(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:
+    """Whether the tensor-core decode attention takes these operands: bfloat16, head size 64 or 128, 16-byte rows."""
+    return (q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and head_dim in (64, 128)
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def attn_decode_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                   seq_slots: torch.Tensor, seq_lens: torch.Tensor, n_seqs: int, n_heads: int, n_kv: int,
+                   head_dim: int, scale: float, window: Optional[int], n_splits: int, out: torch.Tensor,
+                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _bind()
+    _cuda(q, "queries")
+    ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core decode attention takes bfloat16 queries, cache and output")
+    if n_splits > 1:
+        if part_o is None or part_ml is None:
+            raise KernelError("attention slices need scratch memory")
+        if part_o.dtype != torch.float32 or part_o.numel() < n_seqs * n_heads * n_splits * head_dim:
+            raise KernelError("attention scratch for outputs is too small")
+        if part_ml.dtype != torch.float32 or part_ml.numel() < n_seqs * n_heads * n_splits * 2:
+            raise KernelError("attention scratch for maxima and sums is too small")
+    _check(lib, lib.gi_attn_decode_tc(
+        out.data_ptr(), ldo, part_o.data_ptr() if part_o is not None else None,
+        part_ml.data_ptr() if part_ml is not None else None, q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(),
+        _i32(block_table, "block table"), block_table.shape[1], _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"),
+        n_seqs, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(n_splits), _stream()),
+        2 if n_splits > 1 else 1)
+    return out
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
            rng_state: Optional[torch.Tensor] = None, state_index: Optional[torch.Tensor] = None,
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -322,7 +354,8 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
         if n_splits > 1:
             part_o = torch.empty((step.n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
-        return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
-                                   step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
+        kernel = attn_decode_tc if attn_decode_tc_ok(qkv, memory.k, head_dim) else attn_decode_generic
+        return kernel(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
+                      step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
     return attn_prefill_generic(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots,
                                 step.seq_pos0, step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out)

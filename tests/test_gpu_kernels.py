@@ -179,7 +179,29 @@ def test_attention_decode(dtype, H, KV, hd, window, splits):
     torch.testing.assert_close(out.double(), ref, **tol(dtype))
 
 
-@pytest.mark.parametrize("decode", [False, True])
+@pytest.mark.parametrize("H,KV,hd", [(8, 8, 64), (32, 8, 128), (24, 8, 128), (5, 1, 64), (40, 2, 128)])
+@pytest.mark.parametrize("window,splits", [(None, 1), (None, 5), (100, 1), (100, 3)])
+def test_attention_decode_tensor_cores(H, KV, hd, window, splits):
+    """The tensor-core decode kernel: groups of 1, 3, 4, 5 and 20 heads (more than one 16-row tile), pages in
+    shuffled order, rows past each sequence's end poisoned with NaN."""
+    lens = [1, 31, 64, 65, 700, 333, 96]
+    B, S = len(lens), 704
+    k = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=13)
+    v = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=14)
+    q = rnd(B, 1, H * hd, dtype=torch.bfloat16, seed=15)
+    kc, vc, bt = paged_from_dense(k, v, lens, seed=4)
+    out = torch.full((B, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    part_o = torch.full((B * H * splits * hd,), float("nan"), device=DEV)
+    part_ml = torch.full((B * H * splits * 2,), float("nan"), device=DEV)
+    assert ops.attn_decode_tc_ok(q[:, 0], kc, hd)
+    ops.attn_decode_tc(q[:, 0], kc, vc, bt, torch.arange(B, dtype=torch.int32, device=DEV),
+                       torch.tensor(lens, dtype=torch.int32, device=DEV), B, H, KV, hd, 0.17, window, splits, out,
+                       part_o, part_ml)
+    ref = attention_ref(q, k, v, [1] * B, [n - 1 for n in lens], H, KV, hd, 0.17, window)[:, 0]
+    torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("decode", [False, True, "tc"])
 @pytest.mark.parametrize("window", [None, 50])
 def test_attention_finds_one_far_key(decode, window):
     """Random keys would hide a missed row among hundreds.  Here one key, far back (or exactly at the
@@ -196,6 +218,10 @@ def test_attention_finds_one_far_key(decode, window):
         if window:
             k[0, pos - window, kvh] = 40.0 * q[0, 0, (kvh * 2) * hd:(kvh * 2 + 1) * hd]   # just outside: must not count
             v[0, pos - window, kvh] = -500.0
+    if decode == "tc":
+        H, KV, hd = 4, 2, 64
+        k, v, q = [x.to(torch.bfloat16) for x in (torch.cat([k, k], -1), torch.cat([v, v], -1), torch.cat(
+            [q.view(1, 1, 4, 32), torch.zeros(1, 1, 4, 32, device=DEV)], -1).reshape(1, 1, 4 * 64))]
     kc, vc, bt = paged_from_dense(k, v, [n], seed=5)
     ref = attention_ref(q, k, v, [1], [pos], H, KV, hd, 1.0, window)[:, 0]
     if window:
@@ -203,8 +229,13 @@ def test_attention_finds_one_far_key(decode, window):
         assert float(ref.min()) > -1                         # the key just outside the window plays no part
     else:
         assert float(ref[0, 2 * hd]) > 90
-    out = torch.zeros((1, H * hd), device=DEV)
+    out = torch.zeros((1, H * hd), device=DEV, dtype=q.dtype)
     one = torch.ones(1, dtype=torch.int32, device=DEV)
+    if decode == "tc":
+        po, pml = torch.zeros(H * 4 * hd, device=DEV), torch.zeros(H * 4 * 2, device=DEV)
+        ops.attn_decode_tc(q[:, 0], kc, vc, bt, 0 * one, n * one, 1, H, KV, hd, 1.0, window, 4, out, po, pml)
+        torch.testing.assert_close(out.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
+        return
     if decode:
         po, pml = torch.zeros(H * 4 * hd, device=DEV), torch.zeros(H * 4 * 2, device=DEV)
         ops.attn_decode_generic(q[:, 0], kc, vc, bt, 0 * one, n * one, 1, H, KV, hd, 1.0, window, 4, out, po, pml)
