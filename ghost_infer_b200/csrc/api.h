@@ -32,6 +32,16 @@ int gi_gemm_generic(void* out, int out_dtype, int mode, const void* A, int a_dty
 int gi_gemm_skinny_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
                         long ldo, void* stream);
 
+// mode of gi_gemm_tc_bf16 (same meanings as the skinny product's)
+#define GI_TC_STORE_BF16 0
+#define GI_TC_STORE_F32 1
+#define GI_TC_ACCUM_F32 2
+#define GI_TC_SWIGLU 3
+// tcgen05 / TMA product for many rows of activations; tile_n is 128 or 256
+int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
+                    long ldo, int tile_n, void* stream);
+int gi_gemm_tc_status(int* status);
+
 int gi_rope_cache_write(void* qkv, int dtype, long ld, const int* positions, const int* slots, const int* block_table,
                         int max_pages, void* kcache, void* vcache, const float* inv_freq, int n_tokens, int n_heads,
                         int n_kv, int hd, int rot, int adjacent, int write_cache, void* stream);

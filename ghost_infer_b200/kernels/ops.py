@@ -38,6 +38,8 @@ def _bind():
         "gi_rope_cache_write": [P, I, L, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P],
         "gi_attn_prefill_generic": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
+        "gi_gemm_tc_bf16": [P, I, P, P, I, I, I, L, L, L, I, P],
+        "gi_gemm_tc_status": [P],
         "gi_attn_decode_tc": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
     }
@@ -197,6 +199,58 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
     return out
 
 
+TC_TILE_N = 256     # width of the tensor-core product's output tile (128 or 256)
+
+
+def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 product takes these operands: bfloat16, rows 16 bytes apart, 16-byte aligned."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 2
+            and a.shape[0] > 0 and a.shape[1] % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch.Tensor] = None,
+            tile_n: Optional[int] = None) -> torch.Tensor:
+    """out[M, N] (op)= a[M, K] @ w[N, K]^T on tcgen05 tensor cores with TMA-fed operands; modes as gemm_skinny's."""
+    lib = _bind()
+    _cuda(a, "activations")
+    _cuda(w, "weights")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core product takes bfloat16 operands")
+    lda, ldw = _rows(a, "activations"), _rows(w, "weights")
+    m, k = a.shape
+    n, kw = w.shape
+    if k != kw:
+        raise KernelError(f"matrix product: activations are {k} wide, the weights take {kw}")
+    cols = n // 2 if mode == SKINNY_SWIGLU else n
+    want = {SKINNY_STORE_BF16: torch.bfloat16, SKINNY_SWIGLU: torch.bfloat16}.get(mode, torch.float32)
+    if out is None:
+        if mode == SKINNY_ACCUM_F32:
+            raise KernelError("matrix product: accumulation needs an output to add to")
+        out = torch.empty((m, cols), dtype=want, device=a.device)
+    if out.shape != (m, cols) or out.dtype != want:
+        raise KernelError(f"matrix product: output is {tuple(out.shape)} {out.dtype}, wanted {(m, cols)} {want}")
+    ldo = _rows(out, "output")
+    _check(lib, lib.gi_gemm_tc_bf16(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), m, n, k, lda, ldw, ldo,
+                                    int(tile_n or TC_TILE_N), _stream()))
+    return out
+
+
+def gemm_tc_status() -> int:
+    """0 if every wait inside the tensor-core product was met since the last call; synchronises the device."""
+    lib = _bind()
+    status = ctypes.c_int(0)
+    _check(lib, lib.gi_gemm_tc_status(ctypes.byref(status)), 0)
+    return status.value
+
+
+def _tc_out_ok(out: Optional[torch.Tensor], mode: int) -> bool:
+    if out is None:
+        return True
+    align = 8 if mode in (SKINNY_STORE_BF16, SKINNY_SWIGLU) else 4
+    return out.stride(1) == 1 and out.stride(0) % align == 0 and out.data_ptr() % 16 == 0
+
+
 def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
                      block_table: Optional[torch.Tensor], kcache: Optional[torch.Tensor],
                      vcache: Optional[torch.Tensor], inv_freq: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
@@ -323,14 +377,13 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
 # Dispatchers: the one place where a kernel is chosen for an operation.
 def linear(h: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
-    if skinny_ok(h, w):
-        if accumulate:
-            return gemm_skinny(h, w, SKINNY_ACCUM_F32, out)
-        want = out.dtype if out is not None else (out_dtype or h.dtype)
-        if want == torch.bfloat16:
-            return gemm_skinny(h, w, SKINNY_STORE_BF16, out)
-        if want == torch.float32:
-            return gemm_skinny(h, w, SKINNY_STORE_F32, out)
+    want = out.dtype if out is not None else (out_dtype or h.dtype)
+    mode = SKINNY_ACCUM_F32 if accumulate else {torch.bfloat16: SKINNY_STORE_BF16, torch.float32: SKINNY_STORE_F32}.get(want)
+    if mode is not None:
+        if skinny_ok(h, w):
+            return gemm_skinny(h, w, mode, out)
+        if tc_ok(h, w) and _tc_out_ok(out, mode):
+            return gemm_tc(h, w, mode, out)
     return gemm_generic(h, w, out=out, out_dtype=out_dtype, accumulate=accumulate)
 
 
@@ -338,6 +391,8 @@ def swiglu_interleaved(h: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Te
     """silu(Wgate h) * (Wup h) where `w_interleaved` holds gate and up rows in blocks [8 gate | 8 up]."""
     if skinny_ok(h, w_interleaved):
         return gemm_skinny(h, w_interleaved, SKINNY_SWIGLU)
+    if tc_ok(h, w_interleaved) and w_interleaved.shape[0] % 16 == 0:
+        return gemm_tc(h, w_interleaved, SKINNY_SWIGLU)
     gu = linear(h, w_interleaved, out_dtype=h.dtype)
     return silu_mul(gu, interleaved=True)
 

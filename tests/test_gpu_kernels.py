@@ -350,3 +350,37 @@ def test_gemm_skinny_swiglu(m, f, k):
     gd, ud = big.double() @ g.double().T, big.double() @ u.double().T
     torch.testing.assert_close(ops.swiglu_interleaved(big, w).double(), gd / (1 + torch.exp(-gd)) * ud, rtol=2e-2,
                                atol=1e-2 * float((gd * ud).abs().max()))
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (130, 96, 72), (65, 264, 200), (700, 512, 4096), (2048, 1000, 512)])
+def test_gemm_tensor_cores(tile_n, m, n, k):
+    """The tcgen05 / TMA product: whole tiles, and rows, columns and K that stop inside a tile (zero-filled by
+    TMA, masked at the store); store in both precisions and accumulation into a float matrix."""
+    a, w = rnd(m, k, dtype=torch.bfloat16, seed=30), rnd(n, k, dtype=torch.bfloat16, seed=31)
+    assert ops.tc_ok(a, w)
+    ref = a.double() @ w.double().T
+    terms = a.double().abs() @ w.double().abs().T
+    out = ops.gemm_tc(a, w, ops.SKINNY_STORE_F32, tile_n=tile_n)
+    assert ops.gemm_tc_status() == 0
+    assert ((out.double() - ref).abs() <= 2e-6 * terms + 1e-7).all(), float((out.double() - ref).abs().max())
+    out16 = ops.gemm_tc(a, w, ops.SKINNY_STORE_BF16, tile_n=tile_n)
+    assert ((out16.double() - ref).abs() <= 2 ** -8 * ref.abs() + 2e-6 * terms + 1e-7).all()
+    acc = rnd(m, n, seed=32)
+    before = acc.clone()
+    ops.gemm_tc(a, w, ops.SKINNY_ACCUM_F32, acc, tile_n=tile_n)
+    assert ((acc.double() - (before.double() + ref)).abs() <= 2e-6 * (terms + before.abs().double()) + 1e-6).all()
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("m,f,k", [(200, 176, 64), (129, 1000, 520)])
+def test_gemm_tensor_cores_swiglu(tile_n, m, f, k):
+    a = rnd(m, k, dtype=torch.bfloat16, seed=33)
+    g, u = rnd(f, k, dtype=torch.bfloat16, seed=34, scale=0.3), rnd(f, k, dtype=torch.bfloat16, seed=35, scale=0.3)
+    w = torch.stack([g.view(f // 8, 8, k), u.view(f // 8, 8, k)], dim=1).reshape(2 * f, k).contiguous()
+    gd, ud = a.double() @ g.double().T, a.double() @ u.double().T
+    ref = gd / (1 + torch.exp(-gd)) * ud
+    out = ops.gemm_tc(a, w, ops.SKINNY_SWIGLU, tile_n=tile_n)
+    assert ops.gemm_tc_status() == 0
+    torch.testing.assert_close(out.double(), ref, rtol=1e-2, atol=1e-3 * float(ref.abs().max()))
