@@ -55,6 +55,11 @@ int gi_attn_decode_generic(void* out, long ldo, float* part_o, float* part_ml, c
                            const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
                            float scale, int window, int n_splits, void* stream);
 
+// bfloat16, head size 64 or 128: the same operation as gi_attn_prefill_generic, on tensor cores
+int gi_attn_prefill_tc(void* out, long ldo, const void* q, long ldq, const void* kcache, const void* vcache,
+                       const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots,
+                       const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd, float scale,
+                       int window, void* stream);
 // bfloat16, head size 64 or 128: the same operation as gi_attn_decode_generic, on tensor cores
 int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, const void* kcache,
                       const void* vcache, const int* block_table, int max_pages, const int* seq_slots,

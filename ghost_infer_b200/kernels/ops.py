@@ -40,6 +40,7 @@ def _bind():
         "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_gemm_tc_bf16": [P, I, P, P, I, I, I, L, L, L, I, P],
         "gi_gemm_tc_status": [P],
+        "gi_attn_prefill_tc": [P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_decode_tc": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
     }
@@ -244,10 +245,11 @@ def gemm_tc_status() -> int:
     return status.value
 
 
-def _tc_out_ok(out: Optional[torch.Tensor], mode: int) -> bool:
-    if out is None:
-        return True
+def _tc_out_ok(out: Optional[torch.Tensor], mode: int, cols: int) -> bool:
+    """The tensor-core product stores 16 bytes at a time: output rows must start on 16-byte boundaries."""
     align = 8 if mode in (SKINNY_STORE_BF16, SKINNY_SWIGLU) else 4
+    if out is None:
+        return cols % align == 0
     return out.stride(1) == 1 and out.stride(0) % align == 0 and out.data_ptr() % 16 == 0
 
 
@@ -320,6 +322,24 @@ def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Ten
     return out
 
 
+def attn_prefill_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                    cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
+                    max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                    window: Optional[int], out: torch.Tensor) -> torch.Tensor:
+    """As attn_prefill_generic, for bfloat16 and head size 64 or 128, on tensor cores."""
+    lib = _bind()
+    _cuda(q, "queries")
+    ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core prefill attention takes bfloat16 queries, cache and output")
+    _check(lib, lib.gi_attn_prefill_tc(
+        out.data_ptr(), ldo, q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(),
+        _i32(block_table, "block table"), block_table.shape[1], _i32(cu_seqlens, "cu_seqlens"),
+        _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"), n_seqs, max_q_len, n_heads, n_kv, head_dim,
+        float(scale), int(window or 0), _stream()))
+    return out
+
+
 def attn_decode_tc_ok(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:
     """Whether the tensor-core decode attention takes these operands: bfloat16, head size 64 or 128, 16-byte rows."""
     return (q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and head_dim in (64, 128)
@@ -382,7 +402,7 @@ def linear(h: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = No
     if mode is not None:
         if skinny_ok(h, w):
             return gemm_skinny(h, w, mode, out)
-        if tc_ok(h, w) and _tc_out_ok(out, mode):
+        if tc_ok(h, w) and _tc_out_ok(out, mode, w.shape[0]):
             return gemm_tc(h, w, mode, out)
     return gemm_generic(h, w, out=out, out_dtype=out_dtype, accumulate=accumulate)
 
@@ -412,5 +432,6 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
         kernel = attn_decode_tc if attn_decode_tc_ok(qkv, memory.k, head_dim) else attn_decode_generic
         return kernel(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
                       step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
-    return attn_prefill_generic(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots,
-                                step.seq_pos0, step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out)
+    kernel = attn_prefill_tc if attn_decode_tc_ok(qkv, memory.k, head_dim) and out.stride(0) % 2 == 0 else attn_prefill_generic
+    return kernel(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots,
+                  step.seq_pos0, step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out)

@@ -159,6 +159,29 @@ def test_attention_prefill(dtype, H, KV, hd, window):
     torch.testing.assert_close(out.double(), ref, **tol(dtype))
 
 
+@pytest.mark.parametrize("H,KV,hd", [(8, 8, 64), (6, 2, 128), (3, 1, 64), (32, 8, 128)])
+@pytest.mark.parametrize("window", [None, 37, 100])
+def test_attention_prefill_tensor_cores(H, KV, hd, window):
+    """The tensor-core prefill kernel: ragged lengths around its 64-row and 64-key tiles, a sequence that goes on
+    after 70 and one after 200 cached positions, pages in shuffled order, unowned rows poisoned with NaN."""
+    lens_q, pos0 = [1, 45, 64, 65, 200, 33, 130], [0, 0, 0, 0, 0, 70, 200]
+    B, S = len(lens_q), 384
+    k = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=10)
+    v = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=11)
+    q = rnd(B, max(lens_q), H * hd, dtype=torch.bfloat16, seed=12)
+    lens_kv = [p + n for p, n in zip(pos0, lens_q)]
+    kc, vc, bt = paged_from_dense(k, v, lens_kv, seed=3)
+    flat = torch.cat([q[b, :lens_q[b]] for b in range(B)])
+    cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    out = torch.full_like(flat, float("nan"))
+    ops.attn_prefill_tc(flat, kc, vc, bt, cu, slots, torch.tensor(pos0, dtype=torch.int32, device=DEV), B,
+                        max(lens_q), H, KV, hd, 0.21, window, out)
+    ref = attention_ref(q, k, v, lens_q, pos0, H, KV, hd, 0.21, window)
+    ref = torch.cat([ref[b, :lens_q[b]] for b in range(B)])
+    torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,KV,hd", [(4, 2, 16), (5, 1, 48), (8, 8, 64), (32, 8, 128), (2, 1, 256), (24, 2, 80)])
 @pytest.mark.parametrize("window,splits", [(None, 1), (None, 5), (100, 1), (100, 3)])
@@ -235,6 +258,10 @@ def test_attention_finds_one_far_key(decode, window):
         po, pml = torch.zeros(H * 4 * hd, device=DEV), torch.zeros(H * 4 * 2, device=DEV)
         ops.attn_decode_tc(q[:, 0], kc, vc, bt, 0 * one, n * one, 1, H, KV, hd, 1.0, window, 4, out, po, pml)
         torch.testing.assert_close(out.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
+        out2 = torch.zeros_like(out)      # and the prefill kernel: the last position as a one-token chunk
+        ops.attn_prefill_tc(q[:, 0], kc, vc, bt, torch.tensor([0, 1], dtype=torch.int32, device=DEV), 0 * one,
+                            pos * one, 1, 1, H, KV, hd, 1.0, window, out2)
+        torch.testing.assert_close(out2.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
         return
     if decode:
         po, pml = torch.zeros(H * 4 * hd, device=DEV), torch.zeros(H * 4 * 2, device=DEV)
