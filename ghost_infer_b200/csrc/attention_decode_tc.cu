@@ -11,6 +11,8 @@
 // warp order; slices are merged by the combine kernel in slice order.
 #include <math.h>
 
+#include <mutex>
+
 #include "api.h"
 #include "common.cuh"
 #include "mma_utils.cuh"
@@ -295,4 +297,59 @@ extern "C" int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part
   if (rc != GI_OK) return rc;
   if (n_splits > 1) return gi_attn_combine(out, ldo, GI_BF16, part_o, part_ml, n_seqs, n_heads, hd, n_splits, stream);
   return GI_OK;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// The variant that brings its own scratch (see attention_decode_noalloc.h for who needs it and its rules).
+#include "attention_decode_noalloc.h"
+
+namespace {
+
+// Partial outputs first, then (maximum, sum) pairs.  In host code this name is only a handle for
+// cudaGetSymbolAddress: it is not a device address and must never be handed to a kernel as one.
+static __device__ __align__(256) float g_noalloc_scratch[GI_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_noalloc_ptr[MAX_DEVICES] = {nullptr};
+std::mutex g_noalloc_lock;
+
+// The array's address on the current device, looked up once per device.
+int noalloc_scratch(float** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention decode (no allocation): %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= MAX_DEVICES) return gi::fail(GI_ERR_UNSUPPORTED, "attention decode (no allocation): device %d, at most %d", dev, MAX_DEVICES);
+  std::lock_guard<std::mutex> guard(g_noalloc_lock);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return gi::fail(GI_ERR_CUDA, "attention decode (no allocation): the scratch array's address is not to be had: %s", cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = p;
+  }
+  *ptr = g_noalloc_ptr[dev];
+  return GI_OK;
+}
+
+}  // namespace
+
+extern "C" int gi_attn_decode_tc_noalloc(void* out, long ldo, const void* q, long ldq, const void* kcache,
+                                         const void* vcache, const int* block_table, int max_pages,
+                                         const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv,
+                                         int hd, float scale, int window, int n_splits, void* stream) {
+  if (n_seqs <= 0) return GI_OK;
+  if (n_splits < 1 || n_heads <= 0 || hd <= 0) return gi::fail(GI_ERR_ARG, "attention decode (no allocation): bad sizes");
+  const long long need = (long long)n_seqs * n_heads * n_splits * (hd + 2);
+  if (need > GI_NOALLOC_SCRATCH_FLOATS)
+    return gi::fail(GI_ERR_UNSUPPORTED,
+                    "attention decode (no allocation): %d sequences x %d heads x %d slices x (%d + 2) floats = %lld, the built-in "
+                    "scratch holds %d; use fewer slices or the entry point that takes scratch",
+                    n_seqs, n_heads, n_splits, hd, need, GI_NOALLOC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != GI_OK) return rc;
+  float* part_o = scratch;
+  float* part_ml = scratch + (size_t)n_seqs * n_heads * n_splits * hd;
+  return gi_attn_decode_tc(out, ldo, part_o, part_ml, q, ldq, kcache, vcache, block_table, max_pages, seq_slots, seq_lens,
+                           n_seqs, n_heads, n_kv, hd, scale, window, n_splits, stream);
 }
