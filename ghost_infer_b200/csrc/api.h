@@ -42,8 +42,10 @@ int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W, int M, in
                     long ldo, int tile_n, void* stream);
 int gi_gemm_tc_status(int* status);
 
-int gi_rope_cache_write(void* qkv, int dtype, long ld, const int* positions, const int* slots, const int* block_table,
-                        int max_pages, void* kcache, void* vcache, const float* inv_freq, int n_tokens, int n_heads,
+// table[t, i] = (cos, sin)(positions[t] * inv_freq[i]), float2 [n_tokens, rot / 2]
+int gi_rope_table(float* table, const int* positions, const float* inv_freq, int n_tokens, int rot, void* stream);
+int gi_rope_cache_write(void* qkv, int dtype, long ld, const float* table, const int* positions, const int* slots,
+                        const int* block_table, int max_pages, void* kcache, void* vcache, int n_tokens, int n_heads,
                         int n_kv, int hd, int rot, int adjacent, int write_cache, void* stream);
 
 int gi_attn_prefill_generic(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,

@@ -19,12 +19,42 @@ __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ tab
 
 // y = x * (1 / sqrt(mean(x^2) + eps)) * w, one block per row (src/model.rs:919-928, src/cuda.rs:505-515).
 // `rows` (optional) picks which rows of x are normed; output row r is then x[rows[r]].
-template <typename TO, typename TW>
+// The row is read once, four floats at a time, and kept in registers (up to VEC float4 per thread);
+// wider rows, or rows that are no multiple of 4, take the plain loop.
+template <typename TO, typename TW, int VEC>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
                                const int* __restrict__ rows, int d, float eps) {
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
+  TO* o = out + (size_t)r * d;
+  if (VEC > 0) {
+    const int n4 = d / 4;
+    float4 v[VEC > 0 ? VEC : 1];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      v[j] = i < n4 ? reinterpret_cast<const float4*>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      ss = fmaf(v[j].x, v[j].x, ss);
+      ss = fmaf(v[j].y, v[j].y, ss);
+      ss = fmaf(v[j].z, v[j].z, ss);
+      ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = gi::block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < n4) {
+        gi::stf(o + 4 * i, v[j].x * scale * gi::ldf(w + 4 * i));
+        gi::stf(o + 4 * i + 1, v[j].y * scale * gi::ldf(w + 4 * i + 1));
+        gi::stf(o + 4 * i + 2, v[j].z * scale * gi::ldf(w + 4 * i + 2));
+        gi::stf(o + 4 * i + 3, v[j].w * scale * gi::ldf(w + 4 * i + 3));
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     const float v = xr[i];
@@ -32,12 +62,9 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
   }
   ss = gi::block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / (float)d + eps);
-  TO* o = out + (size_t)r * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) gi::stf(o + i, xr[i] * scale * gi::ldf(w + i));
 }
 
-// h = silu(gate) * up from packed rows [gate | up] (src/cuda.rs:3573-3579; silu(g) = g / (1 + exp(-g)),
-// src/quant.rs:1135-1154).
 // `interleaved`: the row holds blocks of 16 values [gate j..j+7 | up j..j+7] instead of [all gates | all ups].
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int f, size_t total, int interleaved) {
@@ -67,8 +94,16 @@ extern "C" int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* 
   if (n_rows <= 0) return GI_OK;
   if (d <= 0) return gi::fail(GI_ERR_ARG, "rmsnorm: bad width %d", d);
   const int threads = d >= 2048 ? 512 : 256;
-  GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW,
-      (rmsnorm_kernel<TO, TW><<<n_rows, threads, 0, (cudaStream_t)stream>>>((TO*)out, x, (const TW*)w, rows, d, eps))));
+  // the register path: rows that are a multiple of 4 wide, start on 16-byte boundaries, and fit 4 float4 per thread
+  const bool vec = d % 4 == 0 && ((uintptr_t)x & 15) == 0 && d / 4 <= 4 * threads;
+  const int per = vec ? (d / 4 + threads - 1) / threads : 0;
+  GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW, {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (per == 1) rmsnorm_kernel<TO, TW, 1><<<n_rows, threads, 0, s>>>((TO*)out, x, (const TW*)w, rows, d, eps);
+    else if (per == 2) rmsnorm_kernel<TO, TW, 2><<<n_rows, threads, 0, s>>>((TO*)out, x, (const TW*)w, rows, d, eps);
+    else if (per == 3 || per == 4) rmsnorm_kernel<TO, TW, 4><<<n_rows, threads, 0, s>>>((TO*)out, x, (const TW*)w, rows, d, eps);
+    else rmsnorm_kernel<TO, TW, 0><<<n_rows, threads, 0, s>>>((TO*)out, x, (const TW*)w, rows, d, eps);
+  }));
   return gi::check_launch("rmsnorm");
 }
 

@@ -144,11 +144,37 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, 
   // ---- highest logit, first index on ties
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = tid; i < n; i += blockDim.x) {
-    const float v = row[i];
-    if (v > bv) {  // strictly greater keeps the first; NaN never enters
-      bv = v;
-      bi = i;
+  if ((((uintptr_t)row) & 15) == 0) {
+    // four logits per load, four loads in flight: a thread's candidates still come in increasing index order
+    const int n4 = n / 4;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    for (int i0 = tid; i0 < n4; i0 += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        v[u] = i < n4 ? row4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int base = 4 * (i0 + u * blockDim.x);
+        if (v[u].x > bv) { bv = v[u].x; bi = base; }
+        if (v[u].y > bv) { bv = v[u].y; bi = base + 1; }
+        if (v[u].z > bv) { bv = v[u].z; bi = base + 2; }
+        if (v[u].w > bv) { bv = v[u].w; bi = base + 3; }
+      }
+    }
+    for (int i = 4 * n4 + tid; i < n; i += blockDim.x) {
+      const float v = row[i];
+      if (v > bv) { bv = v; bi = i; }
+    }
+  } else {
+    for (int i = tid; i < n; i += blockDim.x) {
+      const float v = row[i];
+      if (v > bv) {  // strictly greater keeps the first; NaN never enters
+        bv = v;
+        bi = i;
+      }
     }
   }
 #pragma unroll

@@ -129,6 +129,8 @@ class DecodeRunner:
         g.host_event = ev
         self.engine.bytes_h2d = g.host.numel() * 4
         g.ctx.max_kv_len = max(lens) + 1
+        if g.graph is None:
+            g.ctx.shared.clear()                       # per-step tables are made anew (inside the graph once captured)
         if not self.use_graph:
             l0 = ops.launches
             g.logits = self.engine.forward(g.ctx)

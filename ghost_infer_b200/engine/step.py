@@ -45,6 +45,7 @@ class StepContext:
         self.logit_rows: Optional[torch.Tensor] = None   # int32 [R] flat token indices
         self.empty_f32: torch.Tensor = None
         self.fixed_splits: Optional[int] = None
+        self.shared: dict = {}                  # what parts compute once per step and share (e.g. rotary angles)
         self.sm_count = 148
         # the same facts on the host, for parts that plan their work there
         self.host_q_lens: List[int] = []

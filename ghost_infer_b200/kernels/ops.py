@@ -35,7 +35,8 @@ def _bind():
         "gi_silu_mul": [P, P, I, I, I, I, P],
         "gi_gemm_skinny_bf16": [P, I, P, P, I, I, I, L, L, L, P],
         "gi_gemm_generic": [P, I, I, P, I, P, I, I, I, I, L, L, L, P],
-        "gi_rope_cache_write": [P, I, L, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P],
+        "gi_rope_table": [P, P, P, I, I, P],
+        "gi_rope_cache_write": [P, I, L, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P],
         "gi_attn_prefill_generic": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_gemm_tc_bf16": [P, I, P, P, I, I, I, L, L, L, I, P],
@@ -253,18 +254,33 @@ def _tc_out_ok(out: Optional[torch.Tensor], mode: int, cols: int) -> bool:
     return out.stride(1) == 1 and out.stride(0) % align == 0 and out.data_ptr() % 16 == 0
 
 
-def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """float32 [tokens, pairs, 2]: (cos, sin) of position * frequency, angles formed in 32-bit."""
+    lib = _bind()
+    _cuda(positions, "positions")
+    if inv_freq.dtype != torch.float32 or not inv_freq.is_contiguous():
+        raise KernelError("the rotary frequency table must be contiguous float32")
+    n, half = positions.numel(), inv_freq.numel()
+    table = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
+    _check(lib, lib.gi_rope_table(table.data_ptr(), _i32(positions, "positions"), inv_freq.data_ptr(), n, 2 * half, _stream()))
+    return table
+
+
+def rope_cache_write(qkv: torch.Tensor, table: Optional[torch.Tensor], positions: torch.Tensor, slots: torch.Tensor,
                      block_table: Optional[torch.Tensor], kcache: Optional[torch.Tensor],
-                     vcache: Optional[torch.Tensor], inv_freq: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                     vcache: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int,
                      rotary_dim: int, adjacent: bool, write_cache: bool) -> None:
+    """Rotates the q and k parts of the packed rows by the angles of `table` (q in place, k into the cache)
+    and copies v into the cache."""
     lib = _bind()
     _cuda(qkv, "q/k/v rows")
     ld = _rows(qkv, "q/k/v rows")
     n = qkv.shape[0]
     if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
         raise KernelError(f"q/k/v rows are {qkv.shape[1]} wide, wanted {(n_heads + 2 * n_kv) * head_dim}")
-    if inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2:
-        raise KernelError("the rotary frequency table must hold rotary_dim / 2 float32 values")
+    if rotary_dim:
+        if table is None or table.dtype != torch.float32 or table.numel() != n * (rotary_dim // 2) * 2:
+            raise KernelError("the table of angles must hold tokens x rotary_dim / 2 float32 (cos, sin) pairs")
     if write_cache:
         if kcache is None or vcache is None or block_table is None:
             raise KernelError("cache write without a cache")
@@ -274,10 +290,10 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Te
             raise KernelError(f"cache pages must be contiguous [pages, {n_kv}, 64, {head_dim}], got {tuple(kcache.shape)}")
     max_pages = block_table.shape[1] if block_table is not None else 0
     _check(lib, lib.gi_rope_cache_write(
-        qkv.data_ptr(), _dt(qkv, "q/k/v rows"), ld, _i32(positions, "positions"), _i32(slots, "slots"),
-        _i32(block_table, "block table"), max_pages,
+        qkv.data_ptr(), _dt(qkv, "q/k/v rows"), ld, table.data_ptr() if table is not None else None,
+        _i32(positions, "positions"), _i32(slots, "slots"), _i32(block_table, "block table"), max_pages,
         kcache.data_ptr() if kcache is not None else None, vcache.data_ptr() if vcache is not None else None,
-        inv_freq.data_ptr(), n, n_heads, n_kv, head_dim, rotary_dim, int(adjacent), int(write_cache), _stream()))
+        n, n_heads, n_kv, head_dim, rotary_dim, int(adjacent), int(write_cache), _stream()))
 
 
 def attn_prefill_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,

@@ -63,8 +63,8 @@ class GqaAttention(Mixer):
         if self.position is not None:
             self.position.encode_and_store(qkv, step, memory, self.n_heads, self.n_kv, self.head_dim)
         else:
-            ops.rope_cache_write(qkv, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
-                                 step.empty_f32, self.n_heads, self.n_kv, self.head_dim, 0, False,
+            ops.rope_cache_write(qkv, None, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
+                                 self.n_heads, self.n_kv, self.head_dim, 0, False,
                                  memory.writes and memory.k is not None)
         att = torch.empty((h.shape[0], self.q_dim), dtype=self.rt.dtype, device=h.device)
         ops.attention(qkv, memory, step, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, att)

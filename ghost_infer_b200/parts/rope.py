@@ -63,8 +63,16 @@ class Rotary(PositionEncoding):
     def bind(self, tensors, rt) -> None:
         super().bind(tensors, rt)
         self.inv_freq = self.inv_freq_host.to(rt.device)
+        sc = self.scaling
+        self.table_key = ("rotary", self.rotary_dim, self.theta, repr(sorted(sc.items())) if sc else None)
 
     def encode_and_store(self, qkv, step, memory, n_heads, n_kv_heads, head_dim) -> None:
-        ops.rope_cache_write(qkv, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
-                             self.inv_freq, n_heads, n_kv_heads, head_dim, self.rotary_dim,
+        # the angles depend on the step's positions and this encoding's constants only: one table per step
+        # serves every layer that rotates the same way
+        table = step.shared.get(self.table_key)
+        if table is None:
+            table = ops.rope_table(step.positions, self.inv_freq)
+            step.shared[self.table_key] = table
+        ops.rope_cache_write(qkv, table, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
+                             n_heads, n_kv_heads, head_dim, self.rotary_dim,
                              self.pairing == "adjacent", memory.writes and memory.k is not None)

@@ -94,7 +94,9 @@ def test_rope_and_cache_write(dtype, hd, rot, adjacent):
     kc = torch.zeros(7, KV, 64, hd, dtype=dtype, device=DEV)
     vc = torch.zeros_like(kc)
     inv = torch.from_numpy(pl.rotary_inv_freq(rot, 10000.0, None)).to(DEV)
-    ops.rope_cache_write(qkv, positions, slots, bt, kc, vc, inv, H, KV, hd, rot, adjacent, True)
+    table = ops.rope_table(positions, inv)
+    assert table.shape == (T, rot // 2, 2)
+    ops.rope_cache_write(qkv, table, positions, slots, bt, kc, vc, H, KV, hd, rot, adjacent, True)
     pairing = "adjacent" if adjacent else "half"
     o = orig.double().cpu().numpy()
     pos = positions.cpu().numpy()
