@@ -88,6 +88,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (recorded in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--tune", default="", help="overrides of kernel choices, e.g. small_skinny=0,attn_waves=2")
+    ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another (no programmatic dependent launch)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -106,6 +108,10 @@ def main():
     from ghost_infer_b200.kernels import ops
 
     dev = "cuda:0"
+    ops.set_pdl(not args.no_pdl)
+    for kv in filter(None, args.tune.split(",")):
+        k, v = kv.split("=")
+        ops.TUNE[k] = type(ops.TUNE[k])(float(v))
     cfg = dict(CONFIG_8B)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:

@@ -14,6 +14,9 @@ extern "C" {
 
 const char* gi_last_error(void);
 int gi_abi_version(void);
+// Programmatic dependent launch: kernels of a stream may begin while their predecessor drains (off by default).
+void gi_set_pdl(int on);
+int gi_get_pdl(void);
 
 int gi_embed(float* out, const void* table, int table_dtype, const int* tokens, int n_tokens, int d, int vocab,
              void* stream);
@@ -31,6 +34,14 @@ int gi_gemm_generic(void* out, int out_dtype, int mode, const void* A, int a_dty
 #define GI_SKINNY_SWIGLU 3      // W rows interleaved [8 gate | 8 up]; out[M, N/2] bfloat16 = silu(gate) * up
 int gi_gemm_skinny_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
                         long ldo, void* stream);
+
+// Persistent stream-K tcgen05 product for at most 64 rows of activations (modes as gi_gemm_skinny_bf16).
+// `scratch`: gi_gemm_stream_scratch_floats() floats; `counters`: one int per 128 rows of W, zero at first use.
+// use_pdl: launch with programmatic stream serialization (weights are prefetched before the dependency wait).
+long gi_gemm_stream_scratch_floats(void);
+int gi_gemm_stream_bf16(void* out, int mode, const void* A, const void* W, float* scratch, int* counters, int n_counters,
+                        int M, int N, int K, long lda, long ldw, long ldo, int use_pdl, void* stream);
+int gi_gemm_stream_status(int* status);
 
 // mode of gi_gemm_tc_bf16 (same meanings as the skinny product's)
 #define GI_TC_STORE_BF16 0

@@ -35,6 +35,7 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem;                                       // [16][HD] bf16, swizzled
   unsigned char* ring = smem + 16 * HD * 2;                        // [WARPS][STAGES][K tile | V tile]
+  gi::pdl_prologue();
 
   const int group = n_heads / n_kv;
   const int chunks = (group + 15) / 16;
@@ -260,8 +261,8 @@ int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, f
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention decode: %s", cudaGetErrorString(e));
     configured = true;
   }
-  kern<<<grid, WARPS * 32, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, scale, window, n_splits);
-  return gi::check_launch("attention decode (tensor cores)");
+  return gi::check(gi::launch(kern, grid, dim3(WARPS * 32), smem, s, out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV,
+                              scale, window, n_splits), "attention decode (tensor cores)");
 }
 
 }  // namespace

@@ -268,6 +268,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
 template <typename T>
 __global__ void attn_combine_kernel(T* __restrict__ out, long ldo, const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, int n_heads, int hd, int n_splits) {
+  gi::pdl_prologue();
   const int b = blockIdx.y, h = blockIdx.x;
   const size_t p0 = ((size_t)b * n_heads + h) * n_splits;
   float mm = -INFINITY;
@@ -351,9 +352,10 @@ int pow2_at_least(int v) {
 extern "C" int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const float* part_ml, int n_seqs,
                                int n_heads, int hd, int n_splits, void* stream) {
   dim3 cgrid(n_heads, n_seqs);
+  cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T,
-      (attn_combine_kernel<T><<<cgrid, 64, 0, (cudaStream_t)stream>>>((T*)out, ldo, part_o, part_ml, n_heads, hd, n_splits)));
-  return gi::check_launch("attention combine");
+      e = gi::launch(attn_combine_kernel<T>, cgrid, dim3(64), 0, (cudaStream_t)stream, (T*)out, ldo, part_o, part_ml, n_heads, hd, n_splits));
+  return gi::check(e, "attention combine");
 }
 
 extern "C" int gi_attn_prefill_generic(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,

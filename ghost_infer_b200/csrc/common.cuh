@@ -19,8 +19,17 @@
 
 namespace gi {
 
+bool pdl_enabled();                                // programmatic dependent launch switched on (gi_set_pdl)
 int fail(int code, const char* fmt, ...);          // records the message for gi_last_error(), returns code
 int check_launch(const char* what);                // cudaGetLastError() -> GI_OK or a recorded failure
+
+// First statements of a kernel that may be launched with programmatic stream serialization: let the next
+// kernel in the stream begin its own set-up, then wait until everything before this kernel has completed and
+// is visible.  Both are no-ops for a plain launch.  Nothing a predecessor writes may be touched before this.
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 __device__ __forceinline__ float ldf(const float* p) { return *p; }
 __device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
@@ -59,6 +68,29 @@ template <typename T> struct DType;
 template <> struct DType<float> { static constexpr int code = GI_F32; };
 template <> struct DType<__nv_bfloat16> { static constexpr int code = GI_BF16; };
 
+}  // namespace gi
+
+namespace gi {
+// Launches `kern` on `s`; with programmatic dependent launch switched on, the kernel may start while its
+// predecessor in the stream is still running (it must begin with pdl_prologue()).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+inline int check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) return fail(GI_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return check_launch(what);
+}
 }  // namespace gi
 
 // Calls `body` with `T` bound to the element type named by a dtype code.

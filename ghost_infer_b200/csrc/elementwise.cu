@@ -9,6 +9,7 @@ namespace {
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table, const int* __restrict__ tokens,
                              int d, int vocab) {
+  gi::pdl_prologue();
   const int t = blockIdx.x;
   int id = tokens[t];
   if (id < 0 || id >= vocab) id = 0;  // the host validates ids; padding rows may carry anything
@@ -25,6 +26,7 @@ template <typename TO, typename TW, int VEC>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
                                const int* __restrict__ rows, int d, float eps) {
   __shared__ float scratch[33];
+  gi::pdl_prologue();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
   TO* o = out + (size_t)r * d;
@@ -84,9 +86,10 @@ extern "C" int gi_embed(float* out, const void* table, int table_dtype, const in
                         int vocab, void* stream) {
   if (n_tokens <= 0) return GI_OK;
   if (d <= 0 || vocab <= 0) return gi::fail(GI_ERR_ARG, "embed: bad sizes d=%d vocab=%d", d, vocab);
+  cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(table_dtype, TW,
-                    embed_kernel<TW><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(out, (const TW*)table, tokens, d, vocab));
-  return gi::check_launch("embed");
+                    e = gi::launch(embed_kernel<TW>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, out, (const TW*)table, tokens, d, vocab));
+  return gi::check(e, "embed");
 }
 
 extern "C" int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows,
@@ -97,14 +100,16 @@ extern "C" int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* 
   // the register path: rows that are a multiple of 4 wide, start on 16-byte boundaries, and fit 4 float4 per thread
   const bool vec = d % 4 == 0 && ((uintptr_t)x & 15) == 0 && d / 4 <= 4 * threads;
   const int per = vec ? (d / 4 + threads - 1) / threads : 0;
+  cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW, {
     cudaStream_t s = (cudaStream_t)stream;
-    if (per == 1) rmsnorm_kernel<TO, TW, 1><<<n_rows, threads, 0, s>>>((TO*)out, x, (const TW*)w, rows, d, eps);
-    else if (per == 2) rmsnorm_kernel<TO, TW, 2><<<n_rows, threads, 0, s>>>((TO*)out, x, (const TW*)w, rows, d, eps);
-    else if (per == 3 || per == 4) rmsnorm_kernel<TO, TW, 4><<<n_rows, threads, 0, s>>>((TO*)out, x, (const TW*)w, rows, d, eps);
-    else rmsnorm_kernel<TO, TW, 0><<<n_rows, threads, 0, s>>>((TO*)out, x, (const TW*)w, rows, d, eps);
+    const dim3 g(n_rows), b(threads);
+    if (per == 1) e = gi::launch(rmsnorm_kernel<TO, TW, 1>, g, b, 0, s, (TO*)out, x, (const TW*)w, rows, d, eps);
+    else if (per == 2) e = gi::launch(rmsnorm_kernel<TO, TW, 2>, g, b, 0, s, (TO*)out, x, (const TW*)w, rows, d, eps);
+    else if (per == 3 || per == 4) e = gi::launch(rmsnorm_kernel<TO, TW, 4>, g, b, 0, s, (TO*)out, x, (const TW*)w, rows, d, eps);
+    else e = gi::launch(rmsnorm_kernel<TO, TW, 0>, g, b, 0, s, (TO*)out, x, (const TW*)w, rows, d, eps);
   }));
-  return gi::check_launch("rmsnorm");
+  return gi::check(e, "rmsnorm");
 }
 
 extern "C" int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, int interleaved, void* stream) {

@@ -8,9 +8,11 @@
 
 namespace {
 thread_local char g_last_error[512] = "";
+int g_pdl = 0;
 }
 
 namespace gi {
+bool pdl_enabled() { return g_pdl != 0; }
 int fail(int code, const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
@@ -27,3 +29,7 @@ int check_launch(const char* what) {
 
 extern "C" const char* gi_last_error(void) { return g_last_error; }
 extern "C" int gi_abi_version(void) { return GI_ABI_VERSION; }
+
+// Switches programmatic dependent launch on or off for the kernels that support it (process-wide).
+extern "C" void gi_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+extern "C" int gi_get_pdl(void) { return g_pdl; }

@@ -44,6 +44,7 @@ skinny_kernel(void* __restrict__ out_, const __nv_bfloat16* __restrict__ A, cons
               int K, long lda, long ldw, long ldo) {
   constexpr int RNT = NT < 4 ? NT : 4;
   __shared__ float red[WARPS][2][RNT][32][4];
+  gi::pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * ROWS;
@@ -146,23 +147,24 @@ skinny_kernel(void* __restrict__ out_, const __nv_bfloat16* __restrict__ A, cons
 template <int NT, int UNROLL>
 int launch_mode(int mode, dim3 grid, cudaStream_t s, void* out, const __nv_bfloat16* A, const __nv_bfloat16* W, int M, int N,
                 int K, long lda, long ldw, long ldo) {
+  cudaError_t e = cudaSuccess;
   switch (mode) {
     case GI_SKINNY_STORE_BF16:
-      skinny_kernel<NT, UNROLL, GI_SKINNY_STORE_BF16><<<grid, WARPS * 32, 0, s>>>(out, A, W, M, N, K, lda, ldw, ldo);
+      e = gi::launch(skinny_kernel<NT, UNROLL, GI_SKINNY_STORE_BF16>, grid, dim3(WARPS * 32), 0, s, out, A, W, M, N, K, lda, ldw, ldo);
       break;
     case GI_SKINNY_STORE_F32:
-      skinny_kernel<NT, UNROLL, GI_SKINNY_STORE_F32><<<grid, WARPS * 32, 0, s>>>(out, A, W, M, N, K, lda, ldw, ldo);
+      e = gi::launch(skinny_kernel<NT, UNROLL, GI_SKINNY_STORE_F32>, grid, dim3(WARPS * 32), 0, s, out, A, W, M, N, K, lda, ldw, ldo);
       break;
     case GI_SKINNY_ACCUM_F32:
-      skinny_kernel<NT, UNROLL, GI_SKINNY_ACCUM_F32><<<grid, WARPS * 32, 0, s>>>(out, A, W, M, N, K, lda, ldw, ldo);
+      e = gi::launch(skinny_kernel<NT, UNROLL, GI_SKINNY_ACCUM_F32>, grid, dim3(WARPS * 32), 0, s, out, A, W, M, N, K, lda, ldw, ldo);
       break;
     case GI_SKINNY_SWIGLU:
-      skinny_kernel<NT, UNROLL, GI_SKINNY_SWIGLU><<<grid, WARPS * 32, 0, s>>>(out, A, W, M, N, K, lda, ldw, ldo);
+      e = gi::launch(skinny_kernel<NT, UNROLL, GI_SKINNY_SWIGLU>, grid, dim3(WARPS * 32), 0, s, out, A, W, M, N, K, lda, ldw, ldo);
       break;
     default:
       return gi::fail(GI_ERR_ARG, "skinny product: unknown mode %d", mode);
   }
-  return gi::check_launch("skinny product");
+  return gi::check(e, "skinny product");
 }
 
 }  // namespace

@@ -20,77 +20,17 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "tc_utils.cuh"
 
 namespace {
 
 constexpr int BM = 128;      // rows of A per block = tensor-memory lanes
 constexpr int BK = 64;       // k-columns per stage = one 128-byte swizzle row
 constexpr int THREADS = 192; // warp 0: TMA, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 __device__ int g_status = 0;   // 0 = fine; else which wait ran out (1 producer, 2 mma, 3 epilogue)
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Waits for the phase with this parity to complete; gives up after WAIT_LIMIT tries and says which role did.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int who) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  atomicCAS(&g_status, 0, who);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in 8-row groups of
-// 1024 bytes: start address / 16 in bits 0-13, leading offset (unused here) 1 in bits 16-29, 1024 / 16 between
-// row groups in bits 32-45, descriptor version 1 in bits 46-47, swizzle mode 2 (128 bytes) in bits 61-63.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-         ((uint64_t)2 << 61);
-}
+using namespace gi::tc;
 
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS)
@@ -132,7 +72,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t round = (uint32_t)(kb / STAGES);
-        if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, 1)) break;     // a fresh barrier passes the first round
+        if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, 1, &g_status)) break;     // a fresh barrier passes the first round
         mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
         const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
         tma_load_2d(dst, &map_a, kb * BK, m0, full0 + 8 * s);
@@ -145,7 +85,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % STAGES;
         const uint32_t round = (uint32_t)(kb / STAGES);
-        ok = mbar_wait(full0 + 8 * s, round & 1, 2);
+        ok = mbar_wait(full0 + 8 * s, round & 1, 2, &g_status);
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -161,7 +101,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int quarter = warp & 3;             // the tensor-memory lanes this warp may read: 32 * (warp % 4)
     const int row = quarter * 32 + lane;
     const long m = (long)m0 + row;
-    const bool live = mbar_wait(done, 0, 3);
+    const bool live = mbar_wait(done, 0, 3, &g_status);
     tc_fence_after();
     if (live) {
 #pragma unroll 1
@@ -261,7 +201,9 @@ EncodeTiled encoder() {
 
 // Tensor maps by (address, rows, columns, row stride, box rows): a map is pure data, and the same weights
 // and the same activation buffers come back step after step.
-int tensor_map(CUtensorMap* out, const void* base, int rows, int cols, long ld, int box_rows) {
+}  // namespace
+
+int gi::tensor_map_2d(CUtensorMap* out, const void* base, int rows, int cols, long ld, int box_rows) {
   typedef std::tuple<const void*, int, int, long, int> Key;
   static std::map<Key, CUtensorMap> cache;
   static std::mutex lock;
@@ -286,6 +228,8 @@ int tensor_map(CUtensorMap* out, const void* base, int rows, int cols, long ld, 
   cache[key] = *out;
   return GI_OK;
 }
+
+namespace {
 
 template <int BN, int STAGES, int MODE>
 int launch(void* out, const CUtensorMap& ma, const CUtensorMap& mw, int M, int N, int K, long ldo, cudaStream_t s) {
@@ -327,9 +271,9 @@ extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W
   if (tile_n != 128 && tile_n != 256) return gi::fail(GI_ERR_ARG, "tensor-core product: tile width %d, 128 or 256", tile_n);
   if ((M + BM - 1) / BM > 2147483647 || (N + tile_n - 1) / tile_n > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "tensor-core product: too many tiles");
   CUtensorMap ma, mw;
-  int rc = tensor_map(&ma, A, M, K, lda, BM);
+  int rc = gi::tensor_map_2d(&ma, A, M, K, lda, BM);
   if (rc != GI_OK) return rc;
-  rc = tensor_map(&mw, W, N, K, ldw, tile_n);
+  rc = gi::tensor_map_2d(&mw, W, N, K, ldw, tile_n);
   if (rc != GI_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   if (tile_n == 128) return launch_mode<128, 3>(mode, out, ma, mw, M, N, K, ldo, s);

@@ -15,6 +15,7 @@ namespace {
 // shared by all layers, which rotate with the same positions and frequencies.
 __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
                                   const float* __restrict__ inv_freq, int half, int total) {
+  gi::pdl_prologue();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int t = idx / half, i = idx % half;
@@ -30,6 +31,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* __
                                   const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int n_heads, int n_kv, int hd, int rot,
                                   int adjacent, int write_cache) {
+  gi::pdl_prologue();
   const int t = blockIdx.x, head = blockIdx.y;
   const int half = rot / 2;
   T* src = qkv + (size_t)t * ld + (size_t)head * hd;
@@ -69,8 +71,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* __
 extern "C" int gi_rope_table(float* table, const int* positions, const float* inv_freq, int n_tokens, int rot, void* stream) {
   const int half = rot / 2, total = n_tokens * half;
   if (total <= 0) return GI_OK;
-  rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>((float2*)table, positions, inv_freq, half, total);
-  return gi::check_launch("rope table");
+  return gi::check(gi::launch(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (float2*)table,
+                              positions, inv_freq, half, total), "rope table");
 }
 
 extern "C" int gi_rope_cache_write(void* qkv, int dtype, long ld, const float* table, const int* positions, const int* slots,
@@ -85,8 +87,9 @@ extern "C" int gi_rope_cache_write(void* qkv, int dtype, long ld, const float* t
   if (heads > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "rope: more than 65535 heads in one launch");
   dim3 grid(n_tokens, heads);
   const int threads = hd >= 128 ? 64 : 32;
+  cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T,
-      (rope_cache_kernel<T><<<grid, threads, 0, (cudaStream_t)stream>>>((T*)qkv, ld, (const float2*)table, positions, slots, block_table,
-          max_pages, (T*)kcache, (T*)vcache, n_heads, n_kv, hd, rot, adjacent, write_cache)));
-  return gi::check_launch("rope_cache_write");
+      e = gi::launch(rope_cache_kernel<T>, grid, dim3(threads), 0, (cudaStream_t)stream, (T*)qkv, ld, (const float2*)table, positions,
+                     slots, block_table, max_pages, (T*)kcache, (T*)vcache, n_heads, n_kv, hd, rot, adjacent, write_cache));
+  return gi::check(e, "rope_cache_write");
 }

@@ -138,6 +138,7 @@ __global__ void __launch_bounds__(THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, int n, float temperature, int top_k,
               float top_p, u64* __restrict__ rng_state, const int* __restrict__ state_index) {
   __shared__ Shared sh;
+  gi::pdl_prologue();
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* row = logits + (size_t)r * ld;
 
@@ -331,7 +332,6 @@ extern "C" int gi_sample(int* out_tokens, const float* logits, long ld, int n_ro
   if (vocab <= 0) return gi::fail(GI_ERR_ARG, "sample: empty vocabulary");
   if (temperature > 0.f && !rng_state) return gi::fail(GI_ERR_ARG, "sample: temperature sampling needs generator states");
   if (top_k < 0) return gi::fail(GI_ERR_ARG, "sample: top_k must not be negative");
-  sample_kernel<<<n_rows, THREADS, 0, (cudaStream_t)stream>>>(out_tokens, logits, ld, vocab, temperature, top_k, top_p,
-                                                             rng_state, state_index);
-  return gi::check_launch("sample");
+  return gi::check(gi::launch(sample_kernel, dim3(n_rows), dim3(THREADS), 0, (cudaStream_t)stream, out_tokens, logits, ld, vocab,
+                              temperature, top_k, top_p, rng_state, state_index), "sample");
 }

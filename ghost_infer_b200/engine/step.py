@@ -52,14 +52,15 @@ class StepContext:
         self.host_slots: List[int] = []
         self.host_pos0: List[int] = []
 
-    def decode_splits(self, n_kv: int, group: int) -> int:
-        """Into how many slices of its context a decode block family cuts a sequence."""
+    def decode_splits(self, n_kv: int, group: int, rows_per_block: int = 8, blocks_per_sm: float = 2) -> int:
+        """Into how many slices of its context the decode attention cuts a sequence: as many as fill the GPU
+        once (blocks that wait for a second wave cost more than longer slices), at least 128 positions each."""
         if self.fixed_splits is not None:
             return self.fixed_splits
-        chunks = (group + 7) // 8
+        chunks = (group + rows_per_block - 1) // rows_per_block
         blocks = max(1, self.n_seqs * n_kv * chunks)
-        want = (2 * self.sm_count + blocks - 1) // blocks
-        return int(max(1, min(want, 32, self.max_kv_len // 256)))
+        fit = int(blocks_per_sm * self.sm_count) // blocks
+        return int(max(1, min(fit, 32, self.max_kv_len // 128)))
 
 
 class _Staging:
@@ -194,7 +195,10 @@ class Engine:
         """One slice count for a captured decode step: what the model's attention layers would choose."""
         if not self._attn_shapes:
             return 1
-        return max(ctx.decode_splits(kv, group) for kv, group in self._attn_shapes)
+        fast = self.model.rt.dtype == torch.bfloat16
+        from ..kernels import ops
+        per_sm = (1 if fast else 2) * ops.TUNE["attn_waves"]
+        return max(ctx.decode_splits(kv, group, 16 if fast else 8, per_sm) for kv, group in self._attn_shapes)
 
     def decoder(self, slots: Sequence[int], use_graph: bool = True):
         """A runner of one-token steps for these slots (see engine.decode.DecodeRunner)."""

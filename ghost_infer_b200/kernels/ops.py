@@ -39,6 +39,8 @@ def _bind():
         "gi_rope_cache_write": [P, I, L, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P],
         "gi_attn_prefill_generic": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
+        "gi_gemm_stream_bf16": [P, I, P, P, P, P, I, I, I, I, L, L, L, I, P],
+        "gi_gemm_stream_status": [P],
         "gi_gemm_tc_bf16": [P, I, P, P, I, I, I, L, L, L, I, P],
         "gi_gemm_tc_status": [P],
         "gi_attn_prefill_tc": [P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
@@ -49,6 +51,7 @@ def _bind():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.gi_gemm_stream_scratch_floats.restype = c_long
     _bound = lib
     return lib
 
@@ -199,6 +202,88 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
     ldo = _rows(out, "output")
     _check(lib, lib.gi_gemm_skinny_bf16(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), m, n, k, lda, ldw, ldo, _stream()))
     return out
+
+
+# Choices measured on a B200; benchmarks may override them to try alternatives.
+TUNE = {"small_skinny": False, "attn_waves": 1.0}
+USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch: consecutive kernels of a stream that support it overlap one's start with
+    the other's end (and the decode product prefetches weights meanwhile).  Process-wide."""
+    lib = _bind()
+    lib.gi_set_pdl(int(bool(on)))
+
+
+def get_pdl() -> bool:
+    return bool(_bind().gi_get_pdl())
+
+
+_STREAM_COUNTERS = 8192
+_stream_scratch = {}
+
+
+def _stream_buffers(device: torch.device):
+    """Scratch of the streamed product, one set per device, allocated once (its address is baked into graphs)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _stream_scratch:
+        lib = _bind()
+        n = int(lib.gi_gemm_stream_scratch_floats())
+        _stream_scratch[key] = (torch.empty(n, dtype=torch.float32, device=device),
+                                torch.zeros(_STREAM_COUNTERS, dtype=torch.int32, device=device))
+    return _stream_scratch[key]
+
+
+def gemm_stream(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch.Tensor] = None,
+                pdl: Optional[bool] = None) -> torch.Tensor:
+    """out[M, N] (op)= a[M, K] @ w[N, K]^T for M <= 64: persistent, TMA-fed, tcgen05, stream-K balanced; the decode
+    step's product.  Modes as gemm_skinny's."""
+    lib = _bind()
+    _cuda(a, "activations")
+    _cuda(w, "weights")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the streamed product takes bfloat16 operands")
+    lda, ldw = _rows(a, "activations"), _rows(w, "weights")
+    m, k = a.shape
+    n, kw = w.shape
+    if k != kw:
+        raise KernelError(f"matrix product: activations are {k} wide, the weights take {kw}")
+    cols = n // 2 if mode == SKINNY_SWIGLU else n
+    want = {SKINNY_STORE_BF16: torch.bfloat16, SKINNY_SWIGLU: torch.bfloat16}.get(mode, torch.float32)
+    if out is None:
+        if mode == SKINNY_ACCUM_F32:
+            raise KernelError("matrix product: accumulation needs an output to add to")
+        out = torch.empty((m, cols), dtype=want, device=a.device)
+    if out.shape != (m, cols) or out.dtype != want:
+        raise KernelError(f"matrix product: output is {tuple(out.shape)} {out.dtype}, wanted {(m, cols)} {want}")
+    ldo = _rows(out, "output")
+    scratch, counters = _stream_buffers(a.device)
+    if (n + 127) // 128 > counters.numel():
+        raise KernelError(f"the streamed product takes at most {counters.numel() * 128} rows of weights")
+    _check(lib, lib.gi_gemm_stream_bf16(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), scratch.data_ptr(),
+                                        counters.data_ptr(), counters.numel(), m, n, k, lda, ldw, ldo,
+                                        -1 if pdl is None else int(pdl), _stream()))
+    return out
+
+
+def gemm_stream_status() -> int:
+    lib = _bind()
+    status = ctypes.c_int(0)
+    _check(lib, lib.gi_gemm_stream_status(ctypes.byref(status)), 0)
+    return status.value
+
+
+def _decode_product(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch.Tensor]) -> torch.Tensor:
+    """The streamed product has a fixed cost of a few microseconds (set-up, and partial sums that cross blocks)
+    and then runs at the memory's speed; the register-fed kernel starts faster and streams slower.  Alone, the
+    latter wins for at most 8 rows against less than 64 MB of weights; inside a decode step with dependent
+    launch the streamed one wins everywhere (it fetches weights while its predecessor drains), so it is the
+    default and `TUNE["small_skinny"]` switches the other choice on."""
+    small = TUNE["small_skinny"] and a.shape[0] <= 8 and w.shape[0] * w.shape[1] * 2 < (64 << 20)
+    if USE_STREAM and not small and (w.shape[0] + 127) // 128 <= _STREAM_COUNTERS:
+        return gemm_stream(a, w, mode, out)
+    return gemm_skinny(a, w, mode, out)
 
 
 TC_TILE_N = 256     # width of the tensor-core product's output tile (128 or 256)
@@ -417,7 +502,7 @@ def linear(h: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = No
     mode = SKINNY_ACCUM_F32 if accumulate else {torch.bfloat16: SKINNY_STORE_BF16, torch.float32: SKINNY_STORE_F32}.get(want)
     if mode is not None:
         if skinny_ok(h, w):
-            return gemm_skinny(h, w, mode, out)
+            return _decode_product(h, w, mode, out)
         if tc_ok(h, w) and _tc_out_ok(out, mode, w.shape[0]):
             return gemm_tc(h, w, mode, out)
     return gemm_generic(h, w, out=out, out_dtype=out_dtype, accumulate=accumulate)
@@ -426,7 +511,7 @@ def linear(h: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = No
 def swiglu_interleaved(h: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
     """silu(Wgate h) * (Wup h) where `w_interleaved` holds gate and up rows in blocks [8 gate | 8 up]."""
     if skinny_ok(h, w_interleaved):
-        return gemm_skinny(h, w_interleaved, SKINNY_SWIGLU)
+        return _decode_product(h, w_interleaved, SKINNY_SWIGLU, None)
     if tc_ok(h, w_interleaved) and w_interleaved.shape[0] % 16 == 0:
         return gemm_tc(h, w_interleaved, SKINNY_SWIGLU)
     gu = linear(h, w_interleaved, out_dtype=h.dtype)
@@ -440,12 +525,14 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
     if memory.k is None:
         raise KernelError("attention needs a cache to read from")
     if step.is_decode:
-        n_splits = step.decode_splits(n_kv, n_heads // n_kv)
+        fast = attn_decode_tc_ok(qkv, memory.k, head_dim)
+        # the tensor-core kernel packs 16 heads of a group into a block and keeps one block per SM
+        n_splits = step.decode_splits(n_kv, n_heads // n_kv, 16 if fast else 8, (1 if fast else 2) * TUNE["attn_waves"])
         part_o = part_ml = None
         if n_splits > 1:
             part_o = torch.empty((step.n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
-        kernel = attn_decode_tc if attn_decode_tc_ok(qkv, memory.k, head_dim) else attn_decode_generic
+        kernel = attn_decode_tc if fast else attn_decode_generic
         return kernel(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
                       step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
     kernel = attn_prefill_tc if attn_decode_tc_ok(qkv, memory.k, head_dim) and out.stride(0) % 2 == 0 else attn_prefill_generic

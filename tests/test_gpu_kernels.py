@@ -413,3 +413,40 @@ def test_gemm_tensor_cores_swiglu(tile_n, m, f, k):
     out = ops.gemm_tc(a, w, ops.SKINNY_SWIGLU, tile_n=tile_n)
     assert ops.gemm_tc_status() == 0
     torch.testing.assert_close(out.double(), ref, rtol=1e-2, atol=1e-3 * float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("pdl", [False, True])
+@pytest.mark.parametrize("m", [1, 8, 13, 16, 17, 32, 50, 64])
+@pytest.mark.parametrize("n,k", [(100, 72), (128, 64), (6144, 4096), (4096, 14336), (1000, 520), (40000, 264)])
+def test_gemm_stream(pdl, m, n, k):
+    """The persistent stream-K decode product: tiles cut between blocks (summed by whoever arrives last, in
+    K order), rows of W that stop inside a tile, K that stops inside a block, every token-tile width."""
+    a, w = rnd(m, k, dtype=torch.bfloat16, seed=40), rnd(n, k, dtype=torch.bfloat16, seed=41)
+    ref = a.double() @ w.double().T
+    terms = a.double().abs() @ w.double().abs().T
+    out = ops.gemm_stream(a, w, ops.SKINNY_STORE_F32, pdl=pdl)
+    assert ops.gemm_stream_status() == 0
+    assert ((out.double() - ref).abs() <= 2e-6 * terms + 1e-7).all(), float((out.double() - ref).abs().max())
+    again = ops.gemm_stream(a, w, ops.SKINNY_STORE_F32, pdl=pdl)
+    assert torch.equal(out, again)                    # the same bits whoever arrived last
+    out16 = ops.gemm_stream(a, w, ops.SKINNY_STORE_BF16, pdl=pdl)
+    assert ((out16.double() - ref).abs() <= 2 ** -8 * ref.abs() + 2e-6 * terms + 1e-7).all()
+    acc = rnd(m, n, seed=42)
+    before = acc.clone()
+    ops.gemm_stream(a, w, ops.SKINNY_ACCUM_F32, acc, pdl=pdl)
+    assert ((acc.double() - (before.double() + ref)).abs() <= 2e-6 * (terms + before.abs().double()) + 1e-6).all()
+    assert ops.gemm_stream_status() == 0
+
+
+@pytest.mark.parametrize("m", [1, 8, 20, 64])
+@pytest.mark.parametrize("f,k", [(176, 64), (1000, 4096), (14336, 512)])
+def test_gemm_stream_swiglu(m, f, k):
+    a = rnd(m, k, dtype=torch.bfloat16, seed=43)
+    g, u = rnd(f, k, dtype=torch.bfloat16, seed=44, scale=0.3), rnd(f, k, dtype=torch.bfloat16, seed=45, scale=0.3)
+    w = torch.stack([g.view(f // 8, 8, k), u.view(f // 8, 8, k)], dim=1).reshape(2 * f, k).contiguous()
+    gd, ud = a.double() @ g.double().T, a.double() @ u.double().T
+    ref = gd / (1 + torch.exp(-gd)) * ud
+    out = ops.gemm_stream(a, w, ops.SKINNY_SWIGLU)
+    assert ops.gemm_stream_status() == 0
+    assert out.shape == (m, f)
+    torch.testing.assert_close(out.double(), ref, rtol=1e-2, atol=1e-3 * float(ref.abs().max()))

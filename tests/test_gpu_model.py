@@ -165,3 +165,32 @@ def test_host_checks_come_before_any_launch(engines):
         eng.step([gi.StepEntry(s, [1] * 4000, [0])])
     assert eng.cache.length(s) == 0
     eng.cache.close_slot(s)
+
+
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_decoding_with_dependent_launch(model_dirs, tiny_configs, name):
+    """Programmatic dependent launch lets a kernel start while its predecessor drains; results must not move.
+    A batch decodes through the graph runner with it on, against the plain implementation and against itself off."""
+    from ghost_infer_b200.kernels import ops
+    d = model_dirs(name, "bfloat16")
+    seqs = [tokens_for(tiny_configs[name], n, 40 + i) for i, n in enumerate((150, 90, 131))]
+    refs = [plain_logits(d, s) for s in seqs]
+    outs = {}
+    for pdl in (False, True):
+        ops.set_pdl(pdl)
+        try:
+            eng = make_engine(d, "bfloat16")
+            slots = [eng.cache.open_slot() for _ in seqs]
+            eng.step([gi.StepEntry(s, t[:60], []) for s, t in zip(slots, seqs)])
+            runner = eng.decoder(slots)
+            got = [[] for _ in seqs]
+            for j in range(60, 90):
+                lg = runner.forward(tokens=[t[j] for t in seqs]).cpu().numpy()
+                for i in range(len(seqs)):
+                    got[i].append(lg[i])
+            outs[pdl] = [np.stack(g) for g in got]
+        finally:
+            ops.set_pdl(False)
+    for i in range(len(seqs)):
+        check_logits(outs[True][i], refs[i][60:90], "bfloat16", f"{name} dependent launch request {i}")
+        assert np.array_equal(outs[True][i], outs[False][i])
