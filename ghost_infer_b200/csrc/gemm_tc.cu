@@ -26,40 +26,54 @@ namespace {
 
 constexpr int BM = 128;      // rows of A per block = tensor-memory lanes
 constexpr int BK = 64;       // k-columns per stage = one 128-byte swizzle row
-constexpr int THREADS = 192; // warp 0: TMA, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue
+constexpr int THREADS = 192; // warp 0: TMA loads, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue
 
 __device__ int g_status = 0;   // 0 = fine; else which wait ran out (1 producer, 2 mma, 3 epilogue)
 
 using namespace gi::tc;
 
+// Writes one staged row (128 bytes = eight 16-byte chunks) into a 128-byte-swizzled staging tile.
+__device__ __forceinline__ void stage_chunk(unsigned char* stg, int row, int j, uint4 v) {
+  *reinterpret_cast<uint4*>(stg + row * 128 + ((j ^ (row & 7)) << 4)) = v;
+}
+
 template <int BN, int STAGES, int MODE>
-__global__ void __launch_bounds__(THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out_,
-               int M, int N, int K, long ldo) {
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_o, int M, int N, int K) {
   constexpr uint32_t A_BYTES = BM * BK * 2, W_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+  constexpr uint32_t STG_BYTES = BM * 128;     // a staging tile: 128 rows of 128 bytes
   // instruction descriptor: float accumulator (bits 4-5 = 1), bfloat16 A and B (bits 7-9, 10-12 = 1), both K-major,
   // N / 8 in bits 17-22, M / 16 in bits 24-28
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  // accumulator columns that make one 128-byte row of output: 32 floats, 64 bfloat16, or 128 gate/up values -> 64 activations
+  constexpr int CW = (MODE == GI_TC_SWIGLU) ? 128 : (MODE == GI_TC_STORE_BF16 ? 64 : 32);
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // full[STAGES], empty[STAGES], accumulator ready
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  unsigned char* staging = smem + STAGES * STAGE_BYTES;                 // two staging tiles
+  uint64_t* bars = (uint64_t*)(staging + 2 * STG_BYTES);               // full[S], empty[S], acc_full[2], acc_empty[2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), done = smem_u32(bars + 2 * STAGES);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const uint32_t accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(done, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(accf0 + 8 * b, 1);
+      mbar_init(acce0 + 8 * b, 4);      // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -67,95 +81,90 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  // Tiles in an order that keeps a tile of W in use by neighbouring blocks: the row tile runs fastest.
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t round = (uint32_t)(kb / STAGES);
-        if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, 1, &g_status)) break;     // a fresh barrier passes the first round
-        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-        const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
-        tma_load_2d(dst, &map_a, kb * BK, m0, full0 + 8 * s);
-        tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full0 + 8 * s);
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(empty0 + 8 * s, (((uint32_t)(it / STAGES)) & 1) ^ 1, 1, &g_status);   // a fresh barrier passes
+          if (!ok) break;
+          mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+          const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          tma_load_2d(dst, &map_a, kb * BK, m0, full0 + 8 * s);
+          tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full0 + 8 * s);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      int it = 0, seg = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t round = (uint32_t)(kb / STAGES);
-        ok = mbar_wait(full0 + 8 * s, round & 1, 2, &g_status);
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++seg) {
+        const int buf = seg & 1;
+        ok = mbar_wait(acce0 + 8 * buf, (((uint32_t)(seg >> 1)) & 1) ^ 1, 2, &g_status);      // the buffer was drained
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
-        const uint64_t da = smem_desc(a_addr), dw = smem_desc(a_addr + A_BYTES);
+        const uint32_t d = tmem + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(full0 + 8 * s, ((uint32_t)(it / STAGES)) & 1, 2, &g_status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint64_t da = smem_desc(a_addr), dw = smem_desc(a_addr + A_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k)     // 16 k-columns = 32 bytes further along the swizzled row
-          tc_mma(tmem, da + (uint64_t)(2 * k), dw + (uint64_t)(2 * k), IDESC, (kb > 0 || k > 0) ? 1u : 0u);
-        tc_commit(empty0 + 8 * s);            // arrives when these products no longer read the stage
+          for (int k = 0; k < BK / 16; ++k)     // 16 k-columns = 32 bytes further along the swizzled row
+            tc_mma(d, da + (uint64_t)(2 * k), dw + (uint64_t)(2 * k), IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit(empty0 + 8 * s);            // arrives when these products no longer read the stage
+        }
+        if (ok) tc_commit(accf0 + 8 * buf);     // arrives when the accumulator is complete
       }
-      tc_commit(done);                        // arrives when the accumulator is complete
     }
   } else {
-    const int quarter = warp & 3;             // the tensor-memory lanes this warp may read: 32 * (warp % 4)
+    // Epilogue: tensor memory -> registers -> swizzled staging tile -> TMA store (or TMA add into the float
+    // residual stream: the addition happens at the memory side, nothing is read back here).
+    const int quarter = warp & 3;               // the tensor-memory lanes this warp may read: 32 * (warp % 4)
     const int row = quarter * 32 + lane;
-    const long m = (long)m0 + row;
-    const bool live = mbar_wait(done, 0, 3, &g_status);
-    tc_fence_after();
-    if (live) {
+    const bool issuer = (warp == 2 && lane == 0);
+    int seg = 0, chunk_no = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++seg) {
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int buf = seg & 1;
+      ok = mbar_wait(accf0 + 8 * buf, ((uint32_t)(seg >> 1)) & 1, 3, &g_status);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
-        tc_wait_ld();
-        const int nb = n0 + c * 32;
-        if (m >= M || nb >= N) {
-          // nothing to store for this thread; it still takes part in the next (warp-wide) tensor-memory load
-        } else if (MODE == GI_TC_SWIGLU) {
-          // columns [8 gate | 8 up | 8 gate | 8 up] -> 16 activations
-          __nv_bfloat16* o = (__nv_bfloat16*)out_ + m * ldo + nb / 2;
+      for (int c = 0; c < BN / CW; ++c, ++chunk_no) {
+        unsigned char* stg = staging + (chunk_no & 1) * STG_BYTES;
+        // the TMA operation that last read this staging tile (two chunks ago) must be done with it
+        if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll
-          for (int blk = 0; blk < 2; ++blk) {
-            if (nb + blk * 16 >= N) break;
-            uint32_t packed[4];
+        for (int q = 0; q < CW / 32; ++q) {
+          uint32_t r[32];
+          tc_ld32(tbase + (uint32_t)(c * CW + q * 32), r);
+          tc_wait_ld();
+          if (MODE == GI_TC_SWIGLU) {
+            // columns [8 gate | 8 up | 8 gate | 8 up] -> 16 activations = 32 bytes = chunks 2q, 2q + 1 of the row
 #pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-              const float g0 = __uint_as_float(r[blk * 16 + j]), g1 = __uint_as_float(r[blk * 16 + j + 1]);
-              const float u0 = __uint_as_float(r[blk * 16 + 8 + j]), u1 = __uint_as_float(r[blk * 16 + 8 + j + 1]);
-              __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
-              packed[j / 2] = *reinterpret_cast<uint32_t*>(&v);
+            for (int blk = 0; blk < 2; ++blk) {
+              uint32_t p[4];
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                const float g0 = __uint_as_float(r[blk * 16 + j]), g1 = __uint_as_float(r[blk * 16 + j + 1]);
+                const float u0 = __uint_as_float(r[blk * 16 + 8 + j]), u1 = __uint_as_float(r[blk * 16 + 8 + j + 1]);
+                __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                p[j / 2] = *reinterpret_cast<uint32_t*>(&v);
+              }
+              stage_chunk(stg, row, q * 2 + blk, make_uint4(p[0], p[1], p[2], p[3]));
             }
-            *reinterpret_cast<uint4*>(o + blk * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          }
-        } else if (MODE == GI_TC_ACCUM_F32) {
-          float* o = (float*)out_ + m * ldo + nb;
-          if (nb + 32 <= N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = *reinterpret_cast<float4*>(o + j);
-              v.x += __uint_as_float(r[j]);
-              v.y += __uint_as_float(r[j + 1]);
-              v.z += __uint_as_float(r[j + 2]);
-              v.w += __uint_as_float(r[j + 3]);
-              *reinterpret_cast<float4*>(o + j) = v;
-            }
-          } else {
-            for (int j = 0; j < 32 && nb + j < N; ++j) o[j] += __uint_as_float(r[j]);
-          }
-        } else if (MODE == GI_TC_STORE_F32) {
-          float* o = (float*)out_ + m * ldo + nb;
-          if (nb + 32 <= N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-          } else {
-            for (int j = 0; j < 32 && nb + j < N; ++j) o[j] = __uint_as_float(r[j]);
-          }
-        } else {
-          __nv_bfloat16* o = (__nv_bfloat16*)out_ + m * ldo + nb;
-          if (nb + 32 <= N) {
+          } else if (MODE == GI_TC_STORE_BF16) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               uint32_t p[4];
@@ -164,21 +173,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]), __uint_as_float(r[j + 2 * e + 1]));
                 p[e] = *reinterpret_cast<uint32_t*>(&v);
               }
-              *reinterpret_cast<uint4*>(o + j) = make_uint4(p[0], p[1], p[2], p[3]);
+              stage_chunk(stg, row, q * 4 + j / 8, make_uint4(p[0], p[1], p[2], p[3]));
             }
           } else {
-            for (int j = 0; j < 32 && nb + j < N; ++j) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) stage_chunk(stg, row, j / 4, make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]));
           }
         }
-        __syncwarp();
+        if (c == BN / CW - 1) {
+          // the whole accumulator is in registers or staged: hand the buffer back to the MMA thread
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // staged rows become visible to the TMA engine
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer) {
+          const int x = (MODE == GI_TC_SWIGLU) ? (n0 + c * CW) / 2 : n0 + c * CW;   // in elements of the output
+          const int limit = (MODE == GI_TC_SWIGLU) ? N / 2 : N;
+          if (x < limit) {     // rows and columns past the matrix's edge are clipped by the TMA engine
+            if (MODE == GI_TC_ACCUM_F32)
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&map_o), "r"(smem_u32(stg)), "r"(x), "r"(m0) : "memory");
+            else
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&map_o), "r"(smem_u32(stg)), "r"(x), "r"(m0) : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
       }
     }
+    if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has landed before the block leaves
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(2 * BN)) : "memory");
   }
 }
 
@@ -199,15 +230,15 @@ EncodeTiled encoder() {
   return fn;
 }
 
-// Tensor maps by (address, rows, columns, row stride, box rows): a map is pure data, and the same weights
+// Tensor maps by (address, rows, columns, row stride, element, box): a map is pure data, and the same weights
 // and the same activation buffers come back step after step.
 }  // namespace
 
-int gi::tensor_map_2d(CUtensorMap* out, const void* base, int rows, int cols, long ld, int box_rows) {
-  typedef std::tuple<const void*, int, int, long, int> Key;
+int gi::tensor_map_2d_ex(CUtensorMap* out, const void* base, long rows, long cols, long ld, int elem, int box_cols, int box_rows) {
+  typedef std::tuple<const void*, long, long, long, int, int, int> Key;
   static std::map<Key, CUtensorMap> cache;
   static std::mutex lock;
-  const Key key(base, rows, cols, ld, box_rows);
+  const Key key(base, rows, cols, ld, elem, box_cols, box_rows);
   std::lock_guard<std::mutex> guard(lock);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -216,24 +247,40 @@ int gi::tensor_map_2d(CUtensorMap* out, const void* base, int rows, int cols, lo
   }
   EncodeTiled enc = encoder();
   if (!enc) return gi::fail(GI_ERR_CUDA, "tensor-core product: the driver does not export cuTensorMapEncodeTiled");
+  const int bytes = elem == GI_F32 ? 4 : 2;
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, elem == GI_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return gi::fail(GI_ERR_CUDA, "tensor-core product: cuTensorMapEncodeTiled failed with %d", (int)r);
   if (cache.size() > 4096) cache.clear();
   cache[key] = *out;
   return GI_OK;
 }
 
+int gi::tensor_map_2d(CUtensorMap* out, const void* base, int rows, int cols, long ld, int box_rows) {
+  return gi::tensor_map_2d_ex(out, base, rows, cols, ld, GI_BF16, BK, box_rows);
+}
+
 namespace {
 
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int BN, int STAGES, int MODE>
-int launch(void* out, const CUtensorMap& ma, const CUtensorMap& mw, int M, int N, int K, long ldo, cudaStream_t s) {
-  constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, int M, int N, int K, cudaStream_t s) {
+  constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 2 * BM * 128 + (2 * STAGES + 4) * 8 + 16 + 1024;
   auto kern = gemm_tc_kernel<BN, STAGES, MODE>;
   static bool configured = false;
   if (!configured) {
@@ -241,18 +288,19 @@ int launch(void* out, const CUtensorMap& ma, const CUtensorMap& mw, int M, int N
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "tensor-core product: %s", cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
-  kern<<<grid, THREADS, smem, s>>>(ma, mw, out, M, N, K, ldo);
+  const long tiles = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  kern<<<grid, THREADS, smem, s>>>(ma, mw, mo, M, N, K);
   return gi::check_launch("tensor-core product");
 }
 
 template <int BN, int STAGES>
-int launch_mode(int mode, void* out, const CUtensorMap& ma, const CUtensorMap& mw, int M, int N, int K, long ldo, cudaStream_t s) {
+int launch_mode(int mode, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, int M, int N, int K, cudaStream_t s) {
   switch (mode) {
-    case GI_TC_STORE_BF16: return launch<BN, STAGES, GI_TC_STORE_BF16>(out, ma, mw, M, N, K, ldo, s);
-    case GI_TC_STORE_F32: return launch<BN, STAGES, GI_TC_STORE_F32>(out, ma, mw, M, N, K, ldo, s);
-    case GI_TC_ACCUM_F32: return launch<BN, STAGES, GI_TC_ACCUM_F32>(out, ma, mw, M, N, K, ldo, s);
-    case GI_TC_SWIGLU: return launch<BN, STAGES, GI_TC_SWIGLU>(out, ma, mw, M, N, K, ldo, s);
+    case GI_TC_STORE_BF16: return launch<BN, STAGES, GI_TC_STORE_BF16>(ma, mw, mo, M, N, K, s);
+    case GI_TC_STORE_F32: return launch<BN, STAGES, GI_TC_STORE_F32>(ma, mw, mo, M, N, K, s);
+    case GI_TC_ACCUM_F32: return launch<BN, STAGES, GI_TC_ACCUM_F32>(ma, mw, mo, M, N, K, s);
+    case GI_TC_SWIGLU: return launch<BN, STAGES, GI_TC_SWIGLU>(ma, mw, mo, M, N, K, s);
   }
   return gi::fail(GI_ERR_ARG, "tensor-core product: unknown mode %d", mode);
 }
@@ -270,14 +318,19 @@ extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W
   if (mode == GI_TC_SWIGLU && N % 16 != 0) return gi::fail(GI_ERR_UNSUPPORTED, "tensor-core product: SwiGLU needs interleaved rows, N (%d) a multiple of 16", N);
   if (tile_n != 128 && tile_n != 256) return gi::fail(GI_ERR_ARG, "tensor-core product: tile width %d, 128 or 256", tile_n);
   if ((M + BM - 1) / BM > 2147483647 || (N + tile_n - 1) / tile_n > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "tensor-core product: too many tiles");
-  CUtensorMap ma, mw;
+  CUtensorMap ma, mw, mo;
   int rc = gi::tensor_map_2d(&ma, A, M, K, lda, BM);
   if (rc != GI_OK) return rc;
   rc = gi::tensor_map_2d(&mw, W, N, K, ldw, tile_n);
   if (rc != GI_OK) return rc;
+  // the output as the TMA engine sees it: rows of 128 bytes per box (32 floats or 64 bfloat16)
+  const bool f32 = (mode == GI_TC_STORE_F32 || mode == GI_TC_ACCUM_F32);
+  const long out_cols = mode == GI_TC_SWIGLU ? N / 2 : N;
+  rc = gi::tensor_map_2d_ex(&mo, out, M, out_cols, ldo, f32 ? GI_F32 : GI_BF16, f32 ? 32 : 64, BM);
+  if (rc != GI_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  if (tile_n == 128) return launch_mode<128, 3>(mode, out, ma, mw, M, N, K, ldo, s);
-  return launch_mode<256, 4>(mode, out, ma, mw, M, N, K, ldo, s);
+  if (tile_n == 128) return launch_mode<128, 6>(mode, ma, mw, mo, M, N, K, s);
+  return launch_mode<256, 4>(mode, ma, mw, mo, M, N, K, s);
 }
 
 // Reads and clears the status word of the tensor-core product (0 = every wait was met).  Synchronises the device.

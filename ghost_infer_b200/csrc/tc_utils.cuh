@@ -82,5 +82,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // A 2-D bfloat16 tensor map (box: 64 columns x box_rows rows, 128-byte swizzle, zero fill outside), cached by
 // (address, rows, columns, row stride, box rows).  Defined in gemm_tc.cu.
 int tensor_map_2d(CUtensorMap* out, const void* base, int rows, int cols, long ld, int box_rows);
+// The general form: `elem` is GI_F32 or GI_BF16, the box is box_cols x box_rows elements (box_cols * element size = 128 bytes).
+int tensor_map_2d_ex(CUtensorMap* out, const void* base, long rows, long cols, long ld, int elem, int box_cols, int box_rows);
 
 }  // namespace gi
