@@ -78,6 +78,11 @@ int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part_ml, const 
                       const void* vcache, const int* block_table, int max_pages, const int* seq_slots,
                       const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd, float scale, int window,
                       int n_splits, void* stream);
+// the same with a choice of tile: 32 keys (one block per SM) or 16 keys (two blocks per SM)
+int gi_attn_decode_tc_ex(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, const void* kcache,
+                         const void* vcache, const int* block_table, int max_pages, const int* seq_slots,
+                         const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd, float scale, int window,
+                         int n_splits, int tile_keys, void* stream);
 int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const float* part_ml, int n_seqs, int n_heads,
                     int hd, int n_splits, void* stream);
 

@@ -5,7 +5,7 @@
 // one kv head of one sequence and one slice of its context, and all query heads of the group share every
 // key and value row that is read.  Here the group's heads (up to 16) are the rows of an m16n8k16 tile:
 // scores S = Q K^T and outputs O += P V are mma.sync products with 32-bit accumulators, softmax statistics
-// and the running rescale are 32-bit.  Each of the 4 warps walks its own tiles of 32 keys; keys and values
+// and the running rescale are 32-bit.  Each of the 4 warps walks its own tiles of 16 or 32 keys; keys and values
 // arrive by cp.async into a per-warp ring of shared-memory stages (16-byte chunks, XOR-swizzled for
 // ldmatrix), so the next tiles are in flight while one is used.  Warps are merged through shared memory in
 // warp order; slices are merged by the combine kernel in slice order.
@@ -19,10 +19,9 @@
 
 namespace {
 
-constexpr int KT = 32;       // keys per tile
 constexpr int WARPS = 4;
 
-template <int HD, int STAGES>
+template <int HD, int KT, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restrict__ part_o, float* __restrict__ part_ml,
                       const __nv_bfloat16* __restrict__ q, long ldq, const __nv_bfloat16* __restrict__ kcache,
@@ -247,14 +246,14 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
   }
 }
 
-template <int HD, int STAGES>
+template <int HD, int KT, int STAGES>
 int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, float* pml, const __nv_bfloat16* q, long ldq,
            const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int max_pages, const int* slots, const int* lens,
            int H, int KV, float scale, int window, int n_splits) {
   constexpr size_t ring = (size_t)WARPS * STAGES * 2 * KT * HD * 2;
   constexpr size_t merge = (size_t)(WARPS * 16 * HD + 2 * WARPS * 16) * sizeof(float);
   constexpr size_t smem = 16 * HD * 2 + (ring > merge ? ring : merge);
-  auto kern = attn_decode_tc_kernel<HD, STAGES>;
+  auto kern = attn_decode_tc_kernel<HD, KT, STAGES>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -271,11 +270,26 @@ int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, f
 extern "C" int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const float* part_ml, int n_seqs,
                                int n_heads, int hd, int n_splits, void* stream);
 
+extern "C" int gi_attn_decode_tc_ex(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq,
+                                    const void* kcache, const void* vcache, const int* block_table, int max_pages,
+                                    const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
+                                    float scale, int window, int n_splits, int tile_keys, void* stream);
+
 extern "C" int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq,
                                  const void* kcache, const void* vcache, const int* block_table, int max_pages,
                                  const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
                                  float scale, int window, int n_splits, void* stream) {
+  return gi_attn_decode_tc_ex(out, ldo, part_o, part_ml, q, ldq, kcache, vcache, block_table, max_pages, seq_slots, seq_lens, n_seqs,
+                              n_heads, n_kv, hd, scale, window, n_splits, 32, stream);
+}
+
+// tile_keys: 32 (one block per SM, deep rings) or 16 (two blocks per SM)
+extern "C" int gi_attn_decode_tc_ex(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq,
+                                    const void* kcache, const void* vcache, const int* block_table, int max_pages,
+                                    const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
+                                    float scale, int window, int n_splits, int tile_keys, void* stream) {
   if (n_seqs <= 0) return GI_OK;
+  if (tile_keys != 16 && tile_keys != 32) return gi::fail(GI_ERR_ARG, "attention decode (tensor cores): tiles of %d keys, 16 or 32", tile_keys);
   if (hd != 64 && hd != 128) return gi::fail(GI_ERR_UNSUPPORTED, "attention decode (tensor cores): head size %d, only 64 and 128", hd);
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
     return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
@@ -289,12 +303,15 @@ extern "C" int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part
   dim3 grid(n_splits, n_kv * chunks, n_seqs);
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
-  if (hd == 128)
-    rc = launch<128, 3>(grid, s, (__nv_bfloat16*)out, ldo, part_o, part_ml, (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kcache,
-                        (const __nv_bfloat16*)vcache, block_table, max_pages, seq_slots, seq_lens, n_heads, n_kv, scale, window, n_splits);
-  else
-    rc = launch<64, 4>(grid, s, (__nv_bfloat16*)out, ldo, part_o, part_ml, (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kcache,
-                       (const __nv_bfloat16*)vcache, block_table, max_pages, seq_slots, seq_lens, n_heads, n_kv, scale, window, n_splits);
+#define GI_DECODE_TC(HD_, KT_, ST_)                                                                                          \
+  rc = launch<HD_, KT_, ST_>(grid, s, (__nv_bfloat16*)out, ldo, part_o, part_ml, (const __nv_bfloat16*)q, ldq,               \
+                             (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table, max_pages, seq_slots, \
+                             seq_lens, n_heads, n_kv, scale, window, n_splits)
+  if (hd == 128 && tile_keys == 32) GI_DECODE_TC(128, 32, 3);
+  else if (hd == 128) GI_DECODE_TC(128, 16, 3);
+  else if (tile_keys == 32) GI_DECODE_TC(64, 32, 4);
+  else GI_DECODE_TC(64, 16, 4);
+#undef GI_DECODE_TC
   if (rc != GI_OK) return rc;
   if (n_splits > 1) return gi_attn_combine(out, ldo, GI_BF16, part_o, part_ml, n_seqs, n_heads, hd, n_splits, stream);
   return GI_OK;

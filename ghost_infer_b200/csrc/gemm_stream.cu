@@ -107,10 +107,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tma_load_2d(smem_u32(smem + (size_t)i * STAGE_BYTES), &map_w, kb * BK, tile * TILE_ROWS, full0 + 8 * i);
       }
       if (use_pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+      // (tile, kb) of the running unit, advanced without divisions: this thread should spend its time issuing loads
+      int tile = (int)(mine.first / kb_per_tile), kb = (int)(mine.first % kb_per_tile), s = 0;
+      uint32_t round = 0;
       for (; u < mine.last && ok; ++u, ++it) {
-        const int s = it % STAGES;
-        const uint32_t round = (uint32_t)(it / STAGES);
-        const int tile = (int)(u / kb_per_tile), kb = (int)(u % kb_per_tile);
         const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
         if (it >= ahead) {
           ok = mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, 1, &g_stream_status);
@@ -119,6 +119,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           tma_load_2d(dst, &map_w, kb * BK, tile * TILE_ROWS, full0 + 8 * s);
         }
         tma_load_2d(dst + W_BYTES, &map_a, kb * BK, 0, full0 + 8 * s);
+        if (++kb == kb_per_tile) {
+          kb = 0;
+          ++tile;
+        }
+        if (++s == STAGES) {
+          s = 0;
+          ++round;
+        }
       }
     }
   } else if (warp == 1) {

@@ -197,7 +197,7 @@ class Engine:
             return 1
         fast = self.model.rt.dtype == torch.bfloat16
         from ..kernels import ops
-        per_sm = (1 if fast else 2) * ops.TUNE["attn_waves"]
+        per_sm = (2 if (not fast or ops.TUNE["attn_tile_keys"] == 16) else 1) * ops.TUNE["attn_waves"]
         return max(ctx.decode_splits(kv, group, 16 if fast else 8, per_sm) for kv, group in self._attn_shapes)
 
     def decoder(self, slots: Sequence[int], use_graph: bool = True):

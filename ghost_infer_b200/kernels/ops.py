@@ -45,6 +45,7 @@ def _bind():
         "gi_gemm_tc_status": [P],
         "gi_attn_prefill_tc": [P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_decode_tc": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
+        "gi_attn_decode_tc_ex": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
     }
     for name, argtypes in sigs.items():
@@ -205,7 +206,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 
 
 # Choices measured on a B200; benchmarks may override them to try alternatives.
-TUNE = {"small_skinny": False, "attn_waves": 1.0}
+TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -450,7 +451,9 @@ def attn_decode_tc_ok(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> b
 def attn_decode_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                    seq_slots: torch.Tensor, seq_lens: torch.Tensor, n_seqs: int, n_heads: int, n_kv: int,
                    head_dim: int, scale: float, window: Optional[int], n_splits: int, out: torch.Tensor,
-                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                   tile_keys: Optional[int] = None) -> torch.Tensor:
+    """`tile_keys`: 32 (one block per SM, deep rings) or 16 (two blocks per SM); default TUNE["attn_tile_keys"]."""
     lib = _bind()
     _cuda(q, "queries")
     ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
@@ -463,12 +466,12 @@ def attn_decode_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
             raise KernelError("attention scratch for outputs is too small")
         if part_ml.dtype != torch.float32 or part_ml.numel() < n_seqs * n_heads * n_splits * 2:
             raise KernelError("attention scratch for maxima and sums is too small")
-    _check(lib, lib.gi_attn_decode_tc(
+    _check(lib, lib.gi_attn_decode_tc_ex(
         out.data_ptr(), ldo, part_o.data_ptr() if part_o is not None else None,
         part_ml.data_ptr() if part_ml is not None else None, q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(),
         _i32(block_table, "block table"), block_table.shape[1], _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"),
-        n_seqs, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(n_splits), _stream()),
-        2 if n_splits > 1 else 1)
+        n_seqs, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(n_splits),
+        int(tile_keys or TUNE["attn_tile_keys"]), _stream()), 2 if n_splits > 1 else 1)
     return out
 
 
@@ -527,7 +530,8 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
     if step.is_decode:
         fast = attn_decode_tc_ok(qkv, memory.k, head_dim)
         # the tensor-core kernel packs 16 heads of a group into a block and keeps one block per SM
-        n_splits = step.decode_splits(n_kv, n_heads // n_kv, 16 if fast else 8, (1 if fast else 2) * TUNE["attn_waves"])
+        per_sm = (2 if (not fast or TUNE["attn_tile_keys"] == 16) else 1) * TUNE["attn_waves"]
+        n_splits = step.decode_splits(n_kv, n_heads // n_kv, 16 if fast else 8, per_sm)
         part_o = part_ml = None
         if n_splits > 1:
             part_o = torch.empty((step.n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)

@@ -204,9 +204,10 @@ def test_attention_decode(dtype, H, KV, hd, window, splits):
     torch.testing.assert_close(out.double(), ref, **tol(dtype))
 
 
+@pytest.mark.parametrize("tile_keys", [16, 32])
 @pytest.mark.parametrize("H,KV,hd", [(8, 8, 64), (32, 8, 128), (24, 8, 128), (5, 1, 64), (40, 2, 128)])
 @pytest.mark.parametrize("window,splits", [(None, 1), (None, 5), (100, 1), (100, 3)])
-def test_attention_decode_tensor_cores(H, KV, hd, window, splits):
+def test_attention_decode_tensor_cores(tile_keys, H, KV, hd, window, splits):
     """The tensor-core decode kernel: groups of 1, 3, 4, 5 and 20 heads (more than one 16-row tile), pages in
     shuffled order, rows past each sequence's end poisoned with NaN."""
     lens = [1, 31, 64, 65, 700, 333, 96]
@@ -221,7 +222,7 @@ def test_attention_decode_tensor_cores(H, KV, hd, window, splits):
     assert ops.attn_decode_tc_ok(q[:, 0], kc, hd)
     ops.attn_decode_tc(q[:, 0], kc, vc, bt, torch.arange(B, dtype=torch.int32, device=DEV),
                        torch.tensor(lens, dtype=torch.int32, device=DEV), B, H, KV, hd, 0.17, window, splits, out,
-                       part_o, part_ml)
+                       part_o, part_ml, tile_keys=tile_keys)
     ref = attention_ref(q, k, v, [1] * B, [n - 1 for n in lens], H, KV, hd, 0.17, window)[:, 0]
     torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
 
