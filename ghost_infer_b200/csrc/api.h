@@ -12,6 +12,15 @@
 extern "C" {
 #endif
 
+// Partial sums a deferred product left behind (see GI_SKINNY_ACCUM_DEFER): where they are and how the product cut its work.
+typedef struct {
+  const float* partials;     // null: nothing to settle
+  const int* tile_first_cta; // per 128-row tile: the first and the last block that held a piece of it
+  const int* tile_last_cta;
+  const int* cta_first_tile; // per block: the tile its range began in (that piece sits in the block's slot 0)
+  int nt;                    // token-tile width of the product (16, 32 or 64)
+} gi_settle_t;
+
 const char* gi_last_error(void);
 int gi_abi_version(void);
 // Programmatic dependent launch: kernels of a stream may begin while their predecessor drains (off by default).
@@ -22,6 +31,9 @@ int gi_embed(float* out, const void* table, int table_dtype, const int* tokens, 
              void* stream);
 int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows, int n_rows,
                int d, float eps, void* stream);
+// The same, first adding deferred partial sums to the rows it reads (and writing the settled rows back to x).
+int gi_rmsnorm_settle(void* out, int out_dtype, float* x, const void* w, int w_dtype, const int* rows, int n_rows,
+                      int d, float eps, gi_settle_t settle, void* stream);
 int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, int interleaved, void* stream);
 
 int gi_gemm_generic(void* out, int out_dtype, int mode, const void* A, int a_dtype, const void* W, int w_dtype, int M,
@@ -32,6 +44,8 @@ int gi_gemm_generic(void* out, int out_dtype, int mode, const void* A, int a_dty
 #define GI_SKINNY_STORE_F32 1
 #define GI_SKINNY_ACCUM_F32 2   // out (float) += product
 #define GI_SKINNY_SWIGLU 3      // W rows interleaved [8 gate | 8 up]; out[M, N/2] bfloat16 = silu(gate) * up
+#define GI_SKINNY_ACCUM_DEFER 4 // gi_gemm_stream_bf16 only: as ACCUM_F32, but tiles cut between blocks leave their partial
+                                // sums in `scratch` for gi_rmsnorm / gi_settle to add (no exchange between blocks)
 int gi_gemm_skinny_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
                         long ldo, void* stream);
 
@@ -42,6 +56,10 @@ long gi_gemm_stream_scratch_floats(void);
 int gi_gemm_stream_bf16(void* out, int mode, const void* A, const void* W, float* scratch, int* counters, int n_counters,
                         int M, int N, int K, long lda, long ldw, long ldo, int use_pdl, void* stream);
 int gi_gemm_stream_status(int* status);
+int gi_gemm_stream_geometry(int M, int N, int K, int* n_ctas, int* kb_per_tile, int* nt);
+
+// x[rows, :] += the partial sums, in the order of the K ranges.  rows: optional selection; n_features = width of x.
+int gi_settle(float* x, gi_settle_t settle, const int* rows, int n_rows, int d, void* stream);
 
 // mode of gi_gemm_tc_bf16 (same meanings as the skinny product's)
 #define GI_TC_STORE_BF16 0

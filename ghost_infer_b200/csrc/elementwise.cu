@@ -18,17 +18,53 @@ __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ tab
   for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = gi::ldf(row + i);
 }
 
+// Sum of the partial sums a deferred product left for features f..f+3 of token m (see gemm_stream.cu: a tile of
+// 128 features whose K range was cut between blocks c_first..c_last has one slot per block; they are added in
+// the order of the K ranges, so the result does not depend on any timing).  f is a multiple of 4.
+__device__ __forceinline__ float4 pending_sum(const gi_settle_t& st, int m, int f) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int tile = f / 128, row = f % 128;
+  const int c_first = st.tile_first_cta[tile], c_last = st.tile_last_cta[tile];
+  if (c_first == c_last) return acc;                 // one block had the whole tile and added it itself
+  for (int c = c_first; c <= c_last; ++c) {
+    const int which = (tile == st.cta_first_tile[c]) ? 0 : 1;
+    const float4 p = __ldcg(reinterpret_cast<const float4*>(st.partials + ((size_t)c * 2 + which) * (128 * st.nt) + (size_t)m * 128 + row));
+    acc.x += p.x;
+    acc.y += p.y;
+    acc.z += p.z;
+    acc.w += p.w;
+  }
+  return acc;
+}
+
+// x[row, :] += pending partial sums (for readers of the residual stream that do not settle on their own).
+__global__ void settle_kernel(float* __restrict__ x, gi_settle_t st, const int* __restrict__ rows, int d) {
+  gi::pdl_prologue();
+  const int m = rows ? rows[blockIdx.x] : blockIdx.x;
+  float4* xr = reinterpret_cast<float4*>(x + (size_t)m * d);
+  for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+    float4 v = xr[i];
+    const float4 p = pending_sum(st, m, 4 * i);
+    v.x += p.x;
+    v.y += p.y;
+    v.z += p.z;
+    v.w += p.w;
+    xr[i] = v;
+  }
+}
+
 // y = x * (1 / sqrt(mean(x^2) + eps)) * w, one block per row (src/model.rs:919-928, src/cuda.rs:505-515).
 // `rows` (optional) picks which rows of x are normed; output row r is then x[rows[r]].
 // The row is read once, four floats at a time, and kept in registers (up to VEC float4 per thread);
 // wider rows, or rows that are no multiple of 4, take the plain loop.
-template <typename TO, typename TW, int VEC>
-__global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
-                               const int* __restrict__ rows, int d, float eps) {
+template <typename TO, typename TW, int VEC, bool SETTLE>
+__global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, const TW* __restrict__ w,
+                               const int* __restrict__ rows, int d, float eps, gi_settle_t st) {
   __shared__ float scratch[33];
   gi::pdl_prologue();
   const int r = blockIdx.x;
-  const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
+  const int m = rows ? rows[r] : r;
+  float* xr = x + (size_t)m * d;
   TO* o = out + (size_t)r * d;
   if (VEC > 0) {
     const int n4 = d / 4;
@@ -38,6 +74,14 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
     for (int j = 0; j < VEC; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
       v[j] = i < n4 ? reinterpret_cast<const float4*>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (SETTLE && i < n4) {
+        const float4 p = pending_sum(st, m, 4 * i);
+        v[j].x += p.x;
+        v[j].y += p.y;
+        v[j].z += p.z;
+        v[j].w += p.w;
+        reinterpret_cast<float4*>(xr)[i] = v[j];      // the settled row goes back to the residual stream
+      }
       ss = fmaf(v[j].x, v[j].x, ss);
       ss = fmaf(v[j].y, v[j].y, ss);
       ss = fmaf(v[j].z, v[j].z, ss);
@@ -92,24 +136,54 @@ extern "C" int gi_embed(float* out, const void* table, int table_dtype, const in
   return gi::check(e, "embed");
 }
 
-extern "C" int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows,
-                          int n_rows, int d, float eps, void* stream) {
+namespace {
+template <typename TO, typename TW>
+cudaError_t rmsnorm_launch(int per, bool settle, dim3 g, dim3 b, cudaStream_t s, TO* out, float* x, const TW* w, const int* rows, int d,
+                           float eps, gi_settle_t st) {
+  if (settle) {
+    if (per == 1) return gi::launch(rmsnorm_kernel<TO, TW, 1, true>, g, b, 0, s, out, x, w, rows, d, eps, st);
+    if (per == 2) return gi::launch(rmsnorm_kernel<TO, TW, 2, true>, g, b, 0, s, out, x, w, rows, d, eps, st);
+    return gi::launch(rmsnorm_kernel<TO, TW, 4, true>, g, b, 0, s, out, x, w, rows, d, eps, st);
+  }
+  if (per == 1) return gi::launch(rmsnorm_kernel<TO, TW, 1, false>, g, b, 0, s, out, x, w, rows, d, eps, st);
+  if (per == 2) return gi::launch(rmsnorm_kernel<TO, TW, 2, false>, g, b, 0, s, out, x, w, rows, d, eps, st);
+  if (per == 3 || per == 4) return gi::launch(rmsnorm_kernel<TO, TW, 4, false>, g, b, 0, s, out, x, w, rows, d, eps, st);
+  return gi::launch(rmsnorm_kernel<TO, TW, 0, false>, g, b, 0, s, out, x, w, rows, d, eps, st);
+}
+
+int rmsnorm_impl(void* out, int out_dtype, float* x, const void* w, int w_dtype, const int* rows, int n_rows, int d, float eps,
+                 gi_settle_t st, void* stream) {
   if (n_rows <= 0) return GI_OK;
   if (d <= 0) return gi::fail(GI_ERR_ARG, "rmsnorm: bad width %d", d);
-  const int threads = d >= 2048 ? 512 : 256;
+  const bool settle = st.partials != nullptr;
+  // a settling norm has several dependent loads per value: more threads, fewer values each
+  const int threads = settle ? (d >= 4096 ? 1024 : (d >= 2048 ? 512 : 256)) : (d >= 2048 ? 512 : 256);
   // the register path: rows that are a multiple of 4 wide, start on 16-byte boundaries, and fit 4 float4 per thread
   const bool vec = d % 4 == 0 && ((uintptr_t)x & 15) == 0 && d / 4 <= 4 * threads;
   const int per = vec ? (d / 4 + threads - 1) / threads : 0;
+  if (settle && per == 0) return gi::fail(GI_ERR_UNSUPPORTED, "rmsnorm: settling partial sums needs rows of a multiple of 4 and at most %d values", 16 * threads);
   cudaError_t e = cudaSuccess;
-  GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW, {
-    cudaStream_t s = (cudaStream_t)stream;
-    const dim3 g(n_rows), b(threads);
-    if (per == 1) e = gi::launch(rmsnorm_kernel<TO, TW, 1>, g, b, 0, s, (TO*)out, x, (const TW*)w, rows, d, eps);
-    else if (per == 2) e = gi::launch(rmsnorm_kernel<TO, TW, 2>, g, b, 0, s, (TO*)out, x, (const TW*)w, rows, d, eps);
-    else if (per == 3 || per == 4) e = gi::launch(rmsnorm_kernel<TO, TW, 4>, g, b, 0, s, (TO*)out, x, (const TW*)w, rows, d, eps);
-    else e = gi::launch(rmsnorm_kernel<TO, TW, 0>, g, b, 0, s, (TO*)out, x, (const TW*)w, rows, d, eps);
-  }));
+  GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW,
+      e = (rmsnorm_launch<TO, TW>(per, settle, dim3(n_rows), dim3(threads), (cudaStream_t)stream, (TO*)out, x, (const TW*)w, rows, d, eps, st))));
   return gi::check(e, "rmsnorm");
+}
+}  // namespace
+
+extern "C" int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows,
+                          int n_rows, int d, float eps, void* stream) {
+  gi_settle_t none = {nullptr, nullptr, nullptr, nullptr, 0};
+  return rmsnorm_impl(out, out_dtype, const_cast<float*>(x), w, w_dtype, rows, n_rows, d, eps, none, stream);
+}
+
+extern "C" int gi_rmsnorm_settle(void* out, int out_dtype, float* x, const void* w, int w_dtype, const int* rows,
+                                 int n_rows, int d, float eps, gi_settle_t settle, void* stream) {
+  return rmsnorm_impl(out, out_dtype, x, w, w_dtype, rows, n_rows, d, eps, settle, stream);
+}
+
+extern "C" int gi_settle(float* x, gi_settle_t settle, const int* rows, int n_rows, int d, void* stream) {
+  if (n_rows <= 0 || settle.partials == nullptr) return GI_OK;
+  if (d % 4 != 0 || ((uintptr_t)x & 15)) return gi::fail(GI_ERR_UNSUPPORTED, "settle: rows must be a multiple of 4 wide and 16-byte aligned");
+  return gi::check(gi::launch(settle_kernel, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, x, settle, rows, d), "settle");
 }
 
 extern "C" int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, int interleaved, void* stream) {

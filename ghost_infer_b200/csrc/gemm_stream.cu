@@ -201,7 +201,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
       const int f = tile * TILE_ROWS + row;
       bool finish = whole;
-      if (!whole) {
+      if (!whole && MODE == GI_SKINNY_ACCUM_DEFER) {
+        // leave the partial sums for the next reader of the residual stream (the norm that follows), which adds
+        // them in the order of the K ranges while it reads the row anyway: no exchange between blocks here
+        const int which = (tile == (int)(mine.first / kb_per_tile)) ? 0 : 1;
+        float* slot = scratch + ((size_t)blockIdx.x * 2 + which) * (TILE_ROWS * NT);
+#pragma unroll
+        for (int m = 0; m < NT; ++m) __stcg(slot + m * TILE_ROWS + row, v[m]);
+      } else if (!whole) {
         // a tile shared with other blocks: leave the partial sums, and see whether everyone else has left theirs
         const int c_first = cta_of(tile_first, n_ctas, units), c_last = cta_of(tile_end - 1, n_ctas, units);
         const int which = (tile == (int)(mine.first / kb_per_tile)) ? 0 : 1;
@@ -249,7 +256,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
           for (int m = 0; m < NT; ++m) {
             if (m >= M) break;
-            if (MODE == GI_SKINNY_ACCUM_F32) {
+            if (MODE == GI_SKINNY_ACCUM_F32 || MODE == GI_SKINNY_ACCUM_DEFER) {
               float* o = (float*)out_ + (size_t)m * ldo + f;
               *o += v[m];
             } else if (MODE == GI_SKINNY_STORE_F32) {
@@ -319,6 +326,7 @@ int launch_mode(int mode, void* out, const CUtensorMap& mw, const CUtensorMap& m
     case GI_SKINNY_STORE_F32: return launch<NT, STAGES, GI_SKINNY_STORE_F32>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
     case GI_SKINNY_ACCUM_F32: return launch<NT, STAGES, GI_SKINNY_ACCUM_F32>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
     case GI_SKINNY_SWIGLU: return launch<NT, STAGES, GI_SKINNY_SWIGLU>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
+    case GI_SKINNY_ACCUM_DEFER: return launch<NT, STAGES, GI_SKINNY_ACCUM_DEFER>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
   }
   return gi::fail(GI_ERR_ARG, "streamed product: unknown mode %d", mode);
 }
@@ -352,6 +360,16 @@ extern "C" int gi_gemm_stream_bf16(void* out, int mode, const void* A, const voi
   if (nt == 16) return launch_mode<16, 10>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
   if (nt == 32) return launch_mode<32, 9>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
   return launch_mode<64, 8>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
+}
+
+// How a launch with these sizes cuts its work: blocks, units per tile, token-tile width.  The kernel that settles
+// deferred partial sums (gi_rmsnorm with a settle descriptor, gi_settle) needs exactly these numbers.
+extern "C" int gi_gemm_stream_geometry(int M, int N, int K, int* n_ctas, int* kb_per_tile, int* nt) {
+  const long units = (long)((N + TILE_ROWS - 1) / TILE_ROWS) * ((K + BK - 1) / BK);
+  *n_ctas = (int)(units < sm_count() ? units : sm_count());
+  *kb_per_tile = (K + BK - 1) / BK;
+  *nt = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  return GI_OK;
 }
 
 extern "C" int gi_gemm_stream_status(int* status) {

@@ -186,9 +186,14 @@ class Engine:
         x = model.embedding.forward(ctx.tokens)
         for i, e in enumerate(model.spec.schedule):
             model.layers[e.layer].block.forward(x, ctx, self.cache.memory(i))
+        from ..kernels import ops
         if ctx.logit_rows is None:
+            ops.drop_pending(x)
             return None
+        if not getattr(model.final_norm, "settles_pending", False):
+            ops.settle(x)
         h = model.final_norm.forward(x, rows=ctx.logit_rows)
+        ops.drop_pending(x)
         return model.head.forward(h)
 
     def decode_splits_for(self, ctx: StepContext) -> int:

@@ -7,9 +7,10 @@ the CPU and nothing falls back to library code.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from ctypes import c_float, c_int, c_long, c_void_p
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 
@@ -19,6 +20,13 @@ F32, BF16 = 0, 1
 GEMM_STORE, GEMM_ACCUM_F32 = 0, 1
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class SettleT(ctypes.Structure):
+    """gi_settle_t: where a deferred product left its partial sums and how it had cut its work."""
+    _fields_ = [("partials", c_void_p), ("tile_first_cta", c_void_p), ("tile_last_cta", c_void_p),
+                ("cta_first_tile", c_void_p), ("nt", c_int)]
+
 
 _bound = None
 
@@ -32,6 +40,9 @@ def _bind():
     sigs = {
         "gi_embed": [P, P, I, P, I, I, I, P],
         "gi_rmsnorm": [P, I, P, P, I, P, I, I, F, P],
+        "gi_rmsnorm_settle": [P, I, P, P, I, P, I, I, F, SettleT, P],
+        "gi_settle": [P, SettleT, P, I, I, P],
+        "gi_gemm_stream_geometry": [I, I, I, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)],
         "gi_silu_mul": [P, P, I, I, I, I, P],
         "gi_gemm_skinny_bf16": [P, I, P, P, I, I, I, L, L, L, P],
         "gi_gemm_generic": [P, I, I, P, I, P, I, I, I, I, L, L, L, P],
@@ -125,9 +136,101 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     n = x.shape[0] if rows is None else rows.numel()
     if out is None:
         out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    pending = _pending.pop(x.data_ptr(), None)
+    if pending is not None:
+        # a deferred product left partial sums for this stream: add them while the rows are read anyway
+        _check(lib, lib.gi_rmsnorm_settle(out.data_ptr(), _dt(out, "rmsnorm output"), x.data_ptr(), weight.data_ptr(),
+                                          _dt(weight, "rmsnorm weight"), _i32(rows, "rows"), n, d, float(eps), pending,
+                                          _stream()))
+        return out
     _check(lib, lib.gi_rmsnorm(out.data_ptr(), _dt(out, "rmsnorm output"), x.data_ptr(), weight.data_ptr(),
                                _dt(weight, "rmsnorm weight"), _i32(rows, "rows"), n, d, float(eps), _stream()))
     return out
+
+
+# ---- deferred accumulation into the residual stream ---------------------------------------------------
+# The decode product cuts tiles of W between blocks; adding such a tile's partial sums into the residual
+# stream needs an exchange between blocks at the kernel's end.  When the stream's next reader is a norm, which
+# reads every row anyway, the product leaves the partial sums in scratch and the norm adds them (in a fixed
+# order).  `defer_into(x)` says that accumulations into x may be left pending; `settle(x)` adds what is pending.
+_pending: Dict[int, SettleT] = {}
+_pending_scratch: Dict[int, torch.Tensor] = {}
+_defer_target: Optional[int] = None
+
+
+@contextlib.contextmanager
+def defer_into(x: torch.Tensor):
+    """Inside, a product accumulated into `x` may leave partial sums pending.  The caller promises that the next
+    reader of `x` is `rmsnorm` (which settles them) or that it calls `settle(x)` first."""
+    global _defer_target
+    prev = _defer_target
+    _defer_target = x.data_ptr() if (TUNE["defer_residual"] and x.is_cuda) else None
+    try:
+        yield
+    finally:
+        _defer_target = prev
+
+
+def has_pending(x: torch.Tensor) -> bool:
+    return x.data_ptr() in _pending
+
+
+def settle(x: torch.Tensor) -> None:
+    """Adds pending partial sums (if any) to every row of the float32 matrix `x`."""
+    pending = _pending.pop(x.data_ptr(), None)
+    if pending is None:
+        return
+    lib = _bind()
+    _check(lib, lib.gi_settle(x.data_ptr(), pending, None, x.shape[0], x.shape[1], _stream()))
+
+
+def drop_pending(x: torch.Tensor) -> None:
+    """Forgets partial sums pending for `x` (the stream is not read again)."""
+    _pending.pop(x.data_ptr(), None)
+
+
+def _defer_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    return (_defer_target is not None and out.data_ptr() == _defer_target and out.dtype == torch.float32
+            and out.is_contiguous() and out.shape[1] % 4 == 0 and out.shape[1] <= 8192 and out.data_ptr() % 16 == 0
+            and out.data_ptr() not in _pending)
+
+
+def _gemm_stream_deferred(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    lib = _bind()
+    key = a.device.index if a.device.index is not None else torch.cuda.current_device()
+    if key not in _pending_scratch:
+        _pending_scratch[key] = torch.empty(int(lib.gi_gemm_stream_scratch_floats()), dtype=torch.float32, device=a.device)
+    scratch = _pending_scratch[key]
+    m, k = a.shape
+    n = w.shape[0]
+    _, counters = _stream_buffers(a.device)
+    _check(lib, lib.gi_gemm_stream_bf16(out.data_ptr(), SKINNY_ACCUM_DEFER, a.data_ptr(), w.data_ptr(), scratch.data_ptr(),
+                                        counters.data_ptr(), counters.numel(), m, n, k, a.stride(0), w.stride(0),
+                                        out.stride(0), -1, _stream()))
+    n_ctas, kb, nt = c_int(0), c_int(0), c_int(0)
+    lib.gi_gemm_stream_geometry(m, n, k, ctypes.byref(n_ctas), ctypes.byref(kb), ctypes.byref(nt))
+    tabs = _settle_tables(a.device, (n + 127) // 128, kb.value, n_ctas.value)
+    _pending[out.data_ptr()] = SettleT(scratch.data_ptr(), tabs[0].data_ptr(), tabs[1].data_ptr(), tabs[2].data_ptr(), nt.value)
+    return out
+
+
+_settle_tabs: Dict[tuple, tuple] = {}
+
+
+def _settle_tables(device: torch.device, n_tiles: int, kb_per_tile: int, n_ctas: int):
+    """Which blocks held pieces of which tile, as the streamed product cuts its work: block c takes the units
+    [c * U / G, (c + 1) * U / G) of the U = tiles x K-blocks units.  Built once per shape, kept on the device."""
+    key = (str(device), n_tiles, kb_per_tile, n_ctas)
+    if key not in _settle_tabs:
+        units = n_tiles * kb_per_tile
+        starts = [c * units // n_ctas for c in range(n_ctas + 1)]
+        import bisect
+        cta_of = lambda u: bisect.bisect_right(starts, u) - 1
+        first = [cta_of(t * kb_per_tile) for t in range(n_tiles)]
+        last = [cta_of((t + 1) * kb_per_tile - 1) for t in range(n_tiles)]
+        first_tile = [starts[c] // kb_per_tile for c in range(n_ctas)]
+        _settle_tabs[key] = tuple(torch.tensor(v, dtype=torch.int32, device=device) for v in (first, last, first_tile))
+    return _settle_tabs[key]
 
 
 def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
@@ -168,7 +271,7 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor
     return out
 
 
-SKINNY_STORE_BF16, SKINNY_STORE_F32, SKINNY_ACCUM_F32, SKINNY_SWIGLU = 0, 1, 2, 3
+SKINNY_STORE_BF16, SKINNY_STORE_F32, SKINNY_ACCUM_F32, SKINNY_SWIGLU, SKINNY_ACCUM_DEFER = 0, 1, 2, 3, 4
 SKINNY_MAX_ROWS = 64
 
 
@@ -206,7 +309,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 
 
 # Choices measured on a B200; benchmarks may override them to try alternatives.
-TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16}
+TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -283,6 +386,10 @@ def _decode_product(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[t
     default and `TUNE["small_skinny"]` switches the other choice on."""
     small = TUNE["small_skinny"] and a.shape[0] <= 8 and w.shape[0] * w.shape[1] * 2 < (64 << 20)
     if USE_STREAM and not small and (w.shape[0] + 127) // 128 <= _STREAM_COUNTERS:
+        if mode == SKINNY_ACCUM_F32:
+            if _defer_ok(a, w, out):
+                return _gemm_stream_deferred(a, w, out)
+            settle(out)          # something is pending for this stream already: add it before adding more
         return gemm_stream(a, w, mode, out)
     return gemm_skinny(a, w, mode, out)
 
@@ -502,6 +609,8 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
 def linear(h: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
     want = out.dtype if out is not None else (out_dtype or h.dtype)
+    if accumulate and out is not None and not (skinny_ok(h, w) and USE_STREAM):
+        settle(out)
     mode = SKINNY_ACCUM_F32 if accumulate else {torch.bfloat16: SKINNY_STORE_BF16, torch.float32: SKINNY_STORE_F32}.get(want)
     if mode is not None:
         if skinny_ok(h, w):

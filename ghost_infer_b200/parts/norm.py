@@ -16,6 +16,8 @@ from .registry import register
 
 @register("norm", "rmsnorm")
 class RmsNorm(Norm):
+    settles_pending = True      # its kernel adds partial sums a deferred product left for the rows it reads
+
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.size = int(params["size"])

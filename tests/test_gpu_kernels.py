@@ -451,3 +451,53 @@ def test_gemm_stream_swiglu(m, f, k):
     assert ops.gemm_stream_status() == 0
     assert out.shape == (m, f)
     torch.testing.assert_close(out.double(), ref, rtol=1e-2, atol=1e-3 * float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 40])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (4096, 14336), (512, 264), (2048, 128)])
+def test_deferred_accumulation_is_settled_by_the_norm(m, n, k):
+    """A decode product that adds into the residual stream may leave the partial sums of tiles cut between blocks
+    in scratch; the norm that reads the stream next adds them (and writes the settled rows back)."""
+    a, w = rnd(m, k, dtype=torch.bfloat16, seed=50), rnd(n, k, dtype=torch.bfloat16, seed=51, scale=0.05)
+    wn = (1 + 0.1 * rnd(n, seed=52)).to(torch.bfloat16)
+    x0 = rnd(m, n, seed=53)
+    want_x = x0.double() + a.double() @ w.double().T
+    want_h = want_x * torch.rsqrt((want_x ** 2).mean(-1, keepdim=True) + 1e-5) * wn.double()
+    # through the norm
+    x = x0.clone()
+    with ops.defer_into(x):
+        ops.linear(a, w, out=x, accumulate=True)
+    assert ops.has_pending(x)
+    h = ops.rmsnorm(x, wn, 1e-5, torch.bfloat16)
+    assert not ops.has_pending(x)
+    torch.testing.assert_close(x.double(), want_x, rtol=1e-5, atol=1e-4)
+    torch.testing.assert_close(h.double(), want_h, rtol=1.6e-2, atol=1.6e-2)
+    # selected rows only (the final norm): those rows are settled
+    x = x0.clone()
+    with ops.defer_into(x):
+        ops.linear(a, w, out=x, accumulate=True)
+    rows = torch.tensor([m - 1, 0], dtype=torch.int32, device=DEV)
+    h = ops.rmsnorm(x, wn, 1e-5, torch.float32, rows=rows)
+    torch.testing.assert_close(h.double(), want_h[rows.long()], rtol=1e-4, atol=1e-4)
+    # settled on its own, and twice the same bits
+    outs = []
+    for _ in range(2):
+        x = x0.clone()
+        with ops.defer_into(x):
+            ops.linear(a, w, out=x, accumulate=True)
+        ops.settle(x)
+        outs.append(x.clone())
+    torch.testing.assert_close(outs[0].double(), want_x, rtol=1e-5, atol=1e-4)
+    assert torch.equal(outs[0], outs[1])
+    # outside a deferring context nothing is left pending
+    x = x0.clone()
+    ops.linear(a, w, out=x, accumulate=True)
+    assert not ops.has_pending(x)
+    torch.testing.assert_close(x.double(), want_x, rtol=1e-5, atol=1e-4)
+    # a second accumulation while one is pending settles the first before it adds
+    x = x0.clone()
+    with ops.defer_into(x):
+        ops.linear(a, w, out=x, accumulate=True)
+        ops.linear(a, w, out=x, accumulate=True)
+    ops.settle(x)
+    torch.testing.assert_close(x.double(), x0.double() + 2 * (a.double() @ w.double().T), rtol=1e-5, atol=2e-4)
