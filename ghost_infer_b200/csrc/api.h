@@ -44,6 +44,7 @@ int gi_gemm_generic(void* out, int out_dtype, int mode, const void* A, int a_dty
 #define GI_SKINNY_STORE_F32 1
 #define GI_SKINNY_ACCUM_F32 2   // out (float) += product
 #define GI_SKINNY_SWIGLU 3      // W rows interleaved [8 gate | 8 up]; out[M, N/2] bfloat16 = silu(gate) * up
+#define GI_SKINNY_STORE_DEFER 5 // the same for STORE_BF16: whole tiles are stored, cut tiles stay as partial sums for gi_rope_cache_write
 #define GI_SKINNY_ACCUM_DEFER 4 // gi_gemm_stream_bf16 only: as ACCUM_F32, but tiles cut between blocks leave their partial
                                 // sums in `scratch` for gi_rmsnorm / gi_settle to add (no exchange between blocks)
 int gi_gemm_skinny_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
@@ -76,6 +77,12 @@ int gi_rope_table(float* table, const int* positions, const float* inv_freq, int
 int gi_rope_cache_write(void* qkv, int dtype, long ld, const float* table, const int* positions, const int* slots,
                         const int* block_table, int max_pages, void* kcache, void* vcache, int n_tokens, int n_heads,
                         int n_kv, int hd, int rot, int adjacent, int write_cache, void* stream);
+// The same for rows whose product was deferred (GI_SKINNY_STORE_DEFER): values of tiles that were cut between blocks
+// are the sums of the partial sums, rounded to the row's dtype as a stored value would have been.
+int gi_rope_cache_write_settle(void* qkv, int dtype, long ld, const float* table, const int* positions, const int* slots,
+                               const int* block_table, int max_pages, void* kcache, void* vcache, int n_tokens,
+                               int n_heads, int n_kv, int hd, int rot, int adjacent, int write_cache, gi_settle_t settle,
+                               void* stream);
 
 int gi_attn_prefill_generic(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
                             const void* vcache, const int* block_table, int max_pages, const int* cu_seqlens,

@@ -201,9 +201,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
       const int f = tile * TILE_ROWS + row;
       bool finish = whole;
-      if (!whole && MODE == GI_SKINNY_ACCUM_DEFER) {
-        // leave the partial sums for the next reader of the residual stream (the norm that follows), which adds
-        // them in the order of the K ranges while it reads the row anyway: no exchange between blocks here
+      if (!whole && (MODE == GI_SKINNY_ACCUM_DEFER || MODE == GI_SKINNY_STORE_DEFER)) {
+        // leave the partial sums for the next reader of the output (the norm after a residual add, the rotary
+        // kernel after the q/k/v product), which adds them in the order of the K ranges while it reads the row
+        // anyway: no exchange between blocks here
         const int which = (tile == (int)(mine.first / kb_per_tile)) ? 0 : 1;
         float* slot = scratch + ((size_t)blockIdx.x * 2 + which) * (TILE_ROWS * NT);
 #pragma unroll
@@ -327,6 +328,7 @@ int launch_mode(int mode, void* out, const CUtensorMap& mw, const CUtensorMap& m
     case GI_SKINNY_ACCUM_F32: return launch<NT, STAGES, GI_SKINNY_ACCUM_F32>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
     case GI_SKINNY_SWIGLU: return launch<NT, STAGES, GI_SKINNY_SWIGLU>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
     case GI_SKINNY_ACCUM_DEFER: return launch<NT, STAGES, GI_SKINNY_ACCUM_DEFER>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
+    case GI_SKINNY_STORE_DEFER: return launch<NT, STAGES, GI_SKINNY_STORE_DEFER>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
   }
   return gi::fail(GI_ERR_ARG, "streamed product: unknown mode %d", mode);
 }

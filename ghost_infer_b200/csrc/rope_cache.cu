@@ -24,25 +24,50 @@ __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restr
   table[idx] = make_float2(c, s);
 }
 
+// The value of column f of token t's packed row: what the product stored, or, for a tile of 128 columns that was cut
+// between blocks of a deferred product, the sum of the partial sums in the order of the K ranges, rounded to T.
+template <typename T>
+__device__ __forceinline__ float row_value(const T* row, const gi_settle_t& st, int t, int f) {
+  if (st.partials != nullptr) {
+    const int tile = f / 128, r = f % 128;
+    const int c_first = st.tile_first_cta[tile], c_last = st.tile_last_cta[tile];
+    if (c_first != c_last) {
+      float acc = 0.f;
+      for (int c = c_first; c <= c_last; ++c) {
+        const int which = (tile == st.cta_first_tile[c]) ? 0 : 1;
+        acc += __ldcg(st.partials + ((size_t)c * 2 + which) * (128 * st.nt) + (size_t)t * 128 + r);
+      }
+      T rounded;
+      gi::stf(&rounded, acc);
+      return gi::ldf(&rounded);
+    }
+  }
+  return gi::ldf(row + f);
+}
+
 // One block per (token, head of the packed row): heads 0..H-1 are queries (rotated in place), H..H+KV-1 keys
 // (rotated into the cache), H+KV.. values (copied into the cache).  A thread handles one pair or one value pair.
 template <typename T>
 __global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* __restrict__ table, const int* __restrict__ positions,
                                   const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int n_heads, int n_kv, int hd, int rot,
-                                  int adjacent, int write_cache) {
+                                  int adjacent, int write_cache, gi_settle_t st) {
   gi::pdl_prologue();
   const int t = blockIdx.x, head = blockIdx.y;
   const int half = rot / 2;
-  T* src = qkv + (size_t)t * ld + (size_t)head * hd;
+  T* row = qkv + (size_t)t * ld;
+  const int col0 = head * hd;
+  T* src = row + col0;
   if (head < n_heads) {
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
       const int ia = adjacent ? 2 * i : i, ib = adjacent ? 2 * i + 1 : i + half;
-      const float a = gi::ldf(src + ia), b = gi::ldf(src + ib);
+      const float a = row_value(row, st, t, col0 + ia), b = row_value(row, st, t, col0 + ib);
       const float2 f = table[(size_t)t * half + i];
       gi::stf(src + ia, a * f.x - b * f.y);
       gi::stf(src + ib, a * f.y + b * f.x);
     }
+    if (st.partials != nullptr)     // queries past the rotated part still have to land in the row the attention reads
+      for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) gi::stf(src + d, row_value(row, st, t, col0 + d));
     return;
   }
   if (!write_cache) return;
@@ -54,15 +79,15 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* __
     T* dst = kcache + (((size_t)page * n_kv + (head - n_heads)) * PAGE_TOKENS + off) * hd;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
       const int ia = adjacent ? 2 * i : i, ib = adjacent ? 2 * i + 1 : i + half;
-      const float a = gi::ldf(src + ia), b = gi::ldf(src + ib);
+      const float a = row_value(row, st, t, col0 + ia), b = row_value(row, st, t, col0 + ib);
       const float2 f = table[(size_t)t * half + i];
       gi::stf(dst + ia, a * f.x - b * f.y);
       gi::stf(dst + ib, a * f.y + b * f.x);
     }
-    for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) dst[d] = src[d];   // past the rotated part: as it is
+    for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) gi::stf(dst + d, row_value(row, st, t, col0 + d));   // past the rotated part: as it is
   } else {
     T* dst = vcache + (((size_t)page * n_kv + (head - n_heads - n_kv)) * PAGE_TOKENS + off) * hd;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = src[d];
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) gi::stf(dst + d, row_value(row, st, t, col0 + d));
   }
 }
 
@@ -75,14 +100,17 @@ extern "C" int gi_rope_table(float* table, const int* positions, const float* in
                               positions, inv_freq, half, total), "rope table");
 }
 
-extern "C" int gi_rope_cache_write(void* qkv, int dtype, long ld, const float* table, const int* positions, const int* slots,
-                                   const int* block_table, int max_pages, void* kcache, void* vcache, int n_tokens,
-                                   int n_heads, int n_kv, int hd, int rot, int adjacent, int write_cache, void* stream) {
+namespace {
+int rope_impl(void* qkv, int dtype, long ld, const float* table, const int* positions, const int* slots, const int* block_table,
+              int max_pages, void* kcache, void* vcache, int n_tokens, int n_heads, int n_kv, int hd, int rot, int adjacent,
+              int write_cache, gi_settle_t st, void* stream) {
   if (n_tokens <= 0) return GI_OK;
   if (hd <= 0 || rot < 0 || rot > hd || rot % 2 != 0)
     return gi::fail(GI_ERR_ARG, "rope: rotary size %d does not fit head size %d", rot, hd);
   if (write_cache && (!kcache || !vcache || !block_table)) return gi::fail(GI_ERR_ARG, "rope: cache write without a cache");
   if (rot > 0 && !table) return gi::fail(GI_ERR_ARG, "rope: no table of angles");
+  // with partial sums pending, the k and v blocks must run even without a cache write, so that nothing stays unsettled;
+  // they are only needed for the cache, though, so without a cache they are simply not launched
   const int heads = n_heads + (write_cache ? 2 * n_kv : 0);
   if (heads > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "rope: more than 65535 heads in one launch");
   dim3 grid(n_tokens, heads);
@@ -90,6 +118,23 @@ extern "C" int gi_rope_cache_write(void* qkv, int dtype, long ld, const float* t
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T,
       e = gi::launch(rope_cache_kernel<T>, grid, dim3(threads), 0, (cudaStream_t)stream, (T*)qkv, ld, (const float2*)table, positions,
-                     slots, block_table, max_pages, (T*)kcache, (T*)vcache, n_heads, n_kv, hd, rot, adjacent, write_cache));
+                     slots, block_table, max_pages, (T*)kcache, (T*)vcache, n_heads, n_kv, hd, rot, adjacent, write_cache, st));
   return gi::check(e, "rope_cache_write");
+}
+}  // namespace
+
+extern "C" int gi_rope_cache_write(void* qkv, int dtype, long ld, const float* table, const int* positions, const int* slots,
+                                   const int* block_table, int max_pages, void* kcache, void* vcache, int n_tokens,
+                                   int n_heads, int n_kv, int hd, int rot, int adjacent, int write_cache, void* stream) {
+  gi_settle_t none = {nullptr, nullptr, nullptr, nullptr, 0};
+  return rope_impl(qkv, dtype, ld, table, positions, slots, block_table, max_pages, kcache, vcache, n_tokens, n_heads, n_kv, hd, rot,
+                   adjacent, write_cache, none, stream);
+}
+
+extern "C" int gi_rope_cache_write_settle(void* qkv, int dtype, long ld, const float* table, const int* positions, const int* slots,
+                                          const int* block_table, int max_pages, void* kcache, void* vcache, int n_tokens,
+                                          int n_heads, int n_kv, int hd, int rot, int adjacent, int write_cache,
+                                          gi_settle_t settle, void* stream) {
+  return rope_impl(qkv, dtype, ld, table, positions, slots, block_table, max_pages, kcache, vcache, n_tokens, n_heads, n_kv, hd, rot,
+                   adjacent, write_cache, settle, stream);
 }

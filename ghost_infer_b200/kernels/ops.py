@@ -48,6 +48,7 @@ def _bind():
         "gi_gemm_generic": [P, I, I, P, I, P, I, I, I, I, L, L, L, P],
         "gi_rope_table": [P, P, P, I, I, P],
         "gi_rope_cache_write": [P, I, L, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P],
+        "gi_rope_cache_write_settle": [P, I, L, P, P, P, P, I, P, P, I, I, I, I, I, I, I, SettleT, P],
         "gi_attn_prefill_generic": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_gemm_stream_bf16": [P, I, P, P, P, P, I, I, I, I, L, L, L, I, P],
@@ -171,6 +172,22 @@ def defer_into(x: torch.Tensor):
         _defer_target = prev
 
 
+_defer_store = False
+
+
+@contextlib.contextmanager
+def defer_store():
+    """Inside, a decode product that stores bfloat16 rows may leave the tiles cut between blocks as partial sums.
+    The caller promises that the next reader of the rows is `rope_cache_write`, which adds them."""
+    global _defer_store
+    prev = _defer_store
+    _defer_store = bool(TUNE["defer_residual"])
+    try:
+        yield
+    finally:
+        _defer_store = prev
+
+
 def has_pending(x: torch.Tensor) -> bool:
     return x.data_ptr() in _pending
 
@@ -195,7 +212,7 @@ def _defer_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and out.data_ptr() not in _pending)
 
 
-def _gemm_stream_deferred(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def _gemm_stream_deferred(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = 4) -> torch.Tensor:
     lib = _bind()
     key = a.device.index if a.device.index is not None else torch.cuda.current_device()
     if key not in _pending_scratch:
@@ -204,7 +221,7 @@ def _gemm_stream_deferred(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -
     m, k = a.shape
     n = w.shape[0]
     _, counters = _stream_buffers(a.device)
-    _check(lib, lib.gi_gemm_stream_bf16(out.data_ptr(), SKINNY_ACCUM_DEFER, a.data_ptr(), w.data_ptr(), scratch.data_ptr(),
+    _check(lib, lib.gi_gemm_stream_bf16(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), scratch.data_ptr(),
                                         counters.data_ptr(), counters.numel(), m, n, k, a.stride(0), w.stride(0),
                                         out.stride(0), -1, _stream()))
     n_ctas, kb, nt = c_int(0), c_int(0), c_int(0)
@@ -271,7 +288,7 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor
     return out
 
 
-SKINNY_STORE_BF16, SKINNY_STORE_F32, SKINNY_ACCUM_F32, SKINNY_SWIGLU, SKINNY_ACCUM_DEFER = 0, 1, 2, 3, 4
+SKINNY_STORE_BF16, SKINNY_STORE_F32, SKINNY_ACCUM_F32, SKINNY_SWIGLU, SKINNY_ACCUM_DEFER, SKINNY_STORE_DEFER = 0, 1, 2, 3, 4, 5
 SKINNY_MAX_ROWS = 64
 
 
@@ -390,6 +407,9 @@ def _decode_product(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[t
             if _defer_ok(a, w, out):
                 return _gemm_stream_deferred(a, w, out)
             settle(out)          # something is pending for this stream already: add it before adding more
+        if mode == SKINNY_STORE_BF16 and _defer_store and out is None and w.shape[0] % 8 == 0:
+            out = torch.empty((a.shape[0], w.shape[0]), dtype=torch.bfloat16, device=a.device)
+            return _gemm_stream_deferred(a, w, out, SKINNY_STORE_DEFER)
         return gemm_stream(a, w, mode, out)
     return gemm_skinny(a, w, mode, out)
 
@@ -482,11 +502,15 @@ def rope_cache_write(qkv: torch.Tensor, table: Optional[torch.Tensor], positions
         if tuple(kcache.shape[1:]) != (n_kv, 64, head_dim) or not kcache.is_contiguous() or not vcache.is_contiguous():
             raise KernelError(f"cache pages must be contiguous [pages, {n_kv}, 64, {head_dim}], got {tuple(kcache.shape)}")
     max_pages = block_table.shape[1] if block_table is not None else 0
-    _check(lib, lib.gi_rope_cache_write(
-        qkv.data_ptr(), _dt(qkv, "q/k/v rows"), ld, table.data_ptr() if table is not None else None,
-        _i32(positions, "positions"), _i32(slots, "slots"), _i32(block_table, "block table"), max_pages,
-        kcache.data_ptr() if kcache is not None else None, vcache.data_ptr() if vcache is not None else None,
-        n, n_heads, n_kv, head_dim, rotary_dim, int(adjacent), int(write_cache), _stream()))
+    args = (qkv.data_ptr(), _dt(qkv, "q/k/v rows"), ld, table.data_ptr() if table is not None else None,
+            _i32(positions, "positions"), _i32(slots, "slots"), _i32(block_table, "block table"), max_pages,
+            kcache.data_ptr() if kcache is not None else None, vcache.data_ptr() if vcache is not None else None,
+            n, n_heads, n_kv, head_dim, rotary_dim, int(adjacent), int(write_cache))
+    pending = _pending.pop(qkv.data_ptr(), None)
+    if pending is not None:       # the product left partial sums instead of some of these rows' values
+        _check(lib, lib.gi_rope_cache_write_settle(*args, pending, _stream()))
+    else:
+        _check(lib, lib.gi_rope_cache_write(*args, _stream()))
 
 
 def attn_prefill_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,

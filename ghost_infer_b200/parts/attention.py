@@ -59,7 +59,13 @@ class GqaAttention(Mixer):
             self.position.bind(tensors, rt)
 
     def forward(self, h, residual, step, memory) -> None:
-        qkv = linear(h, self.w_qkv, out_dtype=self.rt.dtype)
+        # in a decode step the product may leave partial sums for the kernel that rotates and stores (it reads
+        # every value anyway); an encoding that does not go through that kernel gets plain rows
+        if self.position is None or getattr(self.position, "settles_pending", False):
+            with ops.defer_store():
+                qkv = linear(h, self.w_qkv, out_dtype=self.rt.dtype)
+        else:
+            qkv = linear(h, self.w_qkv, out_dtype=self.rt.dtype)
         if self.position is not None:
             self.position.encode_and_store(qkv, step, memory, self.n_heads, self.n_kv, self.head_dim)
         else:

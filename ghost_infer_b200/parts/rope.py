@@ -44,6 +44,8 @@ def rotary_inv_freq(rotary_dim: int, theta: float, scaling: Optional[Mapping]) -
 
 @register("position", "rotary")
 class Rotary(PositionEncoding):
+    settles_pending = True      # its kernel adds partial sums a deferred product left in place of row values
+
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.head_dim = int(params["head_dim"])

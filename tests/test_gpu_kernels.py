@@ -501,3 +501,37 @@ def test_deferred_accumulation_is_settled_by_the_norm(m, n, k):
         ops.linear(a, w, out=x, accumulate=True)
     ops.settle(x)
     torch.testing.assert_close(x.double(), x0.double() + 2 * (a.double() @ w.double().T), rtol=1e-5, atol=2e-4)
+
+
+@pytest.mark.parametrize("m", [1, 8, 20])
+@pytest.mark.parametrize("H,KV,hd,rot", [(32, 8, 128, 128), (6, 2, 64, 32), (5, 1, 48, 48)])
+def test_deferred_store_is_settled_by_the_rotary_kernel(m, H, KV, hd, rot):
+    """The q/k/v product of a decode step may leave partial sums instead of values; the kernel that rotates and
+    writes the cache adds them.  Bit for bit what the plain store followed by the same kernel gives."""
+    d = 264
+    n = (H + 2 * KV) * hd
+    a, w = rnd(m, d, dtype=torch.bfloat16, seed=60), rnd(n, d, dtype=torch.bfloat16, seed=61, scale=0.1)
+    positions = torch.arange(5, 5 + m, dtype=torch.int32, device=DEV)
+    slots = torch.zeros(m, dtype=torch.int32, device=DEV)
+    bt = torch.tensor([[2, 1]], dtype=torch.int32, device=DEV)
+    inv = torch.from_numpy(pl.rotary_inv_freq(rot, 10000.0, None)).to(DEV)
+    table = ops.rope_table(positions, inv)
+    outs = []
+    for defer in (False, True):
+        kc = torch.zeros(3, KV, 64, hd, dtype=torch.bfloat16, device=DEV)
+        vc = torch.zeros_like(kc)
+        if defer:
+            with ops.defer_store():
+                qkv = ops.linear(a, w, out_dtype=torch.bfloat16)
+            assert ops.has_pending(qkv)
+        else:
+            qkv = ops.linear(a, w, out_dtype=torch.bfloat16)
+            assert not ops.has_pending(qkv)
+        ops.rope_cache_write(qkv, table, positions, slots, bt, kc, vc, H, KV, hd, rot, False, True)
+        assert not ops.has_pending(qkv)
+        outs.append((qkv[:, :H * hd].clone(), kc, vc))
+    for x, y in zip(outs[0], outs[1]):
+        assert torch.equal(x, y)
+    ref_v = (a.double() @ w.double().T)[:, (H + KV) * hd:]
+    got_v = outs[1][2][2, :, 5:5 + m].transpose(0, 1).reshape(m, KV * hd).double()
+    torch.testing.assert_close(got_v, ref_v, rtol=1.6e-2, atol=1.6e-2)
