@@ -98,6 +98,13 @@ int gi_attn_prefill_tc(void* out, long ldo, const void* q, long ldq, const void*
                        const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots,
                        const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd, float scale,
                        int window, void* stream);
+// bfloat16, head size 128: the same on tcgen05 tensor cores (scores and output accumulate in tensor memory).
+// q_rows: rows of the packed q/k/v matrix; cache_pages: pages the cache tensors hold.
+int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, long q_rows, const void* kcache, const void* vcache,
+                       long cache_pages, const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots,
+                       const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd, float scale, int window,
+                       void* stream);
+int gi_attn_prefill_t5_status(int* status);
 // bfloat16, head size 64 or 128: the same operation as gi_attn_decode_generic, on tensor cores
 int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, const void* kcache,
                       const void* vcache, const int* block_table, int max_pages, const int* seq_slots,

@@ -1,0 +1,347 @@
+// Causal grouped-query attention of a step's prompt tokens over the paged cache on tcgen05 tensor cores
+// (bfloat16, head size 128).
+//
+// Formula: src/model.rs:1320-1419.  The reference's prompt attention (attention_prefill_tc, src/cuda.rs:2408-2613)
+// keeps scores in registers of mma.sync fragments; on sm_100a the same algorithm is laid out around tensor memory:
+// a block takes 128 queries of one head.  One thread issues TMA loads (queries once, then 64-key tiles of K and V
+// fetched page by page through the sequence's page table) and the tcgen05.mma instructions: S = Q K^T into tensor
+// memory, and O += P V with V read in its stored (dimension-contiguous) layout.  Four warps own one query row per
+// thread: they read a row of S with tcgen05.ld, keep the running maximum and sum in 32-bit (base-2 exponentials),
+// write the probabilities as bfloat16 into a swizzled shared-memory tile that the second product reads, and rescale
+// the accumulator in tensor memory when a row's maximum moves.  Two blocks share an SM, so one block's softmax
+// overlaps the other's products.  Every wait has an iteration limit and reports through a status word.
+#include <cuda.h>
+#include <math.h>
+
+#include "api.h"
+#include "common.cuh"
+#include "tc_utils.cuh"
+
+namespace {
+
+using namespace gi::tc;
+
+constexpr int HD = 128;
+constexpr int BQ = 128;          // queries per block = tensor-memory lanes
+constexpr int BKV = 64;          // keys per tile = one page
+constexpr int THREADS = 160;     // warps 0-3: one query row per thread; warp 4: TMA and MMA issue
+constexpr int TMEM_COLS = 256;   // S: columns 0..63, O: columns 64..191
+constexpr uint32_t Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2, P_BYTES = BQ * BKV * 2;
+
+__device__ int g_attn_status = 0;
+
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Descriptor of an operand whose rows (the M or N side) are contiguous along that side ("MN-major"), stored as
+// 64-element-wide, 128-byte-swizzled blocks: 8 rows of K are 1024 bytes apart (SBO), the next 64-wide block of the
+// M/N side is `lbo_bytes` away.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t lbo_bytes) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
+attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, long ldo,
+                       const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_seqlens,
+                       const int* __restrict__ seq_slots, const int* __restrict__ seq_pos0, int n_heads, int n_kv, float scale,
+                       int window, int q_tiles) {
+  // instruction descriptors: float accumulator, bfloat16 operands, M 128; S = Q K^T has N 64 and both operands K-major,
+  // O = P V has N 128 and B (V) MN-major (bit 16)
+  constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+  constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+  // Two blocks must fit one SM (2 x 113 KB), which leaves no room for alignment slack: the tiles need 1024-byte
+  // alignment, the dynamic shared memory of a kernel without static shared memory starts on such a boundary, and
+  // the block checks that before it does anything.
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* q_s = smem;                              // [2 halves][128 rows][64 dims]
+  unsigned char* k_s = q_s + Q_BYTES;                     // [2 stages][2 halves][64 keys][64 dims]
+  unsigned char* v_s = k_s + 2 * KV_BYTES;                // the same
+  unsigned char* p_s = v_s + 2 * KV_BYTES;                // [128 rows][64 keys]
+  uint64_t* bars = (uint64_t*)(p_s + P_BYTES);            // q_full, k_full[2], v_full[2], kv_empty[2], s_full, s_free, p_full, o_full
+  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
+  const int q0 = (q_tiles - 1 - (int)blockIdx.x) * BQ;     // latest tiles first: they have the most keys to visit
+  if (q0 >= qlen) return;
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(&g_attn_status, 0, 9);
+    return;
+  }
+  const int slot = seq_slots[b], pos0 = seq_pos0[b];
+  const int kvh = h / (n_heads / n_kv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_here = min(BQ, qlen - q0);
+  const int p_last = pos0 + q0 + rows_here - 1;
+  int t_first = 0;
+  if (window > 0) t_first = max(0, pos0 + q0 - window + 1);
+  const int kt_begin = (t_first / BKV) * BKV;
+  const int n_tiles = (p_last - kt_begin) / BKV + 1;
+
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = bar0 + 24, kv_empty0 = bar0 + 40;
+  const uint32_t s_full = bar0 + 56, s_free = bar0 + 64, p_full = bar0 + 72, o_full = bar0 + 80;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full0 + 8 * s, 1);
+      mbar_init(v_full0 + 8 * s, 1);
+      mbar_init(kv_empty0 + 8 * s, 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 4);
+    mbar_init(p_full, 4);
+    mbar_init(o_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      bool ok = true;
+      auto load_kv = [&](int tile) {
+        const int s = tile & 1;
+        const int kt = kt_begin + tile * BKV;
+        const int page = block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS];
+        const int row0 = (page * n_kv + kvh) * PAGE_TOKENS;
+        mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
+        tma_load_2d(smem_u32(k_s + s * KV_BYTES), &map_k, 0, row0, k_full0 + 8 * s);
+        tma_load_2d(smem_u32(k_s + s * KV_BYTES + KV_BYTES / 2), &map_k, 64, row0, k_full0 + 8 * s);
+        mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
+        tma_load_2d(smem_u32(v_s + s * KV_BYTES), &map_v, 0, row0, v_full0 + 8 * s);
+        tma_load_2d(smem_u32(v_s + s * KV_BYTES + KV_BYTES / 2), &map_v, 64, row0, v_full0 + 8 * s);
+      };
+      mbar_expect_tx(q_full, Q_BYTES);
+      tma_load_2d(smem_u32(q_s), &map_q, h * HD, tok0 + q0, q_full);
+      tma_load_2d(smem_u32(q_s + Q_BYTES / 2), &map_q, h * HD + 64, tok0 + q0, q_full);
+      load_kv(0);
+      ok = mbar_wait(q_full, 0, 1, &g_attn_status);
+      // S = Q K^T of tile j into tensor memory (the keys are here; the rows of the previous S have been read)
+      auto scores = [&](int j) -> bool {
+        const int s = j & 1;
+        bool good = mbar_wait(k_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 2, &g_attn_status);
+        if (good && j >= 1) good = mbar_wait(s_free, (uint32_t)((j - 1) & 1), 2, &g_attn_status);
+        if (!good) return false;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + s * KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t dq = smem_desc(qa + (ks / 4) * (Q_BYTES / 2) + (ks % 4) * 32);
+          const uint64_t dk = smem_desc(ka + (ks / 4) * (KV_BYTES / 2) + (ks % 4) * 32);
+          tc_mma(tmem_s, dq, dk, IDESC_S, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(s_full);
+        return true;
+      };
+      if (ok) ok = scores(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
+        if (j + 1 < n_tiles) {
+          // the other stage was last used by tile j - 1, whose second product frees it
+          if (j >= 1) ok = mbar_wait(kv_empty0 + 8 * (s ^ 1), (uint32_t)(((j - 1) >> 1) & 1), 1, &g_attn_status);
+          if (!ok) break;
+          load_kv(j + 1);
+          // the next tile's scores are computed while the rows of this tile turn their scores into probabilities
+          ok = scores(j + 1);
+          if (!ok) break;
+        }
+        // O += P V once the probabilities are staged (which also says: O has been rescaled) and the values are here
+        ok = mbar_wait(p_full, (uint32_t)(j & 1), 2, &g_attn_status);
+        if (ok) ok = mbar_wait(v_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 2, &g_attn_status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + s * KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+          const uint64_t dp = smem_desc(pa + kk * 32);
+          const uint64_t dv = smem_desc_mn(va + kk * 2048, KV_BYTES / 2);
+          tc_mma(tmem_o, dp, dv, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(kv_empty0 + 8 * s);
+        tc_commit(o_full);
+      }
+    }
+  } else {
+    const int row = warp * 32 + lane;                 // query row = tensor-memory lane
+    const int p_row = pos0 + q0 + row;                // its position
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const float sl2 = scale * 1.4426950408889634f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j & 1;
+      const int kt = kt_begin + j * BKV;
+      ok = mbar_wait(s_full, (uint32_t)(j & 1), 3, &g_attn_status);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr[2][32];
+      tc_ld32(tmem_s + lane_base, sr[0]);
+      tc_ld32(tmem_s + lane_base + 32, sr[1]);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
+      // scores -> probabilities
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int key = kt + q * 32 + c;
+          const bool vis = key <= p_row && key >= t_first && (window <= 0 || key > p_row - window);
+          const float v = vis ? __uint_as_float(sr[q][c]) * sl2 : -INFINITY;
+          sr[q][c] = __float_as_uint(v);
+          tmax = fmaxf(tmax, v);
+        }
+      const float m_new = fmaxf(m_run, tmax);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+      m_run = m_new;
+      float psum = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const float p0 = exp2f(__uint_as_float(sr[q][c]) - m_use), p1 = exp2f(__uint_as_float(sr[q][c + 1]) - m_use);
+          psum += p0 + p1;
+          __nv_bfloat162 pv = __floats2bfloat162_rn(p0, p1);
+          pk[q * 16 + c / 2] = *reinterpret_cast<uint32_t*>(&pv);
+        }
+      l_run = l_run * alpha + psum;
+      if (j > 0) {
+        // the previous second product is done: O may be rescaled and the probability tile rewritten
+        ok = mbar_wait(o_full, (uint32_t)((j - 1) & 1), 3, &g_attn_status);
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t orow[32];
+            tc_ld32(tmem_o + lane_base + c * 32, orow);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * alpha);
+            tc_st32(tmem_o + lane_base + c * 32, orow);
+          }
+          tc_wait_st();
+        }
+      }
+      // the row of probabilities: 64 bfloat16 = eight 16-byte chunks, swizzled like a TMA tile
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(p_s + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      // keys of this tile that no row of the block may see (past the block's last position, or before every window)
+      // get zero values: their probabilities are zero, but zero times a stale non-number would still be a non-number
+      const int lo = max(0, t_first - kt), hi = min(BKV, p_last + 1 - kt);
+      if (lo > 0 || hi < BKV) {
+        ok = mbar_wait(v_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 3, &g_attn_status);
+        if (!ok) break;
+        unsigned char* vt = v_s + s * KV_BYTES;
+        for (int idx = threadIdx.x; idx < BKV * 16; idx += 128) {
+          const int r = idx / 16, cidx = idx % 16;        // key row, 16-byte chunk among the row's 256 bytes (two halves)
+          if (r < lo || r >= hi) *reinterpret_cast<uint4*>(vt + (cidx / 8) * (KV_BYTES / 2) + r * 128 + (cidx % 8) * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok) ok = mbar_wait(o_full, (uint32_t)((n_tiles - 1) & 1), 3, &g_attn_status);
+    tc_fence_after();
+    if (ok) {
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      __nv_bfloat16* orow_g = out + (size_t)(tok0 + q0 + row) * ldo + (size_t)h * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t orow[32];
+        tc_ld32(tmem_o + lane_base + c * 32, orow);
+        tc_wait_ld();
+        if (row < rows_here) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint32_t pkd[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(orow[e + 2 * u]) * inv, __uint_as_float(orow[e + 2 * u + 1]) * inv);
+              pkd[u] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+            *reinterpret_cast<uint4*>(orow_g + c * 32 + e) = make_uint4(pkd[0], pkd[1], pkd[2], pkd[3]);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace
+
+extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, long q_rows, const void* kcache,
+                                  const void* vcache, long cache_pages, const int* block_table, int max_pages,
+                                  const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
+                                  int max_q_len, int n_heads, int n_kv, int hd, float scale, int window, void* stream) {
+  if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
+  if (hd != HD) return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tcgen05): head size %d, only 128", hd);
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
+    return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
+  if (ldq % 8 != 0 || ldo % 8 != 0 || (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)out) & 15))
+    return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tcgen05): rows must be 16-byte aligned");
+  if (n_seqs > 65535 || n_heads > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "attention: more than 65535 sequences or heads in one launch");
+  CUtensorMap mq, mk, mv;
+  int rc = gi::tensor_map_2d_ex(&mq, q, q_rows, (long)(n_heads + 2 * n_kv) * hd, ldq, GI_BF16, 64, BQ);
+  if (rc != GI_OK) return rc;
+  const long cache_rows = cache_pages * n_kv * PAGE_TOKENS;
+  rc = gi::tensor_map_2d_ex(&mk, kcache, cache_rows, hd, hd, GI_BF16, 64, BKV);
+  if (rc != GI_OK) return rc;
+  rc = gi::tensor_map_2d_ex(&mv, vcache, cache_rows, hd, hd, GI_BF16, 64, BKV);
+  if (rc != GI_OK) return rc;
+  constexpr size_t smem = Q_BYTES + 4 * KV_BYTES + P_BYTES + 12 * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention prefill (tcgen05): %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int q_tiles = (max_q_len + BQ - 1) / BQ;
+  dim3 grid(q_tiles, n_heads, n_seqs);
+  attn_prefill_t5_kernel<<<grid, THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages,
+                                                                        cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window,
+                                                                        q_tiles);
+  return gi::check_launch("attention prefill (tcgen05)");
+}
+
+extern "C" int gi_attn_prefill_t5_status(int* status) {
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(status, g_attn_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int));
+  if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention prefill status: %s", cudaGetErrorString(e));
+  return GI_OK;
+}

@@ -3,7 +3,8 @@
     python -m ghost_infer_b200.kernels.microbench --kernel gemm_stream --m 8 --n 28672 --k 4096
     python -m ghost_infer_b200.kernels.microbench --kernel attn_decode --batch 8 --context 2048
 
-Kernels: gemm_stream, gemm_skinny (decode products), gemm_tc (prefill product), attn_decode, attn_prefill,
+Kernels: gemm_stream, gemm_skinny (decode products), gemm_tc (prefill product), attn_decode, attn_prefill (mma.sync),
+attn_prefill_t5 (tcgen05),
 rmsnorm, rope, sample.  Operands rotate through enough different buffers to exceed the L2 cache, so a bytes
 figure is a DRAM figure.  The same command under `ncu -k regex:<kernel> -c 3` profiles exactly these launches.
 The reference times whole runs only (`bench`, src/main.rs:1241-1285) and, per operation, wall-clock buckets
@@ -81,7 +82,7 @@ def main() -> int:
         out.update(shape=[M, N, K], mode=args.mode, us=round(us, 2), tflops=round(flops / us / 1e6, 1),
                    gbs=round(nbytes / us / 1e3, 1), frac_hbm=round(nbytes / us / 1e3 / hbm, 3),
                    frac_tensor=round(flops / us / 1e6 / tflops, 3))
-    elif args.kernel in ("attn_decode", "attn_prefill"):
+    elif args.kernel in ("attn_decode", "attn_prefill", "attn_prefill_t5"):
         B, S, H, KV, hd = args.batch, args.context, args.heads, args.kv_heads, args.head_dim
         pages_per = (S + 63) // 64
         n_sets = max(2, L2_BYTES * 2 // (B * pages_per * KV * 64 * hd * 2 * 2) + 1) if args.kernel == "attn_decode" else 1
@@ -107,7 +108,8 @@ def main() -> int:
             cu = (torch.arange(B + 1, dtype=torch.int32, device=dev) * S)
             pos0 = torch.zeros(B, dtype=torch.int32, device=dev)
             o = torch.empty(B * S, H * hd, device=dev, dtype=bf)
-            us = _time(lambda i: ops.attn_prefill_tc(q, kc, vc, tables[0], cu, slots, pos0, B, S, H, KV, hd, scale, None, o),
+            fn = ops.attn_prefill_t5 if args.kernel == "attn_prefill_t5" else ops.attn_prefill_tc
+            us = _time(lambda i: fn(q, kc, vc, tables[0], cu, slots, pos0, B, S, H, KV, hd, scale, None, o),
                        1, args.iters, args.warmup)
             flops = 2.0 * B * H * hd * S * (S + 1)
             out.update(shape=[B, S, H, KV, hd], us=round(us, 2), tflops=round(flops / us / 1e6, 1),

@@ -56,6 +56,8 @@ def _bind():
         "gi_gemm_tc_bf16": [P, I, P, P, I, I, I, L, L, L, I, P],
         "gi_gemm_tc_status": [P],
         "gi_attn_prefill_tc": [P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
+        "gi_attn_prefill_t5": [P, L, P, L, L, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, P],
+        "gi_attn_prefill_t5_status": [P],
         "gi_attn_decode_tc": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_attn_decode_tc_ex": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
@@ -326,7 +328,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 
 
 # Choices measured on a B200; benchmarks may override them to try alternatives.
-TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True}
+TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -573,6 +575,34 @@ def attn_prefill_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
     return out
 
 
+def attn_prefill_t5(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                    cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
+                    max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                    window: Optional[int], out: torch.Tensor) -> torch.Tensor:
+    """As attn_prefill_generic, for bfloat16 and head size 128, on tcgen05 tensor cores with TMA-fed operands.
+    `q` is the whole packed [tokens, (H + 2 KV) * head_dim] matrix (its first columns are the queries)."""
+    lib = _bind()
+    _cuda(q, "queries")
+    ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the tcgen05 prefill attention takes bfloat16 queries, cache and output")
+    if not kcache.is_contiguous() or not vcache.is_contiguous() or q.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError("the tcgen05 prefill attention takes the packed q/k/v rows and contiguous cache pages")
+    _check(lib, lib.gi_attn_prefill_t5(
+        out.data_ptr(), ldo, q.data_ptr(), ldq, q.shape[0], kcache.data_ptr(), vcache.data_ptr(), kcache.shape[0],
+        _i32(block_table, "block table"), block_table.shape[1], _i32(cu_seqlens, "cu_seqlens"),
+        _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"), n_seqs, max_q_len, n_heads, n_kv, head_dim,
+        float(scale), int(window or 0), _stream()))
+    return out
+
+
+def attn_prefill_t5_status() -> int:
+    lib = _bind()
+    status = ctypes.c_int(0)
+    _check(lib, lib.gi_attn_prefill_t5_status(ctypes.byref(status)), 0)
+    return status.value
+
+
 def attn_decode_tc_ok(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:
     """Whether the tensor-core decode attention takes these operands: bfloat16, head size 64 or 128, 16-byte rows."""
     return (q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and head_dim in (64, 128)
@@ -672,6 +702,12 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
         kernel = attn_decode_tc if fast else attn_decode_generic
         return kernel(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
                       step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
-    kernel = attn_prefill_tc if attn_decode_tc_ok(qkv, memory.k, head_dim) and out.stride(0) % 2 == 0 else attn_prefill_generic
+    if attn_decode_tc_ok(qkv, memory.k, head_dim) and out.stride(0) % 2 == 0:
+        # head size 128: tcgen05 (scores and output in tensor memory); 64: mma.sync
+        t5 = (TUNE["attn_prefill_tcgen05"] and head_dim == 128 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+              and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim and memory.k.is_contiguous())
+        kernel = attn_prefill_t5 if t5 else attn_prefill_tc
+    else:
+        kernel = attn_prefill_generic
     return kernel(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots,
                   step.seq_pos0, step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out)

@@ -535,3 +535,28 @@ def test_deferred_store_is_settled_by_the_rotary_kernel(m, H, KV, hd, rot):
     ref_v = (a.double() @ w.double().T)[:, (H + KV) * hd:]
     got_v = outs[1][2][2, :, 5:5 + m].transpose(0, 1).reshape(m, KV * hd).double()
     torch.testing.assert_close(got_v, ref_v, rtol=1.6e-2, atol=1.6e-2)
+
+
+@pytest.mark.parametrize("H,KV", [(4, 2), (32, 8), (3, 1)])
+@pytest.mark.parametrize("window", [None, 37, 100])
+def test_attention_prefill_tcgen05(H, KV, window):
+    """The tcgen05 prefill kernel (head size 128): ragged lengths around its 128-row and 64-key tiles, sequences
+    that go on after cached positions, pages in shuffled order, unowned rows poisoned with NaN."""
+    hd = 128
+    lens_q, pos0 = [1, 45, 128, 129, 300, 33, 130], [0, 0, 0, 0, 0, 70, 200]
+    B, S = len(lens_q), 384
+    k = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=10)
+    v = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=11)
+    q = rnd(B, max(lens_q), (H + 2 * KV) * hd, dtype=torch.bfloat16, seed=12)
+    lens_kv = [p + n for p, n in zip(pos0, lens_q)]
+    kc, vc, bt = paged_from_dense(k, v, lens_kv, seed=3)
+    flat = torch.cat([q[b, :lens_q[b]] for b in range(B)])
+    cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    out = torch.full((flat.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attn_prefill_t5(flat, kc, vc, bt, cu, slots, torch.tensor(pos0, dtype=torch.int32, device=DEV), B,
+                        max(lens_q), H, KV, hd, 0.21, window, out)
+    assert ops.attn_prefill_t5_status() == 0
+    ref = attention_ref(q[:, :, :H * hd], k, v, lens_q, pos0, H, KV, hd, 0.21, window)
+    ref = torch.cat([ref[b, :lens_q[b]] for b in range(B)])
+    torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
