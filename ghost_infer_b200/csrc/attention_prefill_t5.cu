@@ -115,6 +115,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
+  gi::pdl_prologue();      // set-up overlapped the previous kernel's end; its results are visible from here on
 
   if (warp == 4) {
     if (lane == 0) {
@@ -332,10 +333,9 @@ extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, 
   }
   const int q_tiles = (max_q_len + BQ - 1) / BQ;
   dim3 grid(q_tiles, n_heads, n_seqs);
-  attn_prefill_t5_kernel<<<grid, THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages,
-                                                                        cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window,
-                                                                        q_tiles);
-  return gi::check_launch("attention prefill (tcgen05)");
+  return gi::check(gi::launch(attn_prefill_t5_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo,
+                              block_table, max_pages, cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles),
+                   "attention prefill (tcgen05)");
 }
 
 extern "C" int gi_attn_prefill_t5_status(int* status) {

@@ -80,6 +80,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  gi::pdl_prologue();      // set-up overlapped the previous kernel's end; its results are visible from here on
 
   // Tiles in an order that keeps a tile of W in use by neighbouring blocks: the row tile runs fastest.
   if (warp == 0) {
@@ -290,8 +291,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, 
   }
   const long tiles = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, THREADS, smem, s>>>(ma, mw, mo, M, N, K);
-  return gi::check_launch("tensor-core product");
+  return gi::check(gi::launch(kern, dim3(grid), dim3(THREADS), smem, s, ma, mw, mo, M, N, K), "tensor-core product");
 }
 
 template <int BN, int STAGES>

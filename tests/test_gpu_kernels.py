@@ -560,3 +560,40 @@ def test_attention_prefill_tcgen05(H, KV, window):
     ref = attention_ref(q[:, :, :H * hd], k, v, lens_q, pos0, H, KV, hd, 0.21, window)
     ref = torch.cat([ref[b, :lens_q[b]] for b in range(B)])
     torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
+
+
+def test_prefill_kernels_chain_under_dependent_launch():
+    """Norm, product, rotary + cache write, tcgen05 attention and an accumulating product in a row, with and without
+    programmatic dependent launch: each kernel may start while its predecessor drains, the bits must not move."""
+    H, KV, hd, d, T = 4, 2, 128, 256, 300
+    x0 = rnd(T, d, seed=70)
+    wn = (1 + 0.1 * rnd(d, seed=71)).to(torch.bfloat16)
+    wqkv = rnd((H + 2 * KV) * hd, d, dtype=torch.bfloat16, seed=72, scale=0.1)
+    wo = rnd(d, H * hd, dtype=torch.bfloat16, seed=73, scale=0.1)
+    positions = torch.arange(T, dtype=torch.int32, device=DEV)
+    slots = torch.zeros(T, dtype=torch.int32, device=DEV)
+    bt = torch.arange(1, 6, dtype=torch.int32, device=DEV).reshape(1, 5)
+    inv = torch.from_numpy(pl.rotary_inv_freq(hd, 10000.0, None)).to(DEV)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    zero = torch.zeros(1, dtype=torch.int32, device=DEV)
+    outs = []
+    for pdl in (False, True, True):
+        ops.set_pdl(pdl)
+        try:
+            x = x0.clone()
+            kc = torch.zeros(6, KV, 64, hd, dtype=torch.bfloat16, device=DEV)
+            vc = torch.zeros_like(kc)
+            h = ops.rmsnorm(x, wn, 1e-5, torch.bfloat16)
+            qkv = ops.linear(h, wqkv, out_dtype=torch.bfloat16)
+            table = ops.rope_table(positions, inv)
+            ops.rope_cache_write(qkv, table, positions, slots, bt, kc, vc, H, KV, hd, hd, False, True)
+            att = torch.empty(T, H * hd, dtype=torch.bfloat16, device=DEV)
+            ops.attn_prefill_t5(qkv, kc, vc, bt, cu, zero, zero, 1, T, H, KV, hd, hd ** -0.5, None, att)
+            ops.linear(att, wo, out=x, accumulate=True)
+            torch.cuda.synchronize()
+            outs.append(x.clone())
+        finally:
+            ops.set_pdl(False)
+    assert ops.gemm_tc_status() == 0 and ops.attn_prefill_t5_status() == 0
+    assert torch.isfinite(outs[0]).all() and float((outs[0] - x0).abs().max()) > 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
