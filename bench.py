@@ -30,6 +30,55 @@ CONTEXT = 8192
 PROMPT = 2048
 
 
+def _llama32(hidden, layers, heads, inter):
+    return {
+        "architectures": ["LlamaForCausalLM"], "hidden_size": hidden, "num_hidden_layers": layers, "num_attention_heads": heads,
+        "num_key_value_heads": 8, "head_dim": hidden // heads, "intermediate_size": inter, "vocab_size": 128256,
+        "max_position_embeddings": 131072, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 8192},
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    }
+
+
+# The other two workloads of the baseline: not the headline, run with --workload 1b / 3b.
+WORKLOADS = {
+    "1b": dict(config=_llama32(2048, 16, 32, 8192), batch=64, prompt=(128, 2048), new=256, step_tokens=None,
+               name="Llama-3.2-1B shape, batch 64, prompts uniform in [128, 2048], 256 decode steps"),
+    "3b": dict(config=_llama32(3072, 28, 24, 8192), batch=8, prompt=(16384, 16384), new=512, step_tokens=32768,
+               name="Llama-3.2-3B shape, batch 8, 16,384-token prompts, 512 decode steps"),
+}
+
+
+def run_workload(key, args):
+    """One of the other baseline workloads, end to end through the Python entry point; one JSON line."""
+    import numpy as np
+    import torch
+    import ghost_infer_b200 as gi
+    from ghost_infer_b200.kernels import ops
+    w = WORKLOADS[key]
+    ops.set_pdl(not args.no_pdl)
+    rng = np.random.default_rng(0)
+    lo, hi = w["prompt"]
+    lens = rng.integers(lo, hi + 1, size=w["batch"]).tolist()
+    prompts = [rng.integers(0, 128256, size=n).tolist() for n in lens]
+    max_tokens = sum(((n + w["new"] + 63) // 64) * 64 for n in lens) + 64 * w["batch"]
+    llm = gi.LLM(w["config"], dtype="bfloat16", device="cuda:0", max_tokens=max_tokens, max_slots=w["batch"],
+                 max_seq_len=hi + w["new"] + 64, seed=0)
+    new = w["new"] if args.steps == 64 else max(2, args.steps)
+    llm.generate(prompts[:2], max_new=2, temperature=0.0, stop_token_ids=(), batch_size=w["batch"])      # warm-up
+    torch.cuda.synchronize()
+    llm.generate(prompts, max_new=new, temperature=0.0, stop_token_ids=(), batch_size=w["batch"], max_step_tokens=w["step_tokens"])
+    st = llm.last_stats
+    print(json.dumps({
+        "metric": f"{w['name']}: decode tok/s through LLM.generate", "value": round(st.gen_tokens / st.gen_secs, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": new, "dtype": "bf16", "impl": "ours", "data": "synthetic",
+        "prefill": {"value": round(st.prompt_tokens / st.prompt_secs, 1), "tokens": st.prompt_tokens, "ms": round(st.prompt_secs * 1e3, 1)},
+        "config": {"model": w["name"], "global_batch": w["batch"], "prompt_min": lo, "prompt_max": hi, "new_tokens": new},
+    }))
+    return 0
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -88,6 +137,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (recorded in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b"], help="8b: the headline; 1b, 3b: the baseline's other workloads")
     ap.add_argument("--tune", default="", help="overrides of kernel choices, e.g. small_skinny=0,attn_waves=2")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another (no programmatic dependent launch)")
     args = ap.parse_args()
@@ -99,6 +149,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload != "8b":
+        return run_workload(args.workload, args)
     W = max(3, args.warmup)
     K = max(1, args.steps)
 

@@ -208,6 +208,21 @@ class SequenceCache:
                 g.table_host[slot, first:dead_before] = 0    # never read again: the device copy may keep them
                 g.first_live[slot] = dead_before
 
+    def reset(self, slot: int) -> None:
+        """The slot starts over: no tokens, pages given back, fixed-size state zero (src/model.rs:772-777)."""
+        if not self.slots.live(slot):
+            raise RuntimeError(f"slot {slot} is not open")
+        for g in self._groups:
+            held = [p for p in g.pages[slot] if p != PagePool.TRASH_PAGE]
+            g.pool.give_back(held)
+            g.pages[slot] = []
+            g.first_live[slot] = 0
+            g.table_host[slot, :] = 0
+            g.dirty.pop(slot, None)
+        for t in self._state.values():
+            t[slot].zero_()
+        self.lengths[slot] = 0
+
     def truncate(self, slot: int, pos: int) -> int:
         """Rewinds a slot to `pos` tokens (src/model.rs:799-821: lowering the position is enough for
         attention caches).  Returns the length actually reached: fixed-size state and released window

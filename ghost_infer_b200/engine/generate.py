@@ -42,9 +42,15 @@ class GenerationLoop:
     `.step(entries) -> logits`; `sampler` needs `.start(n)` and `.pick(logits, request_ids) -> tokens`."""
 
     def __init__(self, engine, sampler, stop_token_ids: Sequence[int] = (), batch_size: int = 8,
-                 on_token: Optional[Callable[[int, int], None]] = None):
+                 on_token: Optional[Callable[[int, int], None]] = None, max_step_tokens: Optional[int] = None):
+        """`max_step_tokens`: the most prompt tokens one step carries; longer batches of prompts are read in
+        several steps that attend to the cache (the reference reads prompts in passes of 1024 tokens,
+        src/cuda.rs:8550).  None: all prompts of a batch in one step."""
         if batch_size < 1:
             raise ValueError("batch_size must be at least 1")
+        if max_step_tokens is not None and max_step_tokens < 1:
+            raise ValueError("max_step_tokens must be at least 1")
+        self.max_step_tokens = max_step_tokens
         self.engine = engine
         self.sampler = sampler
         self.stop = frozenset(int(t) for t in stop_token_ids)
@@ -87,6 +93,35 @@ class GenerationLoop:
             first += n
         return results
 
+    def _read_prompts(self, prompts, slots, live: List[int]):
+        """All prompts of the batch, in one step or in steps of at most `max_step_tokens` tokens; returns the
+        logits after each prompt's last token, in the order of `live`."""
+        limit = self.max_step_tokens
+        if limit is None or sum(len(prompts[i]) for i in live) <= limit:
+            self.stats.steps += 1
+            return self.engine.step([StepEntry(slots[i], prompts[i], [len(prompts[i]) - 1]) for i in live])
+        import torch
+        fed = {i: 0 for i in live}
+        rows = {}
+        while any(fed[i] < len(prompts[i]) for i in live):
+            budget, entries, owners = limit, [], []
+            for i in live:
+                left = len(prompts[i]) - fed[i]
+                if left == 0 or budget == 0:
+                    continue
+                n = min(left, budget)
+                last = fed[i] + n == len(prompts[i])
+                entries.append(StepEntry(slots[i], prompts[i][fed[i]:fed[i] + n], [n - 1] if last else []))
+                if last:
+                    owners.append(i)
+                fed[i] += n
+                budget -= n
+            out = self.engine.step(entries)
+            self.stats.steps += 1
+            for r, i in enumerate(owners):
+                rows[i] = out[r].clone()
+        return torch.stack([rows[i] for i in live])
+
     def _run_batch(self, prompts, results, ids: List[int], max_new: int) -> None:
         cache = self.engine.cache
         slots = {i: cache.open_slot() for i in ids}
@@ -99,8 +134,7 @@ class GenerationLoop:
                 for i in live:
                     results[i].finish_reason = "length"
                 return
-            logits = self.engine.step([StepEntry(slots[i], prompts[i], [len(prompts[i]) - 1]) for i in live])
-            self.stats.steps += 1
+            logits = self._read_prompts(prompts, slots, live)
             picked = self.sampler.pick(logits, live)
             self.stats.prompt_tokens += sum(len(prompts[i]) for i in live)
             t1 = time.perf_counter()

@@ -158,3 +158,18 @@ def test_truncate_rewinds_and_frees():
     cs.reserve([(s, 10)])
     cs.commit(s, 10)
     assert cs.truncate(s, 5) == 10          # fixed-size state cannot be rewound
+
+
+def test_reset_starts_a_slot_over():
+    c = make_cache(max_tokens=640, state=True)
+    s = c.open_slot()
+    c.reserve([(s, 200)])
+    c.commit(s, 200)
+    c.memory(0).state[s] += 3.0
+    c.reset(s)
+    assert c.length(s) == 0 and c.free_pages == 10 and float(c.memory(0).state[s].abs().sum()) == 0.0
+    assert c.slots.live(s)
+    c.reserve([(s, 65)])
+    assert c.free_pages == 8
+    with pytest.raises(RuntimeError):
+        c.reset(s + 1)

@@ -29,7 +29,7 @@ class FakeEngine:
                 row = torch.zeros(VOCAB)
                 row[(e.tokens[w] + 1 + n) % VOCAB] = 1.0
                 rows.append(row)
-        return torch.stack(rows)
+        return torch.stack(rows) if rows else None
 
 
 class ArgmaxSampler:
@@ -126,3 +126,15 @@ def test_max_new_zero_and_on_token():
     assert loop.run([[1]], max_new=0)[0].tokens == []
     res = loop.run([[1], [2, 3]], max_new=2)
     assert sorted(seen) == sorted([(0, t) for t in res[0].tokens] + [(1, t) for t in res[1].tokens])
+
+
+def test_prompts_read_in_several_steps():
+    eng = FakeEngine()
+    loop = GenerationLoop(eng, ArgmaxSampler(), batch_size=4, max_step_tokens=16)
+    prompts = [[1] * 30, [2] * 5, [3] * 12]
+    res = loop.run(prompts, max_new=3)
+    for p, r in zip(prompts, res):
+        assert r.tokens == expected(p, 3)[0]
+    prompt_steps = [c for c in eng.calls if any(n > 1 for _, n in c)]
+    assert all(sum(n for _, n in c) <= 16 for c in prompt_steps) and len(prompt_steps) == 3
+    assert [n for c in prompt_steps for s, n in c if s == 0] == [16, 14]       # request 0 in two pieces
