@@ -33,6 +33,22 @@ TINY_C = {
     "max_position_embeddings": 512, "rope_theta": 20000.0, "rope_scaling": None, "rms_norm_eps": 3e-6,
     "tie_word_embeddings": False,
 }
+# Two more with the head sizes the tensor-core attention kernels take (64 and 128), so that the engine tests run
+# those kernels inside a whole model: groups of 2 and 3 heads, widths that are no power of two.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 192, "num_hidden_layers": 2, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 328, "vocab_size": 520,
+    "max_position_embeddings": 1024, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+}
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 264, "num_hidden_layers": 2, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 400, "vocab_size": 333,
+    "max_position_embeddings": 1024, "rope_theta": 10000.0, "rope_scaling": None, "rms_norm_eps": 2e-6,
+    "tie_word_embeddings": False,
+}
 
 
 def pytest_configure(config):
@@ -58,7 +74,7 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session")
 def tiny_configs():
-    return {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+    return {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 @pytest.fixture(scope="session")
@@ -72,9 +88,9 @@ def model_dirs(tmp_path_factory):
     def get(name, stored):
         key = (name, stored)
         if key not in made:
-            cfg = {"A": TINY_A, "B": TINY_B, "C": TINY_C}[name]
+            cfg = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}[name]
             d = tmp_path_factory.mktemp(f"tiny_{name}_{stored}")
-            seed = {"A": 0, "B": 1, "C": 2}[name]
+            seed = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}[name]
             write_random_model(str(d), cfg, seed=seed, dtype=stored, std=0.05, norm_jitter=0.1)
             made[key] = str(d)
         return made[key]

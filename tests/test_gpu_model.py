@@ -12,7 +12,8 @@ pytestmark = pytest.mark.gpu
 
 CASES = [("A", "float32", "float32"), ("B", "float32", "float32"), ("C", "float32", "bfloat16"),
          ("A", "bfloat16", "bfloat16"), ("B", "bfloat16", "bfloat16"), ("C", "bfloat16", "bfloat16"),
-         ("B", "bfloat16", "float32")]
+         ("B", "bfloat16", "float32"), ("D", "bfloat16", "bfloat16"), ("E", "bfloat16", "bfloat16"),
+         ("E", "float32", "bfloat16")]
 
 
 @pytest.fixture(scope="module")
@@ -121,7 +122,8 @@ def test_unequal_batches_one_after_another(engines, tiny_configs, name, dtype, s
         assert eng.cache.free_pages == eng.cache.n_pages and eng.cache.slots.free_slots == eng.cache.max_slots
 
 
-@pytest.mark.parametrize("name,dtype,stored", [("A", "float32", "float32"), ("B", "bfloat16", "bfloat16")])
+@pytest.mark.parametrize("name,dtype,stored", [("A", "float32", "float32"), ("B", "bfloat16", "bfloat16"),
+                                               ("D", "bfloat16", "bfloat16"), ("E", "bfloat16", "bfloat16")])
 def test_long_decoding(engines, tiny_configs, name, dtype, stored):
     """Three prompt tokens, then 700 single-token steps: page after page, and contexts long enough for the
     decode kernel to cut them into slices."""
@@ -167,7 +169,7 @@ def test_host_checks_come_before_any_launch(engines):
     eng.cache.close_slot(s)
 
 
-@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("name", ["B", "C", "E"])
 def test_decoding_with_dependent_launch(model_dirs, tiny_configs, name):
     """Programmatic dependent launch lets a kernel start while its predecessor drains; results must not move.
     A batch decodes through the graph runner with it on, against the plain implementation and against itself off."""

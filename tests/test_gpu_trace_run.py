@@ -57,7 +57,7 @@ def build_trace(cfg):
     return reqs, steps
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "float32"), ("C", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "float32"), ("C", "bfloat16"), ("E", "bfloat16")])
 def test_trace_replay(tmp_path, model_dirs, tiny_configs, name, dtype):
     d = model_dirs(name, dtype)
     cfg = tiny_configs[name]
