@@ -252,7 +252,8 @@ def main():
 
     # end to end through the Python entry point: host token ids in, host token ids out, every step
     prompts = [rng.integers(0, V, size=PROMPT).tolist() for _ in range(8)]
-    e2e_new = max(8, min(K, 64))
+    # at least 128 steps: right after the 16k-token prefill the SM clock is power-capped for some tens of steps
+    e2e_new = max(K, 128)
     llm.generate(prompts, max_new=3, temperature=0.0, stop_token_ids=(), batch_size=8)     # warm-up
     llm.generate(prompts, max_new=e2e_new, temperature=0.0, stop_token_ids=(), batch_size=8)
     st = llm.last_stats

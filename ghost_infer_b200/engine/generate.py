@@ -123,6 +123,105 @@ class GenerationLoop:
         return torch.stack([rows[i] for i in live])
 
     def _run_batch(self, prompts, results, ids: List[int], max_new: int) -> None:
+        if hasattr(self.engine, "decoder") and hasattr(self.sampler, "pick_device"):
+            return self._run_batch_pipelined(prompts, results, ids, max_new)
+        return self._run_batch_simple(prompts, results, ids, max_new)
+
+    # ---- tokens stay on the device; the host looks at them one step late ---------------------------------
+    def _run_batch_pipelined(self, prompts, results, ids: List[int], max_new: int) -> None:
+        """The same decisions as `_run_batch_simple`, but the host is off the critical path: the step that feeds
+        token k is launched from the device copy of the sampled tokens, and token k is examined on the host
+        (stop tokens, callbacks) while that step runs.  A sequence that turns out to have ended on token k has
+        then been stepped once too often: its extra token is dropped and its slot is given back with the batch."""
+        import torch
+        cache = self.engine.cache
+        slots = {i: cache.open_slot() for i in ids}
+        self.stats.batches += 1
+        finished = {i: False for i in ids}
+        n_sampled = {i: 0 for i in ids}
+        pinned = [torch.empty(len(ids), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        flip = 0
+
+        def to_host(dev_tokens, order):
+            nonlocal flip
+            buf = pinned[flip][:len(order)]
+            flip ^= 1
+            buf.copy_(dev_tokens[:len(order)], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            return buf, ev, list(order)
+
+        def resolve(flight, fed_now):
+            """Host-side decisions on tokens sampled one step ago."""
+            buf, ev, order = flight
+            ev.synchronize()
+            for i, tok in zip(order, buf.tolist()):
+                if finished[i]:
+                    continue                                  # ended earlier; this token came from the extra step
+                res = results[i]
+                self.stats.gen_tokens += 1
+                if tok in self.stop:                          # counted, not kept, not fed (src/main.rs:772-776)
+                    res.finish_reason, res.stopped_on, finished[i] = "stop", tok, True
+                    continue
+                res.tokens.append(tok)
+                if self.on_token is not None:
+                    self.on_token(i, tok)
+                if len(res.tokens) >= max_new:
+                    res.finish_reason, finished[i] = "length", True
+                elif i not in fed_now:
+                    res.finish_reason, finished[i] = "capacity", True     # the reference's `pos < ctx` (src/main.rs:770)
+
+        try:
+            t0 = time.perf_counter()
+            if max_new <= 0:
+                for i in ids:
+                    results[i].finish_reason = "length"
+                return
+            order = list(ids)
+            logits = self._read_prompts(prompts, slots, order)
+            cur = self.sampler.pick_device(logits, order)
+            for i in order:
+                n_sampled[i] = 1
+            flight = to_host(cur, order)
+            self.stats.prompt_tokens += sum(len(prompts[i]) for i in order)
+            torch.cuda.current_stream().synchronize()
+            t1 = time.perf_counter()
+            self.stats.prompt_secs += t1 - t0
+            runner = None
+            while True:
+                feed = [i for i in order if not finished[i] and n_sampled[i] < max_new
+                        and cache.length(slots[i]) + 1 <= cache.max_seq_len]
+                nxt = nxt_flight = None
+                if feed:
+                    if len(feed) == len(order):
+                        tok_in = cur
+                    else:
+                        pos = {i: r for r, i in enumerate(order)}
+                        rows = torch.tensor([pos[i] for i in feed], dtype=torch.int64).to(cur.device, non_blocking=True)
+                        tok_in = cur.index_select(0, rows)
+                    want = [slots[i] for i in feed]
+                    if runner is None or runner.slots != want:
+                        runner = self.engine.decoder(want)
+                    try:
+                        logits = runner.forward(dev_tokens=tok_in)
+                    except CacheFullError:
+                        feed = []
+                    else:
+                        self.stats.steps += 1
+                        nxt = self.sampler.pick_device(logits, feed)
+                        for i in feed:
+                            n_sampled[i] += 1
+                        nxt_flight = to_host(nxt, feed)
+                resolve(flight, set(feed))
+                if not feed:
+                    break
+                order, cur, flight = feed, nxt, nxt_flight
+            self.stats.gen_secs += time.perf_counter() - t1
+        finally:
+            for s in slots.values():
+                cache.close_slot(s)
+
+    def _run_batch_simple(self, prompts, results, ids: List[int], max_new: int) -> None:
         cache = self.engine.cache
         slots = {i: cache.open_slot() for i in ids}
         self.stats.batches += 1

@@ -65,12 +65,15 @@ class DeviceSampler:
         host = torch.tensor([_as_i64(stream_seed(self.seed, i)) for i in range(n_requests)], dtype=torch.int64)
         self.states = host.to(self.device)
 
-    def pick(self, logits: torch.Tensor, request_ids: Sequence[int]) -> List[int]:
-        """One token for each row of `logits`; row r belongs to request `request_ids[r]`."""
+    def pick_device(self, logits: torch.Tensor, request_ids: Sequence[int]) -> torch.Tensor:
+        """One token for each row of `logits` (row r belongs to request `request_ids[r]`), left on the device
+        as int32, so that the next step can be launched before the host has looked at the tokens."""
         p = self.params
         if p.greedy:
-            out = ops.sample(logits, 0.0, 0, 1.0)
-        else:
-            idx = torch.tensor(list(request_ids), dtype=torch.int32).to(self.device, non_blocking=True)
-            out = ops.sample(logits, p.temperature, p.top_k, p.top_p, self.states, idx)
-        return out.cpu().tolist()
+            return ops.sample(logits, 0.0, 0, 1.0)
+        idx = torch.tensor(list(request_ids), dtype=torch.int32).to(self.device, non_blocking=True)
+        return ops.sample(logits, p.temperature, p.top_k, p.top_p, self.states, idx)
+
+    def pick(self, logits: torch.Tensor, request_ids: Sequence[int]) -> List[int]:
+        """The same, brought to the host."""
+        return self.pick_device(logits, request_ids).cpu().tolist()
