@@ -180,3 +180,125 @@ def test_a_layer_named_twice_and_a_shared_cache(tmp_path):
         check_logits(np.concatenate(outs), plain_shared_forward(cfg, w, toks), "float32", "shared cache")
     finally:
         unregister_architecture("ToySharedForCausalLM")
+
+
+# ---------------------------------------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, both defined here.
+from ghost_infer_b200.kernels import ops as _ops
+from ghost_infer_b200.parts import FeedForward, PositionEncoding
+
+
+class RoutedFfn(FeedForward):
+    """Two experts, each one matrix; a router (32-bit logits) sends every token to the expert with the higher
+    logit; the expert's output is scaled by the softmax weight of that logit."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.d = int(params["hidden_size"])
+        self.n = int(params["experts"])
+
+    def weights(self):
+        return [WeightSpec(self.prefix + "moe.router.weight", (self.n, self.d))] + \
+               [WeightSpec(self.prefix + f"moe.experts.{e}.weight", (self.d, self.d)) for e in range(self.n)]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.router = rt.place(tensors[self.prefix + "moe.router.weight"]).float()
+        self.experts = torch.stack([rt.place(tensors[self.prefix + f"moe.experts.{e}.weight"]).float() for e in range(self.n)])
+
+    def forward(self, h, residual, step):
+        x = h.float()
+        logits = x @ self.router.T                              # router logits in 32-bit
+        weight, pick = torch.softmax(logits, -1).max(-1)
+        out = torch.einsum("td,tod->to", x, self.experts[pick])
+        residual += out * weight[:, None]
+
+
+class ScaledPositions(PositionEncoding):
+    """No rotation: queries are scaled by 1 + slope * position (so scores depend on where the query stands)."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.slope = float(params["slope"])
+
+    def encode_and_store(self, qkv, step, memory, n_heads, n_kv_heads, head_dim):
+        q = qkv[:, :n_heads * head_dim]
+        q.mul_((1.0 + self.slope * step.positions.float())[:, None].to(q.dtype))
+        _ops.rope_cache_write(qkv, None, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
+                              n_heads, n_kv_heads, head_dim, 0, False, memory.writes and memory.k is not None)
+
+
+def routed_spec(cfg):
+    base = build_llama_spec(cfg)
+    layers = []
+    for i, ls in enumerate(base.layers):
+        mixer = PartSpec("gqa_attention", dict(ls.mixer.params, position=PartSpec("scaled_positions", {"slope": 0.02})))
+        ffn = PartSpec("toy_routed", {"hidden_size": cfg.hidden_size, "experts": 2}) if i == 1 else ls.ffn
+        layers.append(LayerSpec(prefix=ls.prefix, block=ls.block, mixer_norm=ls.mixer_norm, mixer=mixer,
+                                ffn_norm=ls.ffn_norm, ffn=ffn))
+    return ModelSpec(architecture="ToyRoutedForCausalLM", hidden_size=base.hidden_size, vocab_size=base.vocab_size,
+                     max_positions=base.max_positions, embedding=base.embedding, layers=tuple(layers),
+                     schedule=base.schedule, final_norm=base.final_norm, head=base.head)
+
+
+def plain_routed_forward(cfg, w, tokens):
+    H, KV, hd, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    pos = np.arange(len(tokens))
+    x = pl.embed(w["model.embed_tokens.weight"], tokens)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        h = pl.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+        q = (h @ w[p + "self_attn.q_proj.weight"].T) * (1.0 + 0.02 * pos)[:, None]
+        k, v = h @ w[p + "self_attn.k_proj.weight"].T, h @ w[p + "self_attn.v_proj.weight"].T
+        x = x + pl.attention(q, k, v, H, KV, hd, 1 / math.sqrt(hd)) @ w[p + "self_attn.o_proj.weight"].T
+        h = pl.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+        if i == 1:
+            logits = h @ w[p + "moe.router.weight"].T
+            e = np.exp(logits - logits.max(-1, keepdims=True))
+            prob = e / e.sum(-1, keepdims=True)
+            pick = prob.argmax(-1)
+            out = np.stack([w[p + f"moe.experts.{pick[t]}.weight"] @ h[t] for t in range(len(tokens))])
+            x = x + out * prob.max(-1)[:, None]
+        else:
+            x = x + pl.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return pl.rms_norm(x, w["model.norm.weight"], eps) @ w["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
+    register("feed_forward", "toy_routed", RoutedFfn)
+    register("position", "scaled_positions", ScaledPositions)
+    register_architecture("ToyRoutedForCausalLM", LlamaConfig.from_dict, routed_spec)
+    try:
+        raw = dict(TINY_A, architectures=["ToyRoutedForCausalLM"])
+        d = str(tmp_path / "routed")
+        write_random_model(d, raw, seed=5, dtype=dtype, std=0.05, norm_jitter=0.1)
+        model = gi.Model.from_pretrained(d, dtype=dtype)
+        names = {w.name for w in model.weight_manifest()}
+        assert "model.layers.1.moe.router.weight" in names and "model.layers.1.mlp.gate_proj.weight" not in names
+        cache = model.new_cache(max_tokens=64 * 16, max_seq_len=512)
+        eng = gi.Engine(model, cache)
+        cfg, w = pl.read_model(d)
+        rng = np.random.default_rng(2)
+        seqs = [rng.integers(0, 256, n).tolist() for n in (70, 12)]
+        slots = [cache.open_slot() for _ in seqs]
+        cut = [50, 12]
+        out = eng.step([gi.StepEntry(s, t[:c], list(range(c))) for s, t, c in zip(slots, seqs, cut)]).cpu().numpy()
+        got = [[out[:50]], [out[50:]]]
+        runner = eng.decoder([slots[0]])                  # the graph path, with parts the library has never seen
+        for j in range(50, 70):
+            got[0].append(runner.forward(tokens=[seqs[0][j]]).cpu().numpy())
+        for i, t in enumerate(seqs):
+            ref = plain_routed_forward(cfg, w, t)
+            if dtype == "float32":
+                check_logits(np.concatenate(got[i]), ref, "float32", f"routed request {i}")
+            else:
+                # a 16-bit engine may route a token whose two router logits nearly tie to the other expert
+                err = np.abs(np.concatenate(got[i]) - ref).max(-1)
+                assert np.median(err) <= 0.025 * max(1.0, np.abs(ref).max()), float(np.median(err))
+        for s in slots:
+            cache.close_slot(s)
+    finally:
+        unregister("feed_forward", "toy_routed")
+        unregister("position", "scaled_positions")
+        unregister_architecture("ToyRoutedForCausalLM")
