@@ -91,3 +91,37 @@ def test_command_line_run(model_dirs, tiny_configs):
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "ghost-infer"), "run", d, "--nonsense"],
                          capture_output=True, text=True, timeout=600)
     assert bad.returncode == 1 and "unknown option --nonsense" in bad.stderr
+
+
+def test_command_line_top_kvcheck_and_bench(tmp_path, model_dirs, tiny_configs):
+    d = model_dirs("A", "float32")
+    ids = tokens_for(tiny_configs["A"], 12, 2)
+    exe = [sys.executable, os.path.join(ROOT, "bin", "ghost-infer")]
+    # top: the ten most likely next tokens, and every logit as little-endian float32 when the variable is set
+    dump = tmp_path / "logits.f32"
+    p = subprocess.run(exe + ["top", d, ",".join(map(str, ids))], capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, GHOST_INFER_LOGITS_OUT=str(dump)))
+    assert p.returncode == 0, p.stderr
+    cfg, w = oracle(d)
+    ref = pl.forward(cfg, w, ids)[-1]
+    got = np.fromfile(dump, dtype="<f4")
+    assert got.shape == ref.shape and np.abs(got - ref).max() < 0.05
+    lines = [l for l in p.stdout.splitlines() if "logprob" in l]
+    assert len(lines) == 10 and int(lines[0].split()[0]) in np.argsort(-ref)[:2]
+    # kvcheck: all but the last 4 ids as a prompt, those one at a time; pick and log-probability per token
+    idf, out = tmp_path / "ids.txt", tmp_path / "kv.txt"
+    idf.write_text(" ".join(map(str, ids)))
+    p = subprocess.run(exe + ["kvcheck", d, str(idf), str(out), "4"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr
+    rows = [l.split() for l in out.read_text().splitlines()]
+    assert len(rows) == 4 and "mean NLL" in p.stderr
+    full = pl.forward(cfg, w, ids)
+    for j, (pick, lp) in enumerate(rows):
+        l = full[len(ids) - 5 + j]
+        want = l[ids[len(ids) - 4 + j]] - (np.log(np.exp(l - l.max()).sum()) + l.max())
+        assert abs(float(lp) - want) < 0.02
+    # bench: the reference's fixed workload and its one-line result
+    p = subprocess.run(exe + ["bench", d, "-n", "6", "--prompt-len", "20", "--batch", "2"], capture_output=True, text=True,
+                       timeout=600, env=dict(os.environ, GHOST_INFER_BENCH_ROUNDS="2"))
+    assert p.returncode == 0, p.stderr
+    assert "prompt 20 tok x 2:" in p.stdout and "generate 6 tok x 2:" in p.stdout and p.stderr.count("round ") == 2
