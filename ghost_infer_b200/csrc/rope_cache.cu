@@ -91,6 +91,59 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* __
   }
 }
 
+// The same work for many tokens at once (a prompt): one block per token, 16 bytes per access.  Takes the common
+// case only: half-split pairs, rotary and head sizes that are multiples of 16, nothing pending.  A thread takes
+// eight neighbouring pairs of a head (two 16-byte loads, 8 apart by half the rotary size), or eight values.
+template <typename T>
+__global__ void rope_cache_rows_kernel(T* __restrict__ qkv, long ld, const float2* __restrict__ table, const int* __restrict__ positions,
+                                       const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
+                                       T* __restrict__ kcache, T* __restrict__ vcache, int n_heads, int n_kv, int hd, int rot,
+                                       int write_cache) {
+  constexpr int V = 16 / sizeof(T);            // values per 16-byte access
+  gi::pdl_prologue();
+  const int t = blockIdx.x;
+  const int half = rot / 2;
+  T* row = qkv + (size_t)t * ld;
+  const int pos = positions[t], slot = slots[t];
+  const int page = (write_cache && slot >= 0) ? block_table[(size_t)slot * max_pages + pos / PAGE_TOKENS] : 0;
+  const int off = pos % PAGE_TOKENS;
+  const float2* cs = table + (size_t)t * half;
+  const int chunks = half / V;                 // chunks of V pairs per head
+  const int rot_heads = n_heads + (write_cache ? n_kv : 0);
+  for (int item = threadIdx.x; item < rot_heads * chunks; item += blockDim.x) {
+    const int head = item / chunks, i0 = (item % chunks) * V;
+    T* src = row + (size_t)head * hd;
+    T* dst = src;
+    if (head >= n_heads) dst = kcache + (((size_t)page * n_kv + (head - n_heads)) * PAGE_TOKENS + off) * hd;
+    T a[V], b[V];
+    *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(src + i0);
+    *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(src + i0 + half);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const float2 f = cs[i0 + e];
+      const float x = gi::ldf(a + e), y = gi::ldf(b + e);
+      gi::stf(a + e, x * f.x - y * f.y);
+      gi::stf(b + e, x * f.y + y * f.x);
+    }
+    *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(a);
+    *reinterpret_cast<uint4*>(dst + i0 + half) = *reinterpret_cast<const uint4*>(b);
+  }
+  if (!write_cache) return;
+  // keys past the rotated part, and the values: copied as they are
+  const int tail = (hd - rot) / V, vchunks = hd / V;
+  for (int item = threadIdx.x; item < n_kv * (tail + vchunks); item += blockDim.x) {
+    const int h = item / (tail + vchunks), c = item % (tail + vchunks);
+    const size_t cache_row = (((size_t)page * n_kv + h) * PAGE_TOKENS + off) * hd;
+    if (c < tail) {
+      const int d = rot + c * V;
+      *reinterpret_cast<uint4*>(kcache + cache_row + d) = *reinterpret_cast<const uint4*>(row + (size_t)(n_heads + h) * hd + d);
+    } else {
+      const int d = (c - tail) * V;
+      *reinterpret_cast<uint4*>(vcache + cache_row + d) = *reinterpret_cast<const uint4*>(row + (size_t)(n_heads + n_kv + h) * hd + d);
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" int gi_rope_table(float* table, const int* positions, const float* inv_freq, int n_tokens, int rot, void* stream) {
@@ -111,6 +164,16 @@ int rope_impl(void* qkv, int dtype, long ld, const float* table, const int* posi
   if (rot > 0 && !table) return gi::fail(GI_ERR_ARG, "rope: no table of angles");
   // with partial sums pending, the k and v blocks must run even without a cache write, so that nothing stays unsettled;
   // they are only needed for the cache, though, so without a cache they are simply not launched
+  // a prompt's worth of tokens in the common layout: one block per token, 16-byte accesses
+  const int vals = dtype == GI_F32 ? 4 : 8;
+  if (st.partials == nullptr && n_tokens >= 32 && !adjacent && rot > 0 && (rot / 2) % vals == 0 && hd % vals == 0 && ld % vals == 0 &&
+      (((uintptr_t)qkv | (uintptr_t)kcache | (uintptr_t)vcache) & 15) == 0) {
+    cudaError_t e = cudaSuccess;
+    GI_DISPATCH_DTYPE(dtype, T,
+        e = gi::launch(rope_cache_rows_kernel<T>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, (T*)qkv, ld, (const float2*)table,
+                       positions, slots, block_table, max_pages, (T*)kcache, (T*)vcache, n_heads, n_kv, hd, rot, write_cache));
+    return gi::check(e, "rope_cache_write");
+  }
   const int heads = n_heads + (write_cache ? 2 * n_kv : 0);
   if (heads > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "rope: more than 65535 heads in one launch");
   dim3 grid(n_tokens, heads);

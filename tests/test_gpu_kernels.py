@@ -597,3 +597,39 @@ def test_prefill_kernels_chain_under_dependent_launch():
     assert ops.gemm_tc_status() == 0 and ops.attn_prefill_t5_status() == 0
     assert torch.isfinite(outs[0]).all() and float((outs[0] - x0).abs().max()) > 0
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,rot", [(16, 16), (128, 128), (64, 32), (48, 32)])
+def test_rope_and_cache_write_for_a_prompt(dtype, hd, rot):
+    """Many tokens at once take the kernel with 16-byte accesses (when the sizes allow it): the same numbers as the
+    plain formula, two sequences in different slots, positions that cross pages."""
+    H, KV, T = 5, 2, 90
+    qkv = rnd(T, (H + 2 * KV) * hd, dtype=dtype, seed=80)
+    orig = qkv.clone()
+    positions = torch.cat([torch.arange(60, 110), torch.arange(0, 40)]).to(torch.int32).to(DEV)
+    slots = torch.cat([torch.zeros(50), torch.ones(40)]).to(torch.int32).to(DEV)
+    bt = torch.tensor([[3, 1], [2, 4]], dtype=torch.int32, device=DEV)
+    kc = torch.zeros(5, KV, 64, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    inv = torch.from_numpy(pl.rotary_inv_freq(rot, 500000.0, None)).to(DEV)
+    table = ops.rope_table(positions, inv)
+    ops.rope_cache_write(qkv, table, positions, slots, bt, kc, vc, H, KV, hd, rot, False, True)
+    o = orig.double().cpu().numpy()
+    pos = positions.cpu().numpy()
+
+    def rot_ref(x, heads):
+        x = x.reshape(T, heads, hd)
+        y = x.copy()
+        y[:, :, :rot] = pl.rope(x[:, :, :rot].reshape(T, heads * rot), pos, inv.cpu().numpy(), rot, "half").reshape(T, heads, rot)
+        return y.reshape(T, heads * hd)
+
+    q_ref, k_ref, v_ref = rot_ref(o[:, :H * hd], H), rot_ref(o[:, H * hd:(H + KV) * hd], KV), o[:, (H + KV) * hd:]
+    t = tol(dtype)
+    np.testing.assert_allclose(qkv[:, :H * hd].double().cpu().numpy(), q_ref, rtol=t["rtol"], atol=t["atol"])
+    assert torch.equal(qkv[:, H * hd:], orig[:, H * hd:])
+    for i in range(T):
+        page = int(bt[int(slots[i]), int(pos[i]) // 64])
+        np.testing.assert_allclose(kc[page, :, int(pos[i]) % 64].double().cpu().numpy().reshape(-1), k_ref[i], rtol=t["rtol"], atol=t["atol"])
+        np.testing.assert_array_equal(vc[page, :, int(pos[i]) % 64].double().cpu().numpy().reshape(-1), v_ref[i])
+    assert float(kc[0].abs().sum()) == 0
