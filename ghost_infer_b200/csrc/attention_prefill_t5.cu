@@ -40,6 +40,14 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
         "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
         "r"(r[30]), "r"(r[31]) : "memory");
 }
+// 2^x in one instruction (32-bit, about 2 units in the last place): the softmax of this kernel is bound by the
+// number of instructions per score, and its probabilities are rounded to bfloat16 right after.
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Descriptor of an operand whose rows (the M or N side) are contiguous along that side ("MN-major"), stored as
@@ -202,29 +210,48 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
-      // scores -> probabilities
+      // scores -> probabilities.  A tile every row of the block sees in full needs no mask: one maximum, then one
+      // fused multiply-add, one exponential and one addition per score.  Tiles on the diagonal (or at a window's
+      // edge) take the masked path.
+      const bool interior = (kt + BKV - 1 <= pos0 + q0) && kt >= t_first && (window <= 0 || kt > pos0 + q0 + BQ - 1 - window);
       float tmax = -INFINITY;
+      if (interior) {
 #pragma unroll
-      for (int q = 0; q < 2; ++q)
+        for (int q = 0; q < 2; ++q)
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int key = kt + q * 32 + c;
-          const bool vis = key <= p_row && key >= t_first && (window <= 0 || key > p_row - window);
-          const float v = vis ? __uint_as_float(sr[q][c]) * sl2 : -INFINITY;
-          sr[q][c] = __float_as_uint(v);
-          tmax = fmaxf(tmax, v);
-        }
-      const float m_new = fmaxf(m_run, tmax);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
-      m_run = m_new;
+          for (int c = 0; c < 32; ++c) tmax = fmaxf(tmax, __uint_as_float(sr[q][c]));
+        tmax *= sl2;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int key = kt + q * 32 + c;
+            const bool vis = key <= p_row && key >= t_first && (window <= 0 || key > p_row - window);
+            const float v = vis ? __uint_as_float(sr[q][c]) : -INFINITY;
+            sr[q][c] = __float_as_uint(v);
+            tmax = fmaxf(tmax, v * sl2);
+          }
+      }
+      // The reference point of the exponentials moves only when the row's maximum has grown by more than 2^8 since
+      // it was set: probabilities may then exceed 1 (by at most 2^8, harmless in bfloat16 and float), and the
+      // accumulator in tensor memory is rescaled rarely instead of at every new maximum.  The result O / l does not
+      // depend on the reference point.
+      float alpha = 1.0f;
+      if (m_run == -INFINITY || tmax > m_run + 8.0f) {
+        const float m_new = fmaxf(m_run, tmax);
+        alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
+        m_run = m_new;
+      }
+      const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
       float psum = 0.f;
       uint32_t pk[32];
 #pragma unroll
       for (int q = 0; q < 2; ++q)
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          const float p0 = exp2f(__uint_as_float(sr[q][c]) - m_use), p1 = exp2f(__uint_as_float(sr[q][c + 1]) - m_use);
+          // a masked score is -inf: -inf * sl2 - m = -inf, and 2^-inf = 0
+          const float p0 = ex2(fmaf(__uint_as_float(sr[q][c]), sl2, neg_m)), p1 = ex2(fmaf(__uint_as_float(sr[q][c + 1]), sl2, neg_m));
           psum += p0 + p1;
           __nv_bfloat162 pv = __floats2bfloat162_rn(p0, p1);
           pk[q * 16 + c / 2] = *reinterpret_cast<uint32_t*>(&pv);
