@@ -139,6 +139,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b"], help="8b: the headline; 1b, 3b: the baseline's other workloads")
     ap.add_argument("--tune", default="", help="overrides of kernel choices, e.g. small_skinny=0,attn_waves=2")
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
+                    help="run one phase alone and print its time (a short program for a launch list under a profiler; no bench line)")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another (no programmatic dependent launch)")
     args = ap.parse_args()
 
@@ -211,6 +213,23 @@ def main():
         for s in slots:
             cache.close_slot(s)
         return ms, launched, ctx_tokens
+
+    if args.only == "decode":
+        ms, n, _ = decode_run(8, K, W)
+        print(json.dumps({"only": "decode", "layers": layers, "batch": 8, "ms_per_step": round(ms, 4), "launches_per_step": n // K}))
+        return 0
+    if args.only == "prefill":
+        prompt = rng.integers(0, V, size=PROMPT).tolist()
+        for i in range(W + K):
+            if i == W:
+                torch.cuda.synchronize()
+                t0 = time.time()
+            s = cache.open_slot()
+            eng.step([gi.StepEntry(s, prompt, [PROMPT - 1])])
+            cache.close_slot(s)
+        torch.cuda.synchronize()
+        print(json.dumps({"only": "prefill", "layers": layers, "tokens": PROMPT, "ms": round((time.time() - t0) * 1e3 / K, 3)}))
+        return 0
 
     clocks.start()
     ms8, launches8, ctx8 = decode_run(8, K, W)

@@ -21,6 +21,29 @@ typedef struct {
   int nt;                    // token-tile width of the product (16, 32 or 64)
 } gi_settle_t;
 
+#ifdef __CUDACC__
+// Which blocks of a deferred product hold pieces of the 128-column tile of column f.  Blocks take contiguous ranges
+// of K blocks, so every block after the first began its range inside the tile (its piece sits in its slot 0); only
+// the first block may have come from an earlier tile (slot 1).  The tables are uploaded once per shape and never
+// written by a kernel: a kernel may read them before its dependency wait.
+struct gi_settle_span {
+  int c_first, c_last, first_slot;
+};
+__device__ __forceinline__ gi_settle_span gi_span_of(const gi_settle_t& st, int f) {
+  gi_settle_span s;
+  const int tile = f / 128;
+  s.c_first = st.tile_first_cta[tile];
+  s.c_last = st.tile_last_cta[tile];
+  s.first_slot = (s.c_first != s.c_last && tile != st.cta_first_tile[s.c_first]) ? 1 : 0;
+  return s;
+}
+// The address of block c's piece for token m, column f.
+__device__ __forceinline__ const float* gi_piece(const gi_settle_t& st, const gi_settle_span& s, int c, int m, int f) {
+  const int slot = (c == s.c_first) ? s.first_slot : 0;
+  return st.partials + ((size_t)c * 2 + slot) * (128 * st.nt) + (size_t)m * 128 + f % 128;
+}
+#endif
+
 const char* gi_last_error(void);
 int gi_abi_version(void);
 // Programmatic dependent launch: kernels of a stream may begin while their predecessor drains (off by default).
@@ -56,6 +79,13 @@ int gi_gemm_skinny_bf16(void* out, int mode, const void* A, const void* W, int M
 long gi_gemm_stream_scratch_floats(void);
 int gi_gemm_stream_bf16(void* out, int mode, const void* A, const void* W, float* scratch, int* counters, int n_counters,
                         int M, int N, int K, long lda, long ldw, long ldo, int use_pdl, void* stream);
+// As gi_gemm_stream_bf16; `next_W` [next_N, next_K] (optional) is the matrix that the next streamed product in this
+// stream will read: the kernel asks the L2 cache for the first `units_ahead` 16 KB units of each of that launch's blocks
+// once its own loads are issued (`next_mode`: the mode of that launch, which decides how it cuts its work).  A wrong
+// guess costs bandwidth, never a result; next_W must be valid memory.
+int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const void* W, float* scratch, int* counters, int n_counters,
+                           int M, int N, int K, long lda, long ldw, long ldo, int use_pdl, const void* next_W, int next_N,
+                           int next_K, long next_ldw, int next_mode, int units_ahead, void* stream);
 int gi_gemm_stream_status(int* status);
 int gi_gemm_stream_geometry(int M, int N, int K, int* n_ctas, int* kb_per_tile, int* nt);
 

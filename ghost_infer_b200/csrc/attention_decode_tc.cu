@@ -34,7 +34,11 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem;                                       // [16][HD] bf16, swizzled
   unsigned char* ring = smem + 16 * HD * 2;                        // [WARPS][STAGES][K tile | V tile]
-  gi::pdl_prologue();
+  // Lengths, slots and the block table were uploaded before the step's first kernel, and no kernel of the step
+  // writes a cached position other than each sequence's last one: the first tiles of keys and values are
+  // requested before the dependency wait, while the kernel before this one (which writes the last position and
+  // the queries) still runs.  Only the tile that holds the last position waits.
+  gi::pdl_launch_dependents();
 
   const int group = n_heads / n_kv;
   const int chunks = (group + 15) / 16;
@@ -45,22 +49,6 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
   const int len = seq_lens[b];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-
-  // queries of the group's heads as rows 0..gcount-1 of a 16-row tile (the others zero)
-  for (int idx = tid; idx < 16 * CH; idx += WARPS * 32) {
-    const int r = idx / CH, c = idx % CH;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < gcount) v = *reinterpret_cast<const uint4*>(q + (size_t)b * ldq + (size_t)(h0 + r) * HD + c * 8);
-    *reinterpret_cast<uint4*>(q_s + gi::swz<CH>(r, c)) = v;
-  }
-  __syncthreads();
-  uint32_t qf[HD / 16][4];
-#pragma unroll
-  for (int ks = 0; ks < HD / 16; ++ks) {
-    // matrices: (rows 0-7, k lo), (rows 8-15, k lo), (rows 0-7, k hi), (rows 8-15, k hi) = a0..a3
-    const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = ks * 2 + (lane >> 4);
-    gi::ldmatrix_x4(qf[ks], gi::smem_u32(q_s + gi::swz<CH>(r, c)));
-  }
 
   int t_first = 0;
   if (window > 0) t_first = max(0, len - window);
@@ -97,14 +85,40 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
 
-  // prologue: STAGES - 1 tiles in flight
+  // prologue: STAGES - 1 tiles in flight; the tile with the sequence's last position only after the wait
   int next = tile_lo + warp;
+  int late_stage = -1;
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (next < tile_hi) issue(next, s);
+    if (next < tile_hi) {
+      if (next == tiles - 1) late_stage = s;
+      else issue(next, s);
+    }
     gi::cp_async_commit();
     next += WARPS;
   }
+  gi::pdl_wait();
+  if (late_stage >= 0) {          // a short slice: its last tile is among the first ones; fetch it now and let it land
+    issue(tiles - 1, late_stage);
+    gi::cp_async_commit();
+    gi::cp_async_wait<0>();
+  }
+  // queries of the group's heads as rows 0..gcount-1 of a 16-row tile (the others zero)
+  for (int idx = tid; idx < 16 * CH; idx += WARPS * 32) {
+    const int r = idx / CH, c = idx % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < gcount) v = *reinterpret_cast<const uint4*>(q + (size_t)b * ldq + (size_t)(h0 + r) * HD + c * 8);
+    *reinterpret_cast<uint4*>(q_s + gi::swz<CH>(r, c)) = v;
+  }
+  __syncthreads();
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+    // matrices: (rows 0-7, k lo), (rows 8-15, k lo), (rows 0-7, k hi), (rows 8-15, k hi) = a0..a3
+    const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = ks * 2 + (lane >> 4);
+    gi::ldmatrix_x4(qf[ks], gi::smem_u32(q_s + gi::swz<CH>(r, c)));
+  }
+
   int stage = 0;
   for (int tile = tile_lo + warp; tile < tile_hi; tile += WARPS) {
     // keep the ring full, then wait for the oldest tile

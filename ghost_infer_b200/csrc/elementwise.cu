@@ -21,14 +21,11 @@ __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ tab
 // Sum of the partial sums a deferred product left for features f..f+3 of token m (see gemm_stream.cu: a tile of
 // 128 features whose K range was cut between blocks c_first..c_last has one slot per block; they are added in
 // the order of the K ranges, so the result does not depend on any timing).  f is a multiple of 4.
-__device__ __forceinline__ float4 pending_sum(const gi_settle_t& st, int m, int f) {
+__device__ __forceinline__ float4 pending_sum(const gi_settle_t& st, const gi_settle_span& sp, int m, int f) {
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  const int tile = f / 128, row = f % 128;
-  const int c_first = st.tile_first_cta[tile], c_last = st.tile_last_cta[tile];
-  if (c_first == c_last) return acc;                 // one block had the whole tile and added it itself
-  for (int c = c_first; c <= c_last; ++c) {
-    const int which = (tile == st.cta_first_tile[c]) ? 0 : 1;
-    const float4 p = __ldcg(reinterpret_cast<const float4*>(st.partials + ((size_t)c * 2 + which) * (128 * st.nt) + (size_t)m * 128 + row));
+  if (sp.c_first == sp.c_last) return acc;                 // one block had the whole tile and added it itself
+  for (int c = sp.c_first; c <= sp.c_last; ++c) {
+    const float4 p = __ldcg(reinterpret_cast<const float4*>(gi_piece(st, sp, c, m, f)));
     acc.x += p.x;
     acc.y += p.y;
     acc.z += p.z;
@@ -44,7 +41,7 @@ __global__ void settle_kernel(float* __restrict__ x, gi_settle_t st, const int* 
   float4* xr = reinterpret_cast<float4*>(x + (size_t)m * d);
   for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
     float4 v = xr[i];
-    const float4 p = pending_sum(st, m, 4 * i);
+    const float4 p = pending_sum(st, gi_span_of(st, 4 * i), m, 4 * i);
     v.x += p.x;
     v.y += p.y;
     v.z += p.z;
@@ -61,13 +58,26 @@ template <typename TO, typename TW, int VEC, bool SETTLE>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, const TW* __restrict__ w,
                                const int* __restrict__ rows, int d, float eps, gi_settle_t st) {
   __shared__ float scratch[33];
-  gi::pdl_prologue();
+  gi::pdl_launch_dependents();
   const int r = blockIdx.x;
-  const int m = rows ? rows[r] : r;
+  const int m = rows ? rows[r] : r;         // the selection was uploaded before the step's first kernel
   float* xr = x + (size_t)m * d;
   TO* o = out + (size_t)r * d;
   if (VEC > 0) {
     const int n4 = d / 4;
+    // what no kernel writes (the norm's weights, the tables of a deferred product's cut) is read before the
+    // dependency wait; the rows and the partial sums after it
+    float4 wv[VEC > 0 ? VEC : 1];
+    gi_settle_span sp[VEC > 0 ? VEC : 1];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < n4) {
+        wv[j] = make_float4(gi::ldf(w + 4 * i), gi::ldf(w + 4 * i + 1), gi::ldf(w + 4 * i + 2), gi::ldf(w + 4 * i + 3));
+        if (SETTLE) sp[j] = gi_span_of(st, 4 * i);
+      }
+    }
+    gi::pdl_wait();
     float4 v[VEC > 0 ? VEC : 1];
     float ss = 0.f;
 #pragma unroll
@@ -75,7 +85,7 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, cons
       const int i = threadIdx.x + j * blockDim.x;
       v[j] = i < n4 ? reinterpret_cast<const float4*>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
       if (SETTLE && i < n4) {
-        const float4 p = pending_sum(st, m, 4 * i);
+        const float4 p = pending_sum(st, sp[j], m, 4 * i);
         v[j].x += p.x;
         v[j].y += p.y;
         v[j].z += p.z;
@@ -93,14 +103,15 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, cons
     for (int j = 0; j < VEC; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
       if (i < n4) {
-        gi::stf(o + 4 * i, v[j].x * scale * gi::ldf(w + 4 * i));
-        gi::stf(o + 4 * i + 1, v[j].y * scale * gi::ldf(w + 4 * i + 1));
-        gi::stf(o + 4 * i + 2, v[j].z * scale * gi::ldf(w + 4 * i + 2));
-        gi::stf(o + 4 * i + 3, v[j].w * scale * gi::ldf(w + 4 * i + 3));
+        gi::stf(o + 4 * i, v[j].x * scale * wv[j].x);
+        gi::stf(o + 4 * i + 1, v[j].y * scale * wv[j].y);
+        gi::stf(o + 4 * i + 2, v[j].z * scale * wv[j].z);
+        gi::stf(o + 4 * i + 3, v[j].w * scale * wv[j].w);
       }
     }
     return;
   }
+  gi::pdl_wait();
   float ss = 0.f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     const float v = xr[i];

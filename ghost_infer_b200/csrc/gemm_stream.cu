@@ -3,16 +3,19 @@
 // the instruction and the tokens its "N" side (16, 32 or 64), so the accumulator in tensor memory holds
 // [128 features x tokens].
 //
-// One persistent block per SM.  The work is the flat list of (128-row tile of W, 64-column block of K) units,
-// cut into one contiguous, equally long range per block ("stream-K"), so every SM streams the same number of
-// bytes whatever the matrix's shape.  Inside a block: one thread feeds a deep ring of shared-memory stages with
-// TMA (a 16 KB box of W and the matching small box of activations per stage, so far more bytes are in flight
-// than registers could hold); one thread issues the tcgen05.mma instructions; four warps drain finished
-// accumulators (two buffers in tensor memory, so draining overlaps the next tile's products).  A tile whose K
-// range lies in one block is finished there.  A tile cut between blocks leaves its partial sums in scratch;
-// the block that arrives last (an atomic counter per tile; nobody waits) adds the partials in the order of the
-// K ranges, so the sum does not depend on which block came last.  Epilogues: store (bfloat16 or float), add
-// into the float residual stream, or SwiGLU over gate/up rows interleaved in blocks of 8.
+// One persistent block per SM.  The work is the list of (128-row tile of W, 64-column block of K) units.  Each
+// block first takes an equal contiguous range of the units of the "shared" tiles ("stream-K"), then whole tiles
+// of its own (see Plan), so every SM streams the same number of bytes whatever the matrix's shape.  Inside a
+// block: one thread feeds a deep ring of shared-memory stages with TMA (a 16 KB box of W and the matching small
+// box of activations per stage, so far more bytes are in flight than registers could hold); one thread issues
+// the tcgen05.mma instructions; four warps drain finished accumulators (two buffers in tensor memory, so
+// draining overlaps the next tile's products).  A tile whose K range lies in one block is finished there.  A
+// tile cut between blocks leaves its partial sums in scratch; the block that arrives last (an atomic counter per
+// tile; nobody waits) adds the partials in the order of the K ranges, so the sum does not depend on which block
+// came last; since the shared units come first, that exchange is over long before the block's last tile is.
+// Epilogues: store (bfloat16 or float), add into the float residual stream, or SwiGLU over gate/up rows
+// interleaved in blocks of 8.  Once a block's own loads are issued it asks the L2 cache for the first units of
+// the matrix that the next product in the stream will read, when the caller named it.
 //
 // The role in the reference: its decode matvec kernels (src/cuda.rs:1425-1434), which are bound by weight
 // bytes too and keep a fixed summation order (src/cuda.rs:748-766).
@@ -33,6 +36,12 @@ constexpr int TMEM_COLS = 128;   // two accumulator buffers of up to 64 columns
 
 __device__ int g_stream_status = 0;
 
+// The matrix [N, K] that the next streamed product will read (units_ahead = 0: unknown), and how that launch cuts it
+// (all_shared: it runs in a mode that leaves partial sums to a later kernel).
+struct Next {
+  int N, K, n_ctas, units_ahead, all_shared;
+};
+
 struct Range {
   long first, last;              // units [first, last)
 };
@@ -43,6 +52,35 @@ __device__ __forceinline__ Range range_of(int cta, int n_ctas, long units) {
   r.last = (long)(cta + 1) * units / n_ctas;
   return r;
 }
+// What one block works through, in this order: a contiguous range of the units of the "shared" tiles (cut evenly
+// between all blocks, stream-K), then whole tiles of its own.  With T tiles and G blocks, each block owns
+// floor(T / G) whole tiles (tiles [c * W, c * W + W)) and the last T - W * G tiles are shared.  The shared units
+// come first so that the exchange of partial sums between blocks happens while the whole tiles still stream;
+// a block then ends with a tile that it finishes alone.  The modes that leave partial sums to a later kernel
+// keep every tile shared (W = 0): their readers know that cut (gi_gemm_stream_geometry).
+struct Plan {
+  long shared_base, shared_units;   // the shared tiles' units are [shared_base, shared_base + shared_units)
+  int sharers;                      // blocks 0 .. sharers-1 cut them between themselves (every range non-empty)
+  long s_first, s_last;             // this block's range of them (absolute unit numbers)
+  long w_first, w_last;             // this block's whole tiles, as units
+};
+
+__device__ __forceinline__ Plan plan_of(int cta, int n_ctas, int n_tiles, int kb_per_tile, bool all_shared) {
+  Plan p;
+  const int W = all_shared ? 0 : n_tiles / n_ctas;
+  p.shared_base = (long)W * n_ctas * kb_per_tile;
+  p.shared_units = (long)(n_tiles - W * n_ctas) * kb_per_tile;
+  p.sharers = (int)min((long)n_ctas, p.shared_units);
+  p.s_first = p.s_last = p.shared_base;
+  if (cta < p.sharers) {
+    p.s_first = p.shared_base + (long)cta * p.shared_units / p.sharers;
+    p.s_last = p.shared_base + (long)(cta + 1) * p.shared_units / p.sharers;
+  }
+  p.w_first = (long)cta * W * kb_per_tile;
+  p.w_last = p.w_first + (long)W * kb_per_tile;
+  return p;
+}
+
 // The block whose range holds unit u: the largest c with floor(c * units / n) <= u.
 __device__ __forceinline__ int cta_of(long u, int n_ctas, long units) {
   return (int)(((u + 1) * n_ctas + units - 1) / units - 1);
@@ -51,7 +89,8 @@ __device__ __forceinline__ int cta_of(long u, int n_ctas, long units) {
 template <int NT, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, void* __restrict__ out_,
-                   float* __restrict__ scratch, int* __restrict__ counters, int M, int N, int K, long ldo, int use_pdl) {
+                   float* __restrict__ scratch, int* __restrict__ counters, int M, int N, int K, long ldo, int use_pdl,
+                   const __grid_constant__ CUtensorMap map_next, Next next) {
   constexpr uint32_t W_BYTES = TILE_ROWS * BK * 2, A_BYTES = NT * BK * 2, STAGE_BYTES = W_BYTES + A_BYTES;
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
   extern __shared__ unsigned char smem_raw[];
@@ -63,9 +102,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb_per_tile = (K + BK - 1) / BK;
   const int n_tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
-  const long units = (long)n_tiles * kb_per_tile;
   const int n_ctas = gridDim.x;
-  const Range mine = range_of(blockIdx.x, n_ctas, units);
+  const Plan plan = plan_of(blockIdx.x, n_ctas, n_tiles, kb_per_tile, MODE == GI_SKINNY_ACCUM_DEFER || MODE == GI_SKINNY_STORE_DEFER);
+  const long n_shared = plan.s_last - plan.s_first, n_mine = n_shared + (plan.w_last - plan.w_first);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
   const uint32_t accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
 
@@ -94,23 +133,41 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
-      // Weights do not depend on the kernel before this one: with programmatic launch their first stages are on
-      // their way while that kernel is still finishing; activations are only touched after the dependency wait.
-      long u = mine.first;
-      int it = 0;
+      // (tile, kb) of the running unit, advanced without divisions: this thread should spend its time issuing loads
+      long u = n_shared > 0 ? plan.s_first : plan.w_first;
+      int tile = (int)(u / kb_per_tile), kb = (int)(u % kb_per_tile);
+      auto advance = [&]() {
+        ++u;
+        if (++kb == kb_per_tile) {
+          kb = 0;
+          ++tile;
+        }
+        if (u == plan.s_last && plan.w_last > plan.w_first) {      // after the shared range: the whole tiles
+          u = plan.w_first;
+          tile = (int)(u / kb_per_tile);
+          kb = 0;
+        }
+      };
       bool ok = true;
-      const int ahead = use_pdl ? (int)min((long)STAGES, mine.last - mine.first) : 0;
-      for (int i = 0; i < ahead; ++i) {
-        const long uu = mine.first + i;
-        const int tile = (int)(uu / kb_per_tile), kb = (int)(uu % kb_per_tile);
-        mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
-        tma_load_2d(smem_u32(smem + (size_t)i * STAGE_BYTES), &map_w, kb * BK, tile * TILE_ROWS, full0 + 8 * i);
+      const int ahead = use_pdl ? (int)min((long)STAGES, n_mine) : 0;
+      {
+        // Weights do not depend on the kernel before this one: with programmatic launch their first stages are on
+        // their way while that kernel is still finishing; activations are only touched after the dependency wait.
+        const long u0 = u;
+        const int tile0 = tile, kb0 = kb;
+        for (int i = 0; i < ahead; ++i) {
+          mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+          tma_load_2d(smem_u32(smem + (size_t)i * STAGE_BYTES), &map_w, kb * BK, tile * TILE_ROWS, full0 + 8 * i);
+          advance();
+        }
+        u = u0;
+        tile = tile0;
+        kb = kb0;
       }
       if (use_pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
-      // (tile, kb) of the running unit, advanced without divisions: this thread should spend its time issuing loads
-      int tile = (int)(mine.first / kb_per_tile), kb = (int)(mine.first % kb_per_tile), s = 0;
+      int s = 0;
       uint32_t round = 0;
-      for (; u < mine.last && ok; ++u, ++it) {
+      for (long it = 0; it < n_mine && ok; ++it) {
         const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
         if (it >= ahead) {
           ok = mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, 1, &g_stream_status);
@@ -119,13 +176,24 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           tma_load_2d(dst, &map_w, kb * BK, tile * TILE_ROWS, full0 + 8 * s);
         }
         tma_load_2d(dst + W_BYTES, &map_a, kb * BK, 0, full0 + 8 * s);
-        if (++kb == kb_per_tile) {
-          kb = 0;
-          ++tile;
-        }
+        advance();
         if (++s == STAGES) {
           s = 0;
           ++round;
+        }
+      }
+      // This block's own loads are all on their way.  When the caller named the matrix that the next product in
+      // the stream will read, ask the L2 cache for the first units of that product's blocks now: the memory keeps
+      // streaming while this kernel drains and the next one starts, instead of idling across the boundary.
+      if (ok && next.units_ahead > 0) {
+        const int kbn = (next.K + BK - 1) / BK, tiles_n = (next.N + TILE_ROWS - 1) / TILE_ROWS;
+        for (int c = blockIdx.x; c < next.n_ctas; c += gridDim.x) {
+          const Plan pn = plan_of(c, next.n_ctas, tiles_n, kbn, next.all_shared != 0);
+          int left = next.units_ahead;
+          for (long uu = pn.s_first; uu < pn.s_last && left > 0; ++uu, --left)
+            tma_prefetch_l2_2d(&map_next, (int)(uu % kbn) * BK, (int)(uu / kbn) * TILE_ROWS);
+          for (long uu = pn.w_first; uu < pn.w_last && left > 0; ++uu, --left)
+            tma_prefetch_l2_2d(&map_next, (int)(uu % kbn) * BK, (int)(uu / kbn) * TILE_ROWS);
         }
       }
     }
@@ -133,32 +201,35 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (lane == 0) {
       int it = 0, seg = 0;
       bool ok = true;
-      long u = mine.first;
-      while (u < mine.last && ok) {
-        const int tile = (int)(u / kb_per_tile);
-        const long seg_end = min(mine.last, (long)(tile + 1) * kb_per_tile);
-        const int buf = seg & 1;
-        ok = mbar_wait(acce0 + 8 * buf, (((uint32_t)(seg >> 1)) & 1) ^ 1, 2, &g_stream_status);   // the buffer was drained
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t d = tmem + (uint32_t)(buf * 64);
-        bool first = true;
-        for (; u < seg_end; ++u, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(full0 + 8 * s, ((uint32_t)(it / STAGES)) & 1, 2, &g_stream_status);
+      for (int part = 0; part < 2; ++part) {                       // the shared range, then the whole tiles
+        long u = part ? plan.w_first : plan.s_first;
+        const long part_end = part ? plan.w_last : plan.s_last;
+        while (u < part_end && ok) {
+          const int tile = (int)(u / kb_per_tile);
+          const long seg_end = min(part_end, (long)(tile + 1) * kb_per_tile);
+          const int buf = seg & 1;
+          ok = mbar_wait(acce0 + 8 * buf, (((uint32_t)(seg >> 1)) & 1) ^ 1, 2, &g_stream_status);   // the buffer was drained
           if (!ok) break;
           tc_fence_after();
-          const uint32_t w_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
-          const uint64_t dw = smem_desc(w_addr), da = smem_desc(w_addr + W_BYTES);
+          const uint32_t d = tmem + (uint32_t)(buf * 64);
+          bool first = true;
+          for (; u < seg_end; ++u, ++it) {
+            const int s = it % STAGES;
+            ok = mbar_wait(full0 + 8 * s, ((uint32_t)(it / STAGES)) & 1, 2, &g_stream_status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t w_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+            const uint64_t dw = smem_desc(w_addr), da = smem_desc(w_addr + W_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            tc_mma(d, dw + (uint64_t)(2 * k), da + (uint64_t)(2 * k), IDESC, first ? 0u : 1u);
-            first = false;
+            for (int k = 0; k < BK / 16; ++k) {
+              tc_mma(d, dw + (uint64_t)(2 * k), da + (uint64_t)(2 * k), IDESC, first ? 0u : 1u);
+              first = false;
+            }
+            tc_commit(empty0 + 8 * s);
           }
-          tc_commit(empty0 + 8 * s);
+          if (ok) tc_commit(accf0 + 8 * buf);
+          ++seg;
         }
-        if (ok) tc_commit(accf0 + 8 * buf);
-        ++seg;
       }
     }
   } else {
@@ -167,12 +238,15 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int etid = (warp - 2) * 32 + lane;       // 0..127 among the epilogue threads
     int seg = 0;
     bool ok = true;
-    long u = mine.first;
+    const int first_shared_tile = (int)(plan.s_first / kb_per_tile);
     if (use_pdl) asm volatile("griddepcontrol.wait;" ::: "memory");    // outputs and scratch are shared with earlier kernels
-    while (u < mine.last && ok) {
+    for (int part = 0; part < 2; ++part) {
+    long u = part ? plan.w_first : plan.s_first;
+    const long part_end = part ? plan.w_last : plan.s_last;
+    while (u < part_end && ok) {
       const int tile = (int)(u / kb_per_tile);
       const long tile_first = (long)tile * kb_per_tile, tile_end = tile_first + kb_per_tile;
-      const long seg_end = min(mine.last, tile_end);
+      const long seg_end = min(part_end, tile_end);
       const bool whole = (u == tile_first && seg_end == tile_end);
       const int buf = seg & 1;
       ok = mbar_wait(accf0 + 8 * buf, ((uint32_t)(seg >> 1)) & 1, 3, &g_stream_status);
@@ -205,14 +279,15 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // leave the partial sums for the next reader of the output (the norm after a residual add, the rotary
         // kernel after the q/k/v product), which adds them in the order of the K ranges while it reads the row
         // anyway: no exchange between blocks here
-        const int which = (tile == (int)(mine.first / kb_per_tile)) ? 0 : 1;
+        const int which = (tile == first_shared_tile) ? 0 : 1;
         float* slot = scratch + ((size_t)blockIdx.x * 2 + which) * (TILE_ROWS * NT);
 #pragma unroll
         for (int m = 0; m < NT; ++m) __stcg(slot + m * TILE_ROWS + row, v[m]);
       } else if (!whole) {
         // a tile shared with other blocks: leave the partial sums, and see whether everyone else has left theirs
-        const int c_first = cta_of(tile_first, n_ctas, units), c_last = cta_of(tile_end - 1, n_ctas, units);
-        const int which = (tile == (int)(mine.first / kb_per_tile)) ? 0 : 1;
+        const int c_first = cta_of(tile_first - plan.shared_base, plan.sharers, plan.shared_units);
+        const int c_last = cta_of(tile_end - 1 - plan.shared_base, plan.sharers, plan.shared_units);
+        const int which = (tile == first_shared_tile) ? 0 : 1;
         float* slot = scratch + ((size_t)blockIdx.x * 2 + which) * (TILE_ROWS * NT);
 #pragma unroll
         for (int m = 0; m < NT; ++m) __stcg(slot + m * TILE_ROWS + row, v[m]);
@@ -232,7 +307,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
           for (int m = 0; m < NT; ++m) v[m] = 0.f;
           for (int c = c_first; c <= c_last; ++c) {      // in the order of the K ranges
-            const int wh = (tile == (int)(range_of(c, n_ctas, units).first / kb_per_tile)) ? 0 : 1;
+            const int wh = (tile == (int)((plan.shared_base + range_of(c, plan.sharers, plan.shared_units).first) / kb_per_tile)) ? 0 : 1;
             const float* src = scratch + ((size_t)c * 2 + wh) * (TILE_ROWS * NT);
 #pragma unroll
             for (int m = 0; m < NT; ++m) v[m] += __ldcg(src + m * TILE_ROWS + row);
@@ -271,6 +346,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       u = seg_end;
       ++seg;
     }
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -293,7 +369,7 @@ int sm_count() {
 
 template <int NT, int STAGES, int MODE>
 int launch(void* out, const CUtensorMap& mw, const CUtensorMap& ma, float* scratch, int* counters, int M, int N, int K, long ldo,
-           int use_pdl, cudaStream_t s) {
+           int use_pdl, cudaStream_t s, const CUtensorMap& mn, Next next) {
   constexpr size_t smem = (size_t)STAGES * (TILE_ROWS * BK * 2 + NT * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
   auto kern = gemm_stream_kernel<NT, STAGES, MODE>;
   static bool configured = false;
@@ -314,21 +390,21 @@ int launch(void* out, const CUtensorMap& mw, const CUtensorMap& ma, float* scrat
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = use_pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, ma, out, scratch, counters, M, N, K, ldo, use_pdl);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, ma, out, scratch, counters, M, N, K, ldo, use_pdl, mn, next);
   if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "streamed product: %s", cudaGetErrorString(e));
   return GI_OK;
 }
 
 template <int NT, int STAGES>
 int launch_mode(int mode, void* out, const CUtensorMap& mw, const CUtensorMap& ma, float* scratch, int* counters, int M, int N,
-                int K, long ldo, int use_pdl, cudaStream_t s) {
+                int K, long ldo, int use_pdl, cudaStream_t s, const CUtensorMap& mn, Next next) {
   switch (mode) {
-    case GI_SKINNY_STORE_BF16: return launch<NT, STAGES, GI_SKINNY_STORE_BF16>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
-    case GI_SKINNY_STORE_F32: return launch<NT, STAGES, GI_SKINNY_STORE_F32>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
-    case GI_SKINNY_ACCUM_F32: return launch<NT, STAGES, GI_SKINNY_ACCUM_F32>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
-    case GI_SKINNY_SWIGLU: return launch<NT, STAGES, GI_SKINNY_SWIGLU>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
-    case GI_SKINNY_ACCUM_DEFER: return launch<NT, STAGES, GI_SKINNY_ACCUM_DEFER>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
-    case GI_SKINNY_STORE_DEFER: return launch<NT, STAGES, GI_SKINNY_STORE_DEFER>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
+    case GI_SKINNY_STORE_BF16: return launch<NT, STAGES, GI_SKINNY_STORE_BF16>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
+    case GI_SKINNY_STORE_F32: return launch<NT, STAGES, GI_SKINNY_STORE_F32>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
+    case GI_SKINNY_ACCUM_F32: return launch<NT, STAGES, GI_SKINNY_ACCUM_F32>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
+    case GI_SKINNY_SWIGLU: return launch<NT, STAGES, GI_SKINNY_SWIGLU>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
+    case GI_SKINNY_ACCUM_DEFER: return launch<NT, STAGES, GI_SKINNY_ACCUM_DEFER>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
+    case GI_SKINNY_STORE_DEFER: return launch<NT, STAGES, GI_SKINNY_STORE_DEFER>(out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
   }
   return gi::fail(GI_ERR_ARG, "streamed product: unknown mode %d", mode);
 }
@@ -342,6 +418,13 @@ extern "C" long gi_gemm_stream_scratch_floats(void) { return (long)sm_count() * 
 extern "C" int gi_gemm_stream_bf16(void* out, int mode, const void* A, const void* W, float* scratch, int* counters,
                                    int n_counters, int M, int N, int K, long lda, long ldw, long ldo, int use_pdl,
                                    void* stream) {
+  return gi_gemm_stream_bf16_ex(out, mode, A, W, scratch, counters, n_counters, M, N, K, lda, ldw, ldo, use_pdl, nullptr, 0, 0, 0, 0, 0, stream);
+}
+
+extern "C" int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const void* W, float* scratch, int* counters,
+                                      int n_counters, int M, int N, int K, long lda, long ldw, long ldo, int use_pdl,
+                                      const void* next_W, int next_N, int next_K, long next_ldw, int next_mode,
+                                      int units_ahead, void* stream) {
   if (M <= 0 || N <= 0) return GI_OK;
   if (M > 64) return gi::fail(GI_ERR_UNSUPPORTED, "streamed product: %d rows of activations, at most 64", M);
   if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0)
@@ -358,10 +441,21 @@ extern "C" int gi_gemm_stream_bf16(void* out, int mode, const void* A, const voi
   if (rc != GI_OK) return rc;
   rc = gi::tensor_map_2d(&ma, A, M, K, lda, nt);
   if (rc != GI_OK) return rc;
+  // the next product's matrix, if the caller knows it and it can have a tensor map; otherwise nothing is fetched ahead
+  Next next = {0, 0, 0, 0, 0};
+  CUtensorMap mn = mw;
+  if (next_W && units_ahead > 0 && next_N > 0 && next_K > 0 && next_K % 8 == 0 && next_ldw % 8 == 0 && !((uintptr_t)next_W & 15) &&
+      gi::tensor_map_2d(&mn, next_W, next_N, next_K, next_ldw, TILE_ROWS) == GI_OK) {
+    const long units_n = (long)((next_N + TILE_ROWS - 1) / TILE_ROWS) * ((next_K + BK - 1) / BK);
+    next = {next_N, next_K, (int)(units_n < sm_count() ? units_n : sm_count()), units_ahead,
+            (next_mode == GI_SKINNY_ACCUM_DEFER || next_mode == GI_SKINNY_STORE_DEFER) ? 1 : 0};
+  } else {
+    mn = mw;
+  }
   cudaStream_t s = (cudaStream_t)stream;
-  if (nt == 16) return launch_mode<16, 10>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
-  if (nt == 32) return launch_mode<32, 9>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
-  return launch_mode<64, 8>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s);
+  if (nt == 16) return launch_mode<16, 10>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
+  if (nt == 32) return launch_mode<32, 9>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
+  return launch_mode<64, 8>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
 }
 
 // How a launch with these sizes cuts its work: blocks, units per tile, token-tile width.  The kernel that settles

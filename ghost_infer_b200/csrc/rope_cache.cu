@@ -25,24 +25,23 @@ __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restr
 }
 
 // The value of column f of token t's packed row: what the product stored, or, for a tile of 128 columns that was cut
-// between blocks of a deferred product, the sum of the partial sums in the order of the K ranges, rounded to T.
+// between blocks of a deferred product (`sp`, looked up before the dependency wait), the sum of the partial sums in
+// the order of the K ranges, rounded to T.
 template <typename T>
-__device__ __forceinline__ float row_value(const T* row, const gi_settle_t& st, int t, int f) {
-  if (st.partials != nullptr) {
-    const int tile = f / 128, r = f % 128;
-    const int c_first = st.tile_first_cta[tile], c_last = st.tile_last_cta[tile];
-    if (c_first != c_last) {
-      float acc = 0.f;
-      for (int c = c_first; c <= c_last; ++c) {
-        const int which = (tile == st.cta_first_tile[c]) ? 0 : 1;
-        acc += __ldcg(st.partials + ((size_t)c * 2 + which) * (128 * st.nt) + (size_t)t * 128 + r);
-      }
-      T rounded;
-      gi::stf(&rounded, acc);
-      return gi::ldf(&rounded);
-    }
+__device__ __forceinline__ float row_value(const T* row, const gi_settle_t& st, const gi_settle_span& sp, int t, int f) {
+  if (sp.c_first != sp.c_last) {
+    float acc = 0.f;
+    for (int c = sp.c_first; c <= sp.c_last; ++c) acc += __ldcg(gi_piece(st, sp, c, t, f));
+    T rounded;
+    gi::stf(&rounded, acc);
+    return gi::ldf(&rounded);
   }
   return gi::ldf(row + f);
+}
+__device__ __forceinline__ gi_settle_span span_or_none(const gi_settle_t& st, int f) {
+  if (st.partials != nullptr) return gi_span_of(st, f);
+  gi_settle_span none = {0, 0, 0};
+  return none;
 }
 
 // One block per (token, head of the packed row): heads 0..H-1 are queries (rotated in place), H..H+KV-1 keys
@@ -52,42 +51,51 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* __
                                   const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int n_heads, int n_kv, int hd, int rot,
                                   int adjacent, int write_cache, gi_settle_t st) {
-  gi::pdl_prologue();
+  // Positions, slots, the block table and the tables of the product's cut were uploaded before the step's first
+  // kernel: they are read while the product before this kernel drains.  The rows, the partial sums and the angle
+  // table (written by a kernel of this step) are read after the dependency wait.
+  gi::pdl_launch_dependents();
   const int t = blockIdx.x, head = blockIdx.y;
   const int half = rot / 2;
   T* row = qkv + (size_t)t * ld;
   const int col0 = head * hd;
   T* src = row + col0;
-  if (head < n_heads) {
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-      const int ia = adjacent ? 2 * i : i, ib = adjacent ? 2 * i + 1 : i + half;
-      const float a = row_value(row, st, t, col0 + ia), b = row_value(row, st, t, col0 + ib);
-      const float2 f = table[(size_t)t * half + i];
-      gi::stf(src + ia, a * f.x - b * f.y);
-      gi::stf(src + ib, a * f.y + b * f.x);
-    }
-    if (st.partials != nullptr)     // queries past the rotated part still have to land in the row the attention reads
-      for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) gi::stf(src + d, row_value(row, st, t, col0 + d));
-    return;
+  T* dst = src;                                 // queries are rotated in place
+  if (head >= n_heads) {
+    if (!write_cache) return;
+    const int pos = positions[t], slot = slots[t];
+    // a padding row (slot < 0) writes to the trash page, which no live sequence reads
+    const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + pos / PAGE_TOKENS] : 0;
+    const int off = pos % PAGE_TOKENS;
+    const bool is_k = head < n_heads + n_kv;
+    dst = (is_k ? kcache : vcache) + (((size_t)page * n_kv + (head - n_heads - (is_k ? 0 : n_kv))) * PAGE_TOKENS + off) * hd;
   }
-  if (!write_cache) return;
-  const int pos = positions[t], slot = slots[t];
-  // a padding row (slot < 0) writes to the trash page, which no live sequence reads
-  const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + pos / PAGE_TOKENS] : 0;
-  const int off = pos % PAGE_TOKENS;
-  if (head < n_heads + n_kv) {
-    T* dst = kcache + (((size_t)page * n_kv + (head - n_heads)) * PAGE_TOKENS + off) * hd;
+  const bool rotate = head < n_heads + n_kv;
+  // the first two columns this thread reads (one pair, or two values): their spans are looked up before the wait
+  const int i0 = threadIdx.x;
+  const int e0 = rotate ? (adjacent ? 2 * i0 : i0) : i0;
+  const int e1 = rotate ? (adjacent ? 2 * i0 + 1 : i0 + half) : i0 + (int)blockDim.x;
+  gi_settle_span sp0 = {0, 0, 0}, sp1 = {0, 0, 0};
+  if (e0 < hd) sp0 = span_or_none(st, col0 + e0);
+  if (e1 < hd) sp1 = span_or_none(st, col0 + e1);
+  gi::pdl_wait();
+  if (rotate) {
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
       const int ia = adjacent ? 2 * i : i, ib = adjacent ? 2 * i + 1 : i + half;
-      const float a = row_value(row, st, t, col0 + ia), b = row_value(row, st, t, col0 + ib);
+      const gi_settle_span sa = (i == i0) ? sp0 : span_or_none(st, col0 + ia), sb = (i == i0) ? sp1 : span_or_none(st, col0 + ib);
+      const float a = row_value(row, st, sa, t, col0 + ia), b = row_value(row, st, sb, t, col0 + ib);
       const float2 f = table[(size_t)t * half + i];
       gi::stf(dst + ia, a * f.x - b * f.y);
       gi::stf(dst + ib, a * f.y + b * f.x);
     }
-    for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) gi::stf(dst + d, row_value(row, st, t, col0 + d));   // past the rotated part: as it is
+    // past the rotated part: as it is (queries only when they are still partial sums: the attention reads the row)
+    if (head >= n_heads || st.partials != nullptr)
+      for (int d = rot + threadIdx.x; d < hd; d += blockDim.x) gi::stf(dst + d, row_value(row, st, span_or_none(st, col0 + d), t, col0 + d));
   } else {
-    T* dst = vcache + (((size_t)page * n_kv + (head - n_heads - n_kv)) * PAGE_TOKENS + off) * hd;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) gi::stf(dst + d, row_value(row, st, t, col0 + d));
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+      const gi_settle_span sd = (d == e0) ? sp0 : ((d == e1) ? sp1 : span_or_none(st, col0 + d));
+      gi::stf(dst + d, row_value(row, st, sd, t, col0 + d));
+    }
   }
 }
 

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
+import weakref
 from ctypes import c_float, c_int, c_long, c_void_p
 from typing import Dict, Optional
 
@@ -52,6 +53,7 @@ def _bind():
         "gi_attn_prefill_generic": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_gemm_stream_bf16": [P, I, P, P, P, P, I, I, I, I, L, L, L, I, P],
+        "gi_gemm_stream_bf16_ex": [P, I, P, P, P, P, I, I, I, I, L, L, L, I, P, I, I, L, I, I, P],
         "gi_gemm_stream_status": [P],
         "gi_gemm_tc_bf16": [P, I, P, P, I, I, I, L, L, L, I, P],
         "gi_gemm_tc_status": [P],
@@ -223,9 +225,9 @@ def _gemm_stream_deferred(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m
     m, k = a.shape
     n = w.shape[0]
     _, counters = _stream_buffers(a.device)
-    _check(lib, lib.gi_gemm_stream_bf16(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), scratch.data_ptr(),
-                                        counters.data_ptr(), counters.numel(), m, n, k, a.stride(0), w.stride(0),
-                                        out.stride(0), -1, _stream()))
+    _check(lib, lib.gi_gemm_stream_bf16_ex(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), scratch.data_ptr(),
+                                           counters.data_ptr(), counters.numel(), m, n, k, a.stride(0), w.stride(0),
+                                           out.stride(0), -1, *_next_weights(w, mode), _stream()))
     n_ctas, kb, nt = c_int(0), c_int(0), c_int(0)
     lib.gi_gemm_stream_geometry(m, n, k, ctypes.byref(n_ctas), ctypes.byref(kb), ctypes.byref(nt))
     tabs = _settle_tables(a.device, (n + 127) // 128, kb.value, n_ctas.value)
@@ -328,7 +330,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 
 
 # Choices measured on a B200; benchmarks may override them to try alternatives.
-TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True}
+TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -384,10 +386,34 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
     scratch, counters = _stream_buffers(a.device)
     if (n + 127) // 128 > counters.numel():
         raise KernelError(f"the streamed product takes at most {counters.numel() * 128} rows of weights")
-    _check(lib, lib.gi_gemm_stream_bf16(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), scratch.data_ptr(),
-                                        counters.data_ptr(), counters.numel(), m, n, k, lda, ldw, ldo,
-                                        -1 if pdl is None else int(pdl), _stream()))
+    _check(lib, lib.gi_gemm_stream_bf16_ex(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), scratch.data_ptr(),
+                                           counters.data_ptr(), counters.numel(), m, n, k, lda, ldw, ldo,
+                                           -1 if pdl is None else int(pdl), *_next_weights(w, mode), _stream()))
     return out
+
+
+# ---- which matrix the next streamed product reads -----------------------------------------------------
+# A decode step runs the same products in the same order every time.  Each streamed product remembers which
+# matrix followed it the last time and tells its kernel, which asks the L2 cache for that matrix's first units
+# while it drains, so the memory does not idle across the kernel boundary.  A wrong guess only costs bandwidth.
+_followed_by: Dict[int, tuple] = {}            # weights' address -> (weak reference to the next weights, that product's mode)
+_last_streamed: Optional[int] = None
+
+
+def _next_weights(w: torch.Tensor, mode: int):
+    """(pointer, rows, columns, row stride, mode, units ahead) of the product that followed `w`'s last time, or nothing."""
+    global _last_streamed
+    here = w.data_ptr()
+    if _last_streamed is not None and _last_streamed != here:
+        _followed_by[_last_streamed] = (weakref.ref(w), mode)
+    _last_streamed = here
+    ref, next_mode = _followed_by.get(here, (None, 0))
+    nxt = ref() if ref is not None else None
+    ahead = int(TUNE["prefetch_units"])
+    if (nxt is None or ahead <= 0 or nxt.dtype != torch.bfloat16 or nxt.dim() != 2 or nxt.stride(1) != 1
+            or nxt.device != w.device):
+        return None, 0, 0, 0, 0, 0
+    return nxt.data_ptr(), nxt.shape[0], nxt.shape[1], nxt.stride(0), next_mode, ahead
 
 
 def gemm_stream_status() -> int:

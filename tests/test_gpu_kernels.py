@@ -418,7 +418,7 @@ def test_gemm_tensor_cores_swiglu(tile_n, m, f, k):
 
 @pytest.mark.parametrize("pdl", [False, True])
 @pytest.mark.parametrize("m", [1, 8, 13, 16, 17, 32, 50, 64])
-@pytest.mark.parametrize("n,k", [(100, 72), (128, 64), (6144, 4096), (4096, 14336), (1000, 520), (40000, 264)])
+@pytest.mark.parametrize("n,k", [(100, 72), (128, 64), (6144, 4096), (4096, 14336), (1000, 520), (40000, 264), (19100, 200)])
 def test_gemm_stream(pdl, m, n, k):
     """The persistent stream-K decode product: tiles cut between blocks (summed by whoever arrives last, in
     K order), rows of W that stop inside a tile, K that stops inside a block, every token-tile width."""
