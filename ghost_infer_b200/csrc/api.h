@@ -42,6 +42,54 @@ __device__ __forceinline__ const float* gi_piece(const gi_settle_t& st, const gi
   const int slot = (c == s.c_first) ? s.first_slot : 0;
   return st.partials + ((size_t)c * 2 + slot) * (128 * st.nt) + (size_t)m * 128 + f % 128;
 }
+// The sum of a column's pieces in the order of the K ranges.  The loads of up to eight pieces are issued together
+// (absent ones count as +0, which changes no sum), so that the sum costs one trip to the L2 cache, not one per piece.
+__device__ __forceinline__ float gi_sum_pieces(const gi_settle_t& st, const gi_settle_span& s, int m, int f) {
+  float acc = 0.f;
+  for (int c0 = s.c_first; c0 <= s.c_last; c0 += 8) {
+    float p[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p[j] = (c0 + j <= s.c_last) ? __ldcg(gi_piece(st, s, c0 + j, m, f)) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += p[j];
+  }
+  return acc;
+}
+// Two columns of the same tile at once (a rotated pair): both columns' loads are in flight together.
+__device__ __forceinline__ float2 gi_sum_pieces2(const gi_settle_t& st, const gi_settle_span& s, int m, int fa, int fb) {
+  float2 acc = make_float2(0.f, 0.f);
+  for (int c0 = s.c_first; c0 <= s.c_last; c0 += 8) {
+    float pa[8], pb[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      pa[j] = (c0 + j <= s.c_last) ? __ldcg(gi_piece(st, s, c0 + j, m, fa)) : 0.f;
+      pb[j] = (c0 + j <= s.c_last) ? __ldcg(gi_piece(st, s, c0 + j, m, fb)) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      acc.x += pa[j];
+      acc.y += pb[j];
+    }
+  }
+  return acc;
+}
+__device__ __forceinline__ float4 gi_sum_pieces4(const gi_settle_t& st, const gi_settle_span& s, int m, int f) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = s.c_first; c0 <= s.c_last; c0 += 8) {
+    float4 p[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      p[j] = (c0 + j <= s.c_last) ? __ldcg(reinterpret_cast<const float4*>(gi_piece(st, s, c0 + j, m, f))) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      acc.x += p[j].x;
+      acc.y += p[j].y;
+      acc.z += p[j].z;
+      acc.w += p[j].w;
+    }
+  }
+  return acc;
+}
 #endif
 
 const char* gi_last_error(void);

@@ -22,16 +22,8 @@ __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ tab
 // 128 features whose K range was cut between blocks c_first..c_last has one slot per block; they are added in
 // the order of the K ranges, so the result does not depend on any timing).  f is a multiple of 4.
 __device__ __forceinline__ float4 pending_sum(const gi_settle_t& st, const gi_settle_span& sp, int m, int f) {
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (sp.c_first == sp.c_last) return acc;                 // one block had the whole tile and added it itself
-  for (int c = sp.c_first; c <= sp.c_last; ++c) {
-    const float4 p = __ldcg(reinterpret_cast<const float4*>(gi_piece(st, sp, c, m, f)));
-    acc.x += p.x;
-    acc.y += p.y;
-    acc.z += p.z;
-    acc.w += p.w;
-  }
-  return acc;
+  if (sp.c_first == sp.c_last) return make_float4(0.f, 0.f, 0.f, 0.f);   // one block had the whole tile and added it itself
+  return gi_sum_pieces4(st, sp, m, f);
 }
 
 // x[row, :] += pending partial sums (for readers of the residual stream that do not settle on their own).

@@ -30,8 +30,7 @@ __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restr
 template <typename T>
 __device__ __forceinline__ float row_value(const T* row, const gi_settle_t& st, const gi_settle_span& sp, int t, int f) {
   if (sp.c_first != sp.c_last) {
-    float acc = 0.f;
-    for (int c = sp.c_first; c <= sp.c_last; ++c) acc += __ldcg(gi_piece(st, sp, c, t, f));
+    const float acc = gi_sum_pieces(st, sp, t, f);
     T rounded;
     gi::stf(&rounded, acc);
     return gi::ldf(&rounded);
