@@ -212,22 +212,24 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
   gi::cp_async_wait<0>();
   __syncthreads();
 
-  // merge the warps (reusing the ring): natural-log maxima so that the combine kernel can go on
-  float* Mo = reinterpret_cast<float*>(ring);            // [WARPS][16][HD]
-  float* Mm = Mo + WARPS * 16 * HD;                      // [WARPS][16]
+  // merge the warps (reusing the ring): natural-log maxima so that the combine kernel can go on.  Only the rows
+  // that hold a head are written (a group of 4 heads uses 4 of the tile's 16 rows); rows are HD + 8 floats apart,
+  // which spreads the eight rows a warp writes at once over the banks.
+  constexpr int MROW = HD + 8;
+  float* Mo = reinterpret_cast<float*>(ring);            // [WARPS][16][MROW]
+  float* Mm = Mo + WARPS * 16 * MROW;                    // [WARPS][16]
   float* Ml = Mm + WARPS * 16;                           // [WARPS][16]
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = g + h * 8;
+    if (r >= gcount) continue;
     if (t == 0) {
       Mm[warp * 16 + r] = m_run[h];
       Ml[warp * 16 + r] = l_run[h];
     }
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-      Mo[(warp * 16 + r) * HD + i * 8 + 2 * t] = o[i][h * 2];
-      Mo[(warp * 16 + r) * HD + i * 8 + 2 * t + 1] = o[i][h * 2 + 1];
-    }
+    for (int i = 0; i < HD / 8; ++i)
+      *reinterpret_cast<float2*>(Mo + (warp * 16 + r) * MROW + i * 8 + 2 * t) = make_float2(o[i][h * 2], o[i][h * 2 + 1]);
   }
   __syncthreads();
   for (int idx = tid; idx < gcount * HD; idx += WARPS * 32) {
@@ -243,7 +245,7 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
         if (mw == -INFINITY) continue;
         const float wgt = exp2f(mw - mm);
         tot += Ml[w * 16 + r] * wgt;
-        val += Mo[(w * 16 + r) * HD + d] * wgt;
+        val += Mo[(w * 16 + r) * MROW + d] * wgt;
       }
     }
     const int h = h0 + r;
@@ -265,7 +267,7 @@ int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, f
            const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int max_pages, const int* slots, const int* lens,
            int H, int KV, float scale, int window, int n_splits) {
   constexpr size_t ring = (size_t)WARPS * STAGES * 2 * KT * HD * 2;
-  constexpr size_t merge = (size_t)(WARPS * 16 * HD + 2 * WARPS * 16) * sizeof(float);
+  constexpr size_t merge = (size_t)(WARPS * 16 * (HD + 8) + 2 * WARPS * 16) * sizeof(float);
   constexpr size_t smem = 16 * HD * 2 + (ring > merge ? ring : merge);
   auto kern = attn_decode_tc_kernel<HD, KT, STAGES>;
   static bool configured = false;

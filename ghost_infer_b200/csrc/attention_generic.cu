@@ -268,20 +268,39 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
 template <typename T>
 __global__ void attn_combine_kernel(T* __restrict__ out, long ldo, const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, int n_heads, int hd, int n_splits) {
+  // The loads of eight slices are issued together (a slice past the end counts as an empty one): the merge costs
+  // a trip or two to the L2 cache, not one per slice.  The arithmetic and its order are those of a plain loop.
   gi::pdl_prologue();
   const int b = blockIdx.y, h = blockIdx.x;
   const size_t p0 = ((size_t)b * n_heads + h) * n_splits;
+  const float2* ml = reinterpret_cast<const float2*>(part_ml) + p0;
   float mm = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[(p0 + s) * 2]);
+  for (int s0 = 0; s0 < n_splits; s0 += 8) {
+    float m8[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m8[j] = (s0 + j < n_splits) ? __ldcg(ml + s0 + j).x : -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mm = fmaxf(mm, m8[j]);
+  }
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float tot = 0.f, val = 0.f;
     if (mm != -INFINITY) {
-      for (int s = 0; s < n_splits; ++s) {
-        const float ms = part_ml[(p0 + s) * 2];
-        if (ms == -INFINITY) continue;
-        const float w = expf(ms - mm);
-        tot += part_ml[(p0 + s) * 2 + 1] * w;
-        val += part_o[(p0 + s) * hd + d] * w;
+      for (int s0 = 0; s0 < n_splits; s0 += 8) {
+        float2 m8[8];
+        float o8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const bool in = s0 + j < n_splits;
+          m8[j] = in ? __ldcg(ml + s0 + j) : make_float2(-INFINITY, 0.f);
+          o8[j] = in ? __ldcg(part_o + (p0 + s0 + j) * hd + d) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (m8[j].x == -INFINITY) continue;
+          const float w = expf(m8[j].x - mm);
+          tot += m8[j].y * w;
+          val += o8[j] * w;
+        }
       }
     }
     gi::stf(out + (size_t)b * ldo + (size_t)h * hd + d, tot > 0.f ? val / tot : 0.f);
