@@ -129,6 +129,34 @@ def model_numbers(cfg, layers):
             "kv_bytes_per_token": 2 * layers * KV * hd * 2}
 
 
+def decode_timeline(ops, decode_run, layers, steps, warmup):
+    """Prints, for the last decode step's streamed products (q/k/v, o, gate/up, down of every layer, then the head), the
+    times of their blocks' stamps relative to the end of the product before: how long the kernels between two
+    products take (the wait), how long a product streams, how far its blocks' ends spread."""
+    import numpy as np
+    per_step = 4 * layers + 1
+    ops.stream_timeline_start(2 * per_step)
+    decode_run(8, steps, warmup)
+    tl, n = ops.stream_timeline_stop()
+    live = [i for i in range(tl.shape[0]) if tl[i, :, 0].max() > 0]
+    order = sorted(live, key=lambda i: tl[i, :, 0][tl[i, :, 0] > 0].min())[-per_step:]
+    names = ["q/k/v", "o", "gate/up", "down"]
+    print(f"{n} launches stamped; the last step's {len(order)} streamed products, microseconds after the end of the product before")
+    print(f"{'product':8s} {'first entry':>11s} {'wait over':>10s} {'first stage':>11s} {'last load':>10s} {'last product (min/med/max)':>27s} {'end (med/max)':>15s}")
+    prev_end = None
+    for k, i in enumerate(order):
+        used = tl[i, :, 0] > 0
+        t = tl[i, used, :]
+        if prev_end is None:
+            prev_end = t[:, 0].min()
+        e = (t - prev_end).astype(np.float64) / 1e3          # the subtraction in integers: the clock's values need 61 bits
+        name = names[k % 4] if k < len(order) - 1 else "head"
+        print(f"{name:8s} {e[:, 0].min():11.2f} {np.median(e[:, 3]):10.2f} {np.median(e[:, 4]):11.2f} {np.median(e[:, 5]):10.2f} "
+              f"{e[:, 6].min():9.2f}/{np.median(e[:, 6]):7.2f}/{e[:, 6].max():7.2f} {np.median(e[:, 7]):7.2f}/{e[:, 7].max():7.2f}")
+        prev_end = t[:, 7].max()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -139,8 +167,9 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b"], help="8b: the headline; 1b, 3b: the baseline's other workloads")
     ap.add_argument("--tune", default="", help="overrides of kernel choices, e.g. small_skinny=0,attn_waves=2")
-    ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
-                    help="run one phase alone and print its time (a short program for a launch list under a profiler; no bench line)")
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode", "timeline"],
+                    help="run one phase alone and print its time (a short program for a launch list under a profiler; no bench "
+                         "line).  timeline: a table of when the streamed products of a decode step start, wait, stream and end")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another (no programmatic dependent launch)")
     args = ap.parse_args()
 
@@ -214,6 +243,8 @@ def main():
             cache.close_slot(s)
         return ms, launched, ctx_tokens
 
+    if args.only == "timeline":
+        return decode_timeline(ops, decode_run, layers, K, W)
     if args.only == "decode":
         ms, n, _ = decode_run(8, K, W)
         print(json.dumps({"only": "decode", "layers": layers, "batch": 8, "ms_per_step": round(ms, 4), "launches_per_step": n // K}))

@@ -135,6 +135,8 @@ int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const void* W, fl
                            int M, int N, int K, long lda, long ldw, long ldo, int use_pdl, const void* next_W, int next_N,
                            int next_K, long next_ldw, int next_mode, int units_ahead, void* stream);
 int gi_gemm_stream_status(int* status);
+// Time stamps of the streamed products' blocks, for a timeline of a decode step: see gemm_stream.cu.
+long gi_gemm_stream_timeline(unsigned long long* buf, int slots);
 int gi_gemm_stream_geometry(int M, int N, int K, int* n_ctas, int* kb_per_tile, int* nt);
 
 // x[rows, :] += the partial sums, in the order of the K ranges.  rows: optional selection; n_features = width of x.

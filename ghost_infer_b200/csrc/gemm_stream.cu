@@ -32,6 +32,18 @@ using namespace gi::tc;
 constexpr int TILE_ROWS = 128;   // rows of W per tile = tensor-memory lanes
 constexpr int BK = 64;           // K columns per unit = one 128-byte swizzle row
 constexpr int THREADS = 192;     // warp 0: TMA, warp 1: MMA + tensor-memory allocation, warps 2-5: epilogue
+
+// Time stamps for a timeline of a decode step (gi_gemm_stream_timeline): when a launch carries a buffer, each block
+// notes the nanosecond clock at eight places of its life.  Without one (the usual case) a stamp is a predicated-off store.
+constexpr int TL_EVENTS = 8;       // 0 entry, 1 set up, 2 the SM's number, 3 dependency wait over, 4 first stage landed,
+                                   // 5 last load issued, 6 last product issued, 7 last epilogue done
+constexpr int TL_BLOCKS = 256;     // blocks per launch that a buffer has room for
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TL(ev) do { if (next.timeline != nullptr && blockIdx.x < TL_BLOCKS) next.timeline[blockIdx.x * TL_EVENTS + (ev)] = gtime(); } while (0)
 constexpr int TMEM_COLS = 128;   // two accumulator buffers of up to 64 columns
 
 __device__ int g_stream_status = 0;
@@ -40,6 +52,7 @@ __device__ int g_stream_status = 0;
 // (all_shared: it runs in a mode that leaves partial sums to a later kernel).
 struct Next {
   int N, K, n_ctas, units_ahead, all_shared;
+  unsigned long long* timeline;   // this launch's [TL_BLOCKS][TL_EVENTS] stamps, or null
 };
 
 struct Range {
@@ -99,6 +112,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
   int* last_flag = (int*)(tmem_slot + 1);
 
+  if (threadIdx.x == 0) TL(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb_per_tile = (K + BK - 1) / BK;
   const int n_tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
@@ -133,6 +147,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
+      TL(1);
       // (tile, kb) of the running unit, advanced without divisions: this thread should spend its time issuing loads
       long u = n_shared > 0 ? plan.s_first : plan.w_first;
       int tile = (int)(u / kb_per_tile), kb = (int)(u % kb_per_tile);
@@ -164,7 +179,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tile = tile0;
         kb = kb0;
       }
+      if (next.timeline != nullptr && blockIdx.x < TL_BLOCKS) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        next.timeline[blockIdx.x * TL_EVENTS + 2] = smid;
+      }
       if (use_pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+      TL(3);
       int s = 0;
       uint32_t round = 0;
       for (long it = 0; it < n_mine && ok; ++it) {
@@ -182,6 +203,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           ++round;
         }
       }
+      TL(5);
       // This block's own loads are all on their way.  When the caller named the matrix that the next product in
       // the stream will read, ask the L2 cache for the first units of that product's blocks now: the memory keeps
       // streaming while this kernel drains and the next one starts, instead of idling across the boundary.
@@ -217,6 +239,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int s = it % STAGES;
             ok = mbar_wait(full0 + 8 * s, ((uint32_t)(it / STAGES)) & 1, 2, &g_stream_status);
             if (!ok) break;
+            if (it == 0) TL(4);
             tc_fence_after();
             const uint32_t w_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
             const uint64_t dw = smem_desc(w_addr), da = smem_desc(w_addr + W_BYTES);
@@ -231,6 +254,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           ++seg;
         }
       }
+      TL(6);
     }
   } else {
     const int quarter = warp & 3;
@@ -347,6 +371,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       ++seg;
     }
     }
+    if (etid == 0) TL(7);
   }
   tc_fence_before();
   __syncthreads();
@@ -411,6 +436,10 @@ int launch_mode(int mode, void* out, const CUtensorMap& mw, const CUtensorMap& m
 
 }  // namespace
 
+static unsigned long long* g_timeline = nullptr;
+static int g_timeline_slots = 1;
+static long g_timeline_launches = 0;
+
 // Scratch the caller provides: `scratch` holds gi_gemm_stream_scratch_floats() floats (partial sums of tiles cut
 // between blocks), `counters` one int per 128-row tile of W, zero before the first use (the kernel leaves them zero).
 extern "C" long gi_gemm_stream_scratch_floats(void) { return (long)sm_count() * 2 * TILE_ROWS * 64; }
@@ -442,16 +471,17 @@ extern "C" int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const 
   rc = gi::tensor_map_2d(&ma, A, M, K, lda, nt);
   if (rc != GI_OK) return rc;
   // the next product's matrix, if the caller knows it and it can have a tensor map; otherwise nothing is fetched ahead
-  Next next = {0, 0, 0, 0, 0};
+  Next next = {0, 0, 0, 0, 0, nullptr};
   CUtensorMap mn = mw;
   if (next_W && units_ahead > 0 && next_N > 0 && next_K > 0 && next_K % 8 == 0 && next_ldw % 8 == 0 && !((uintptr_t)next_W & 15) &&
       gi::tensor_map_2d(&mn, next_W, next_N, next_K, next_ldw, TILE_ROWS) == GI_OK) {
     const long units_n = (long)((next_N + TILE_ROWS - 1) / TILE_ROWS) * ((next_K + BK - 1) / BK);
     next = {next_N, next_K, (int)(units_n < sm_count() ? units_n : sm_count()), units_ahead,
-            (next_mode == GI_SKINNY_ACCUM_DEFER || next_mode == GI_SKINNY_STORE_DEFER) ? 1 : 0};
+            (next_mode == GI_SKINNY_ACCUM_DEFER || next_mode == GI_SKINNY_STORE_DEFER) ? 1 : 0, nullptr};
   } else {
     mn = mw;
   }
+  if (g_timeline != nullptr) next.timeline = g_timeline + (size_t)(g_timeline_launches++ % g_timeline_slots) * TL_BLOCKS * TL_EVENTS;
   cudaStream_t s = (cudaStream_t)stream;
   if (nt == 16) return launch_mode<16, 10>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
   if (nt == 32) return launch_mode<32, 9>(mode, out, mw, ma, scratch, counters, M, N, K, ldo, use_pdl, s, mn, next);
@@ -466,6 +496,17 @@ extern "C" int gi_gemm_stream_geometry(int M, int N, int K, int* n_ctas, int* kb
   *kb_per_tile = (K + BK - 1) / BK;
   *nt = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   return GI_OK;
+}
+
+// From now on every streamed product writes its blocks' time stamps into slot (launch number mod slots) of `buf`
+// ([slots][256 blocks][8 events] 64-bit values on the device); buf = null switches it off.  Returns how many
+// launches have been stamped since the last call.  A launch captured in a CUDA graph keeps the slot it was captured with.
+extern "C" long gi_gemm_stream_timeline(unsigned long long* buf, int slots) {
+  const long n = g_timeline_launches;
+  g_timeline = (buf != nullptr && slots > 0) ? buf : nullptr;
+  g_timeline_slots = slots > 0 ? slots : 1;
+  g_timeline_launches = 0;
+  return n;
 }
 
 extern "C" int gi_gemm_stream_status(int* status) {

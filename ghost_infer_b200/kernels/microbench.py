@@ -94,7 +94,9 @@ def main() -> int:
         if args.kernel == "attn_decode":
             q = torch.randn(B, (H + 2 * KV) * hd, device=dev, dtype=bf)
             lens = torch.full((B,), S, dtype=torch.int32, device=dev)
-            splits = args.splits or max(1, min(32, 148 // max(1, B * KV * ((H // KV + 15) // 16)), S // 128))
+            # the engine's choice (StepContext.decode_splits): one wave of two blocks per SM, slices of at least 128 keys
+            sms = torch.cuda.get_device_properties(0).multi_processor_count
+            splits = args.splits or max(1, min(32, (2 * sms) // max(1, B * KV * ((H // KV + 15) // 16)), S // 128))
             o = torch.empty(B, H * hd, device=dev, dtype=bf)
             po = torch.empty(B * H * splits * hd, device=dev)
             pml = torch.empty(B * H * splits * 2, device=dev)

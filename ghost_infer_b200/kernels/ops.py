@@ -416,6 +416,35 @@ def _next_weights(w: torch.Tensor, mode: int):
     return nxt.data_ptr(), nxt.shape[0], nxt.shape[1], nxt.stride(0), next_mode, ahead
 
 
+_timeline_buf: Optional[torch.Tensor] = None
+
+
+def stream_timeline_start(slots: int, device="cuda") -> None:
+    """From now on each streamed product's blocks note the nanosecond clock at eight places of their life, launch n
+    into slot n mod `slots` (a launch captured in a CUDA graph keeps its slot).  For timelines of a decode step."""
+    global _timeline_buf
+    lib = _bind()
+    _timeline_buf = torch.zeros((slots, 256, 8), dtype=torch.int64, device=device)
+    lib.gi_gemm_stream_timeline.restype = c_long
+    lib.gi_gemm_stream_timeline.argtypes = [c_void_p, c_int]
+    lib.gi_gemm_stream_timeline(_timeline_buf.data_ptr(), slots)
+
+
+def stream_timeline_stop():
+    """Stops the stamping.  Returns (stamps [slots, 256 blocks, 8 events] as an int64 array, launches stamped).
+    Events: 0 entry, 1 set up, 2 the SM's number, 3 dependency wait over, 4 first stage landed, 5 last load issued,
+    6 last product issued, 7 last epilogue done."""
+    global _timeline_buf
+    lib = _bind()
+    lib.gi_gemm_stream_timeline.restype = c_long
+    lib.gi_gemm_stream_timeline.argtypes = [c_void_p, c_int]
+    n = int(lib.gi_gemm_stream_timeline(None, 0))
+    torch.cuda.synchronize()
+    out = _timeline_buf.cpu().numpy() if _timeline_buf is not None else None
+    _timeline_buf = None
+    return out, n
+
+
 def gemm_stream_status() -> int:
     lib = _bind()
     status = ctypes.c_int(0)
