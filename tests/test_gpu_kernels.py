@@ -439,6 +439,28 @@ def test_gemm_stream(pdl, m, n, k):
     assert ops.gemm_stream_status() == 0
 
 
+def test_gemm_stream_time_stamps():
+    """With a buffer given, every block of a streamed product notes the clock along its life, in order; without
+    one, nothing is written."""
+    a, w = rnd(8, 4096, dtype=torch.bfloat16, seed=40), rnd(6144, 4096, dtype=torch.bfloat16, seed=41)
+    ops.stream_timeline_start(4)
+    ops.gemm_stream(a, w, ops.SKINNY_STORE_F32)
+    ops.gemm_stream(a, w, ops.SKINNY_STORE_F32)
+    stamps, n = ops.stream_timeline_stop()
+    assert n == 2 and stamps.shape == (4, 256, 8)
+    assert (stamps[2:] == 0).all()
+    for launch in stamps[:2]:
+        blocks = launch[launch[:, 0] > 0]
+        assert 1 <= len(blocks) <= 256
+        for a_ev, b_ev in ((0, 1), (1, 3), (3, 4), (4, 6), (5, 6), (6, 7)):
+            assert (blocks[:, a_ev] <= blocks[:, b_ev]).all(), (a_ev, b_ev)
+    assert stamps[1, :, 0].max() >= stamps[0, :, 7][stamps[0, :, 7] > 0].min()     # the second launch came later
+    out = ops.gemm_stream(a, w, ops.SKINNY_STORE_F32)                               # switched off again: results as ever
+    assert ops.gemm_stream_status() == 0
+    terms = a.double().abs() @ w.double().abs().T
+    assert ((out.double() - a.double() @ w.double().T).abs() <= 2e-6 * terms + 1e-7).all()
+
+
 @pytest.mark.parametrize("m", [1, 8, 20, 64])
 @pytest.mark.parametrize("f,k", [(176, 64), (1000, 4096), (14336, 512)])
 def test_gemm_stream_swiglu(m, f, k):
