@@ -79,9 +79,12 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* bars = (uint64_t*)(p_s + P_BYTES);            // q_full, k_full[2], v_full[2], kv_empty[2], s_full, s_free, p_full, o_full
   uint32_t* tmem_slot = (uint32_t*)(bars + 12);
 
-  const int b = blockIdx.z, h = blockIdx.y;
+  // Blocks start in the order x, y, z: heads fastest (the heads of a group read the same keys and values at the
+  // same time), then sequences, then query tiles from the latest down: the blocks with the most keys to visit start
+  // first, for every head and sequence of the launch, and the short ones fill the gaps at the end.
+  const int h = blockIdx.x, b = blockIdx.y;
   const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
-  const int q0 = (q_tiles - 1 - (int)blockIdx.x) * BQ;     // latest tiles first: they have the most keys to visit
+  const int q0 = (q_tiles - 1 - (int)blockIdx.z) * BQ;
   if (q0 >= qlen) return;
   if (smem_u32(smem) & 1023u) {
     if (threadIdx.x == 0) atomicCAS(&g_attn_status, 0, 9);
@@ -342,7 +345,7 @@ extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, 
     return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
   if (ldq % 8 != 0 || ldo % 8 != 0 || (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)out) & 15))
     return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tcgen05): rows must be 16-byte aligned");
-  if (n_seqs > 65535 || n_heads > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "attention: more than 65535 sequences or heads in one launch");
+  if (n_seqs > 65535 || (max_q_len + BQ - 1) / BQ > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "attention: more than 65535 sequences or query tiles in one launch");
   CUtensorMap mq, mk, mv;
   int rc = gi::tensor_map_2d_ex(&mq, q, q_rows, (long)(n_heads + 2 * n_kv) * hd, ldq, GI_BF16, 64, BQ);
   if (rc != GI_OK) return rc;
@@ -359,7 +362,7 @@ extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, 
     configured = true;
   }
   const int q_tiles = (max_q_len + BQ - 1) / BQ;
-  dim3 grid(q_tiles, n_heads, n_seqs);
+  dim3 grid(n_heads, n_seqs, q_tiles);
   return gi::check(gi::launch(attn_prefill_t5_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo,
                               block_table, max_pages, cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles),
                    "attention prefill (tcgen05)");

@@ -46,7 +46,8 @@ __global__ void settle_kernel(float* __restrict__ x, gi_settle_t st, const int* 
 // `rows` (optional) picks which rows of x are normed; output row r is then x[rows[r]].
 // The row is read once, four floats at a time, and kept in registers (up to VEC float4 per thread);
 // wider rows, or rows that are no multiple of 4, take the plain loop.
-template <typename TO, typename TW, int VEC, bool SETTLE>
+// ALIGNED: the weights and the output rows start on 16-byte boundaries too (four values per access there as well).
+template <typename TO, typename TW, int VEC, bool SETTLE, bool ALIGNED>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, const TW* __restrict__ w,
                                const int* __restrict__ rows, int d, float eps, gi_settle_t st) {
   __shared__ float scratch[33];
@@ -65,7 +66,8 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, cons
     for (int j = 0; j < VEC; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
       if (i < n4) {
-        wv[j] = make_float4(gi::ldf(w + 4 * i), gi::ldf(w + 4 * i + 1), gi::ldf(w + 4 * i + 2), gi::ldf(w + 4 * i + 3));
+        wv[j] = ALIGNED ? gi::ld4(w + 4 * i)
+                        : make_float4(gi::ldf(w + 4 * i), gi::ldf(w + 4 * i + 1), gi::ldf(w + 4 * i + 2), gi::ldf(w + 4 * i + 3));
         if (SETTLE) sp[j] = gi_span_of(st, 4 * i);
       }
     }
@@ -95,10 +97,15 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, cons
     for (int j = 0; j < VEC; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
       if (i < n4) {
-        gi::stf(o + 4 * i, v[j].x * scale * wv[j].x);
-        gi::stf(o + 4 * i + 1, v[j].y * scale * wv[j].y);
-        gi::stf(o + 4 * i + 2, v[j].z * scale * wv[j].z);
-        gi::stf(o + 4 * i + 3, v[j].w * scale * wv[j].w);
+        const float4 y = make_float4(v[j].x * scale * wv[j].x, v[j].y * scale * wv[j].y, v[j].z * scale * wv[j].z, v[j].w * scale * wv[j].w);
+        if (ALIGNED) {
+          gi::st4(o + 4 * i, y);
+        } else {
+          gi::stf(o + 4 * i, y.x);
+          gi::stf(o + 4 * i + 1, y.y);
+          gi::stf(o + 4 * i + 2, y.z);
+          gi::stf(o + 4 * i + 3, y.w);
+        }
       }
     }
     return;
@@ -140,18 +147,18 @@ extern "C" int gi_embed(float* out, const void* table, int table_dtype, const in
 }
 
 namespace {
-template <typename TO, typename TW>
+template <typename TO, typename TW, bool ALIGNED>
 cudaError_t rmsnorm_launch(int per, bool settle, dim3 g, dim3 b, cudaStream_t s, TO* out, float* x, const TW* w, const int* rows, int d,
                            float eps, gi_settle_t st) {
   if (settle) {
-    if (per == 1) return gi::launch(rmsnorm_kernel<TO, TW, 1, true>, g, b, 0, s, out, x, w, rows, d, eps, st);
-    if (per == 2) return gi::launch(rmsnorm_kernel<TO, TW, 2, true>, g, b, 0, s, out, x, w, rows, d, eps, st);
-    return gi::launch(rmsnorm_kernel<TO, TW, 4, true>, g, b, 0, s, out, x, w, rows, d, eps, st);
+    if (per == 1) return gi::launch(rmsnorm_kernel<TO, TW, 1, true, ALIGNED>, g, b, 0, s, out, x, w, rows, d, eps, st);
+    if (per == 2) return gi::launch(rmsnorm_kernel<TO, TW, 2, true, ALIGNED>, g, b, 0, s, out, x, w, rows, d, eps, st);
+    return gi::launch(rmsnorm_kernel<TO, TW, 4, true, ALIGNED>, g, b, 0, s, out, x, w, rows, d, eps, st);
   }
-  if (per == 1) return gi::launch(rmsnorm_kernel<TO, TW, 1, false>, g, b, 0, s, out, x, w, rows, d, eps, st);
-  if (per == 2) return gi::launch(rmsnorm_kernel<TO, TW, 2, false>, g, b, 0, s, out, x, w, rows, d, eps, st);
-  if (per == 3 || per == 4) return gi::launch(rmsnorm_kernel<TO, TW, 4, false>, g, b, 0, s, out, x, w, rows, d, eps, st);
-  return gi::launch(rmsnorm_kernel<TO, TW, 0, false>, g, b, 0, s, out, x, w, rows, d, eps, st);
+  if (per == 1) return gi::launch(rmsnorm_kernel<TO, TW, 1, false, ALIGNED>, g, b, 0, s, out, x, w, rows, d, eps, st);
+  if (per == 2) return gi::launch(rmsnorm_kernel<TO, TW, 2, false, ALIGNED>, g, b, 0, s, out, x, w, rows, d, eps, st);
+  if (per == 3 || per == 4) return gi::launch(rmsnorm_kernel<TO, TW, 4, false, ALIGNED>, g, b, 0, s, out, x, w, rows, d, eps, st);
+  return gi::launch(rmsnorm_kernel<TO, TW, 0, false, false>, g, b, 0, s, out, x, w, rows, d, eps, st);
 }
 
 int rmsnorm_impl(void* out, int out_dtype, float* x, const void* w, int w_dtype, const int* rows, int n_rows, int d, float eps,
@@ -160,14 +167,20 @@ int rmsnorm_impl(void* out, int out_dtype, float* x, const void* w, int w_dtype,
   if (d <= 0) return gi::fail(GI_ERR_ARG, "rmsnorm: bad width %d", d);
   const bool settle = st.partials != nullptr;
   // a settling norm has several dependent loads per value: more threads, fewer values each
-  const int threads = settle ? (d >= 4096 ? 1024 : (d >= 2048 ? 512 : 256)) : (d >= 2048 ? 512 : 256);
+  // few rows (a decode step): many threads per row; many rows (a prompt): 256 threads with more values each, so that
+  // an SM holds eight rows' loads in flight instead of four
+  const bool many = n_rows >= 512;
+  const int threads = settle ? (d >= 4096 ? 1024 : (d >= 2048 ? 512 : 256)) : ((d >= 2048 && !(many && d <= 4096)) ? 512 : 256);
   // the register path: rows that are a multiple of 4 wide, start on 16-byte boundaries, and fit 4 float4 per thread
   const bool vec = d % 4 == 0 && ((uintptr_t)x & 15) == 0 && d / 4 <= 4 * threads;
   const int per = vec ? (d / 4 + threads - 1) / threads : 0;
   if (settle && per == 0) return gi::fail(GI_ERR_UNSUPPORTED, "rmsnorm: settling partial sums needs rows of a multiple of 4 and at most %d values", 16 * threads);
   cudaError_t e = cudaSuccess;
+  // d % 4 == 0 here whenever per > 0, so every output row starts as aligned as the first
+  const bool aligned = ((uintptr_t)out & 15) == 0 && ((uintptr_t)w & 15) == 0;
   GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW,
-      e = (rmsnorm_launch<TO, TW>(per, settle, dim3(n_rows), dim3(threads), (cudaStream_t)stream, (TO*)out, x, (const TW*)w, rows, d, eps, st))));
+      e = aligned ? (rmsnorm_launch<TO, TW, true>(per, settle, dim3(n_rows), dim3(threads), (cudaStream_t)stream, (TO*)out, x, (const TW*)w, rows, d, eps, st))
+                  : (rmsnorm_launch<TO, TW, false>(per, settle, dim3(n_rows), dim3(threads), (cudaStream_t)stream, (TO*)out, x, (const TW*)w, rows, d, eps, st))));
   return gi::check(e, "rmsnorm");
 }
 }  // namespace
