@@ -129,14 +129,14 @@ def model_numbers(cfg, layers):
             "kv_bytes_per_token": 2 * layers * KV * hd * 2}
 
 
-def decode_timeline(ops, decode_run, layers, steps, warmup):
+def decode_timeline(ops, decode_run, layers, steps, warmup, batch=8):
     """Prints, for the last decode step's streamed products (q/k/v, o, gate/up, down of every layer, then the head), the
     times of their blocks' stamps relative to the end of the product before: how long the kernels between two
     products take (the wait), how long a product streams, how far its blocks' ends spread."""
     import numpy as np
     per_step = 4 * layers + 1
     ops.stream_timeline_start(2 * per_step)
-    decode_run(8, steps, warmup)
+    decode_run(batch, steps, warmup)
     tl, n = ops.stream_timeline_stop()
     live = [i for i in range(tl.shape[0]) if tl[i, :, 0].max() > 0]
     order = sorted(live, key=lambda i: tl[i, :, 0][tl[i, :, 0] > 0].min())[-per_step:]
@@ -170,6 +170,7 @@ def main():
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "timeline"],
                     help="run one phase alone and print its time (a short program for a launch list under a profiler; no bench "
                          "line).  timeline: a table of when the streamed products of a decode step start, wait, stream and end")
+    ap.add_argument("--batch", type=int, default=8, help="sequences per decode step for --only decode|timeline (the bench line is always batch 8)")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another (no programmatic dependent launch)")
     args = ap.parse_args()
 
@@ -244,10 +245,10 @@ def main():
         return ms, launched, ctx_tokens
 
     if args.only == "timeline":
-        return decode_timeline(ops, decode_run, layers, K, W)
+        return decode_timeline(ops, decode_run, layers, K, W, args.batch)
     if args.only == "decode":
-        ms, n, _ = decode_run(8, K, W)
-        print(json.dumps({"only": "decode", "layers": layers, "batch": 8, "ms_per_step": round(ms, 4), "launches_per_step": n // K}))
+        ms, n, _ = decode_run(args.batch, K, W)
+        print(json.dumps({"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": round(ms, 4), "launches_per_step": n // K}))
         return 0
     if args.only == "prefill":
         prompt = rng.integers(0, V, size=PROMPT).tolist()

@@ -41,6 +41,15 @@ __device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat16
 __device__ __forceinline__ void stf(float* p, float v) { *p = v; }
 __device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+// silu(g) * u = g / (1 + e^-g) * u for the epilogues that round to bfloat16 right after: 2^x and the division by the
+// approximate instructions (each good to about 2 units in the last place of a float; 32-bit arithmetic throughout).
+// Six instructions instead of forty, which matters where one warp per scheduler works through a whole tile.
+__device__ __forceinline__ float silu_mul_bf16(float g, float u) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+  return __fdividef(g, 1.0f + e) * u;
+}
+
 // Four neighbouring values at once (the pointer is aligned to the four of them).
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {

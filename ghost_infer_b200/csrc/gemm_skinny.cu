@@ -119,7 +119,7 @@ skinny_kernel(void* __restrict__ out_, const __nv_bfloat16* __restrict__ A, cons
           up += red[wv][mt][nt][ln][2 + c];
         }
         const int f = n0 / 2 + fl, m = ntb * 8 + ml;
-        if (m < M && f < N / 2) ((__nv_bfloat16*)out_)[(size_t)m * ldo + f] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+        if (m < M && f < N / 2) ((__nv_bfloat16*)out_)[(size_t)m * ldo + f] = __float2bfloat16_rn(gi::silu_mul_bf16(gate, up));
       }
       continue;
     }

@@ -346,11 +346,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           const int fo = (f >> 4) * 8 + (f & 7);
 #pragma unroll
           for (int m = 0; m < NT; ++m) {
+            if (m >= M) break;                      // the same for every lane
             const float up = __shfl_down_sync(0xffffffffu, v[m], 8);
-            if (is_gate && m < M && f < N) {
-              const float g = v[m];
-              ((__nv_bfloat16*)out_)[(size_t)m * ldo + fo] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * up);
-            }
+            if (is_gate && f < N) ((__nv_bfloat16*)out_)[(size_t)m * ldo + fo] = __float2bfloat16_rn(gi::silu_mul_bf16(v[m], up));
           }
         } else if (f < N) {
 #pragma unroll

@@ -160,7 +160,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               for (int j = 0; j < 8; j += 2) {
                 const float g0 = __uint_as_float(r[blk * 16 + j]), g1 = __uint_as_float(r[blk * 16 + j + 1]);
                 const float u0 = __uint_as_float(r[blk * 16 + 8 + j]), u1 = __uint_as_float(r[blk * 16 + 8 + j + 1]);
-                __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                __nv_bfloat162 v = __floats2bfloat162_rn(gi::silu_mul_bf16(g0, u0), gi::silu_mul_bf16(g1, u1));
                 p[j / 2] = *reinterpret_cast<uint32_t*>(&v);
               }
               stage_chunk(stg, row, q * 2 + blk, make_uint4(p[0], p[1], p[2], p[3]));
