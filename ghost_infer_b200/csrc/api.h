@@ -102,7 +102,8 @@ int gi_embed(float* out, const void* table, int table_dtype, const int* tokens, 
              void* stream);
 int gi_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows, int n_rows,
                int d, float eps, void* stream);
-// The same, first adding deferred partial sums to the rows it reads (and writing the settled rows back to x).
+// The same, first adding deferred partial sums to the rows it reads (and writing the settled rows back to x, unless
+// `rows` selects: then x is left as it is and must not be read again).
 int gi_rmsnorm_settle(void* out, int out_dtype, float* x, const void* w, int w_dtype, const int* rows, int n_rows,
                       int d, float eps, gi_settle_t settle, void* stream);
 int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, int interleaved, void* stream);

@@ -84,7 +84,9 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, cons
         v[j].y += p.y;
         v[j].z += p.z;
         v[j].w += p.w;
-        reinterpret_cast<float4*>(xr)[i] = v[j];      // the settled row goes back to the residual stream
+        // the settled row goes back to the residual stream; not for a selection of rows (it may name a row twice,
+        // and nothing reads the stream after the norm that selects)
+        if (rows == nullptr) reinterpret_cast<float4*>(xr)[i] = v[j];
       }
       ss = fmaf(v[j].x, v[j].x, ss);
       ss = fmaf(v[j].y, v[j].y, ss);
@@ -166,9 +168,9 @@ int rmsnorm_impl(void* out, int out_dtype, float* x, const void* w, int w_dtype,
   if (n_rows <= 0) return GI_OK;
   if (d <= 0) return gi::fail(GI_ERR_ARG, "rmsnorm: bad width %d", d);
   const bool settle = st.partials != nullptr;
-  // a settling norm has several dependent loads per value: more threads, fewer values each
   // few rows (a decode step): many threads per row; many rows (a prompt): 256 threads with more values each, so that
   // an SM holds eight rows' loads in flight instead of four
+  // (a settling norm has several loads per value: more threads, fewer values each)
   const bool many = n_rows >= 512;
   const int threads = settle ? (d >= 4096 ? 1024 : (d >= 2048 ? 512 : 256)) : ((d >= 2048 && !(many && d <= 4096)) ? 512 : 256);
   // the register path: rows that are a multiple of 4 wide, start on 16-byte boundaries, and fit 4 float4 per thread

@@ -143,7 +143,9 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
         out = torch.empty((n, d), dtype=out_dtype, device=x.device)
     pending = _pending.pop(x.data_ptr(), None)
     if pending is not None:
-        # a deferred product left partial sums for this stream: add them while the rows are read anyway
+        # a deferred product left partial sums for this stream: add them while the rows are read anyway (and write
+        # the settled rows back; with a selection of rows nothing is written back: the selection may name a row twice,
+        # and the stream's other rows stay unsettled, so whoever selects rows must be the stream's last reader)
         _check(lib, lib.gi_rmsnorm_settle(out.data_ptr(), _dt(out, "rmsnorm output"), x.data_ptr(), weight.data_ptr(),
                                           _dt(weight, "rmsnorm weight"), _i32(rows, "rows"), n, d, float(eps), pending,
                                           _stream()))

@@ -152,6 +152,24 @@ def test_chunked_prompt_and_partial_wants(engines, tiny_configs, name, dtype, st
     check_logits(np.concatenate([a, b]), ref[[0, 69, 76, 149]], dtype, f"{name} {dtype} chunks")
 
 
+@pytest.mark.parametrize("name,dtype,stored", [("B", "bfloat16", "bfloat16"), ("E", "bfloat16", "bfloat16"), ("A", "float32", "float32")])
+def test_a_place_wanted_twice(engines, tiny_configs, name, dtype, stored):
+    """The same place named twice among the wanted ones, in a prompt and in one-token steps (where the last product
+    of the last layer may leave partial sums to the final norm, which then reads that row for both)."""
+    eng, d = engines(name, dtype, stored)
+    toks = tokens_for(tiny_configs[name], 40, 12)
+    ref = plain_logits(d, toks)
+    s = eng.cache.open_slot()
+    a = eng.step([gi.StepEntry(s, toks[:30], [29, 3, 29])]).cpu().numpy()
+    check_logits(a, ref[[29, 3, 29]], dtype, f"{name} {dtype} prompt")
+    assert np.array_equal(a[0], a[2])
+    for i in range(30, 40):
+        b = eng.step([gi.StepEntry(s, toks[i:i + 1], [0, 0, 0])]).cpu().numpy()
+        check_logits(b, ref[[i, i, i]], dtype, f"{name} {dtype} token {i}")
+        assert np.array_equal(b[0], b[1]) and np.array_equal(b[0], b[2])
+    eng.cache.close_slot(s)
+
+
 def test_host_checks_come_before_any_launch(engines):
     eng, _ = engines("A", "float32", "float32")
     s = eng.cache.open_slot()
