@@ -1,5 +1,5 @@
 // Causal grouped-query attention of a step's prompt tokens over the paged cache on tcgen05 tensor cores
-// (bfloat16, head size 128).
+// (bfloat16, head size 64 or 128).
 //
 // Formula: src/model.rs:1320-1419.  The reference's prompt attention (attention_prefill_tc, src/cuda.rs:2408-2613)
 // keeps scores in registers of mma.sync fragments; on sm_100a the same algorithm is laid out around tensor memory:
@@ -21,12 +21,12 @@ namespace {
 
 using namespace gi::tc;
 
-constexpr int HD = 128;
 constexpr int BQ = 128;          // queries per block = tensor-memory lanes
 constexpr int BKV = 64;          // keys per tile = one page
 constexpr int THREADS = 160;     // warps 0-3: one query row per thread; warp 4: TMA and MMA issue
-constexpr int TMEM_COLS = 256;   // S: columns 0..63, O: columns 64..191
-constexpr uint32_t Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2, P_BYTES = BQ * BKV * 2;
+constexpr int TMEM_COLS = 256;   // S: columns 0..63, O: columns 64..64 + head size - 1
+constexpr uint32_t Q_HALF = BQ * 128, KV_HALF = BKV * 128;   // a 64-dimension half of a tile: rows of 128 bytes, swizzled
+constexpr uint32_t P_BYTES = BQ * BKV * 2;
 
 __device__ int g_attn_status = 0;
 
@@ -58,22 +58,25 @@ __device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t lbo_byt
          ((uint64_t)2 << 61);
 }
 
+template <int HD>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, long ldo,
                        const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slots, const int* __restrict__ seq_pos0, int n_heads, int n_kv, float scale,
                        int window, int q_tiles) {
+  constexpr int HALVES = HD / 64;
+  constexpr uint32_t Q_BYTES = HALVES * Q_HALF, KV_BYTES = HALVES * KV_HALF;
   // instruction descriptors: float accumulator, bfloat16 operands, M 128; S = Q K^T has N 64 and both operands K-major,
   // O = P V has N 128 and B (V) MN-major (bit 16)
   constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
   constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
-  // Two blocks must fit one SM (2 x 113 KB), which leaves no room for alignment slack: the tiles need 1024-byte
+  // Two blocks must fit one SM (2 x 113 KB at head size 128), which leaves no room for alignment slack: the tiles need 1024-byte
   // alignment, the dynamic shared memory of a kernel without static shared memory starts on such a boundary, and
   // the block checks that before it does anything.
   extern __shared__ __align__(1024) unsigned char smem[];
-  unsigned char* q_s = smem;                              // [2 halves][128 rows][64 dims]
-  unsigned char* k_s = q_s + Q_BYTES;                     // [2 stages][2 halves][64 keys][64 dims]
+  unsigned char* q_s = smem;                              // [halves][128 rows][64 dims]
+  unsigned char* k_s = q_s + Q_BYTES;                     // [2 stages][halves][64 keys][64 dims]
   unsigned char* v_s = k_s + 2 * KV_BYTES;                // the same
   unsigned char* p_s = v_s + 2 * KV_BYTES;                // [128 rows][64 keys]
   uint64_t* bars = (uint64_t*)(p_s + P_BYTES);            // q_full, k_full[2], v_full[2], kv_empty[2], s_full, s_free, p_full, o_full
@@ -137,15 +140,15 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int page = block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS];
         const int row0 = (page * n_kv + kvh) * PAGE_TOKENS;
         mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
-        tma_load_2d(smem_u32(k_s + s * KV_BYTES), &map_k, 0, row0, k_full0 + 8 * s);
-        tma_load_2d(smem_u32(k_s + s * KV_BYTES + KV_BYTES / 2), &map_k, 64, row0, k_full0 + 8 * s);
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(smem_u32(k_s + s * KV_BYTES + hf * KV_HALF), &map_k, hf * 64, row0, k_full0 + 8 * s);
         mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
-        tma_load_2d(smem_u32(v_s + s * KV_BYTES), &map_v, 0, row0, v_full0 + 8 * s);
-        tma_load_2d(smem_u32(v_s + s * KV_BYTES + KV_BYTES / 2), &map_v, 64, row0, v_full0 + 8 * s);
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(smem_u32(v_s + s * KV_BYTES + hf * KV_HALF), &map_v, hf * 64, row0, v_full0 + 8 * s);
       };
       mbar_expect_tx(q_full, Q_BYTES);
-      tma_load_2d(smem_u32(q_s), &map_q, h * HD, tok0 + q0, q_full);
-      tma_load_2d(smem_u32(q_s + Q_BYTES / 2), &map_q, h * HD + 64, tok0 + q0, q_full);
+#pragma unroll
+      for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(smem_u32(q_s + hf * Q_HALF), &map_q, h * HD + hf * 64, tok0 + q0, q_full);
       load_kv(0);
       ok = mbar_wait(q_full, 0, 1, &g_attn_status);
       // S = Q K^T of tile j into tensor memory (the keys are here; the rows of the previous S have been read)
@@ -158,8 +161,8 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + s * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint64_t dq = smem_desc(qa + (ks / 4) * (Q_BYTES / 2) + (ks % 4) * 32);
-          const uint64_t dk = smem_desc(ka + (ks / 4) * (KV_BYTES / 2) + (ks % 4) * 32);
+          const uint64_t dq = smem_desc(qa + (ks / 4) * Q_HALF + (ks % 4) * 32);
+          const uint64_t dk = smem_desc(ka + (ks / 4) * KV_HALF + (ks % 4) * 32);
           tc_mma(tmem_s, dq, dk, IDESC_S, ks > 0 ? 1u : 0u);
         }
         tc_commit(s_full);
@@ -186,7 +189,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
           const uint64_t dp = smem_desc(pa + kk * 32);
-          const uint64_t dv = smem_desc_mn(va + kk * 2048, KV_BYTES / 2);
+          const uint64_t dv = smem_desc_mn(va + kk * 2048, KV_HALF);
           tc_mma(tmem_o, dp, dv, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(kv_empty0 + 8 * s);
@@ -289,9 +292,9 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         ok = mbar_wait(v_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 3, &g_attn_status);
         if (!ok) break;
         unsigned char* vt = v_s + s * KV_BYTES;
-        for (int idx = threadIdx.x; idx < BKV * 16; idx += 128) {
-          const int r = idx / 16, cidx = idx % 16;        // key row, 16-byte chunk among the row's 256 bytes (two halves)
-          if (r < lo || r >= hi) *reinterpret_cast<uint4*>(vt + (cidx / 8) * (KV_BYTES / 2) + r * 128 + (cidx % 8) * 16) = make_uint4(0, 0, 0, 0);
+        for (int idx = threadIdx.x; idx < BKV * (HD / 8); idx += 128) {
+          const int r = idx / (HD / 8), cidx = idx % (HD / 8);   // key row, 16-byte chunk of the row (its halves lie apart)
+          if (r < lo || r >= hi) *reinterpret_cast<uint4*>(vt + (cidx / 8) * KV_HALF + r * 128 + (cidx % 8) * 16) = make_uint4(0, 0, 0, 0);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -333,6 +336,22 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
 }
 
+template <int HD>
+int launch_t5(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, __nv_bfloat16* out,
+              long ldo, const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots, const int* seq_pos0,
+              int n_heads, int n_kv, float scale, int window, int q_tiles) {
+  constexpr size_t smem = (HD / 64) * (Q_HALF + 4 * KV_HALF) + P_BYTES + 12 * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_t5_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention prefill (tcgen05): %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  return gi::check(gi::launch(attn_prefill_t5_kernel<HD>, grid, dim3(THREADS), smem, stream, mq, mk, mv, out, ldo, block_table, max_pages,
+                              cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles),
+                   "attention prefill (tcgen05)");
+}
+
 }  // namespace
 
 extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, long q_rows, const void* kcache,
@@ -340,7 +359,7 @@ extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, 
                                   const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
                                   int max_q_len, int n_heads, int n_kv, int hd, float scale, int window, void* stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
-  if (hd != HD) return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tcgen05): head size %d, only 128", hd);
+  if (hd != 64 && hd != 128) return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tcgen05): head size %d, only 64 and 128", hd);
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
     return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
   if (ldq % 8 != 0 || ldo % 8 != 0 || (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)out) & 15))
@@ -354,18 +373,13 @@ extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, 
   if (rc != GI_OK) return rc;
   rc = gi::tensor_map_2d_ex(&mv, vcache, cache_rows, hd, hd, GI_BF16, 64, BKV);
   if (rc != GI_OK) return rc;
-  constexpr size_t smem = Q_BYTES + 4 * KV_BYTES + P_BYTES + 12 * 8 + 16;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention prefill (tcgen05): %s", cudaGetErrorString(e));
-    configured = true;
-  }
   const int q_tiles = (max_q_len + BQ - 1) / BQ;
   dim3 grid(n_heads, n_seqs, q_tiles);
-  return gi::check(gi::launch(attn_prefill_t5_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo,
-                              block_table, max_pages, cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles),
-                   "attention prefill (tcgen05)");
+  if (hd == 128)
+    return launch_t5<128>(grid, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages, cu_seqlens, seq_slots,
+                          seq_pos0, n_heads, n_kv, scale, window, q_tiles);
+  return launch_t5<64>(grid, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages, cu_seqlens, seq_slots,
+                       seq_pos0, n_heads, n_kv, scale, window, q_tiles);
 }
 
 extern "C" int gi_attn_prefill_t5_status(int* status) {

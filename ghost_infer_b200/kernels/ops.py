@@ -636,7 +636,7 @@ def attn_prefill_t5(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                     cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
                     max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
                     window: Optional[int], out: torch.Tensor) -> torch.Tensor:
-    """As attn_prefill_generic, for bfloat16 and head size 128, on tcgen05 tensor cores with TMA-fed operands.
+    """As attn_prefill_generic, for bfloat16 and head size 64 or 128, on tcgen05 tensor cores with TMA-fed operands.
     `q` is the whole packed [tokens, (H + 2 KV) * head_dim] matrix (its first columns are the queries)."""
     lib = _bind()
     _cuda(q, "queries")
@@ -760,8 +760,8 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
         return kernel(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
                       step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
     if attn_decode_tc_ok(qkv, memory.k, head_dim) and out.stride(0) % 2 == 0:
-        # head size 128: tcgen05 (scores and output in tensor memory); 64: mma.sync
-        t5 = (TUNE["attn_prefill_tcgen05"] and head_dim == 128 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+        # tcgen05 (scores and output in tensor memory); mma.sync when that is switched off or the rows do not suit TMA
+        t5 = (TUNE["attn_prefill_tcgen05"] and head_dim in (64, 128) and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
               and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim and memory.k.is_contiguous())
         kernel = attn_prefill_t5 if t5 else attn_prefill_tc
     else:

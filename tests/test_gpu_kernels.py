@@ -559,12 +559,12 @@ def test_deferred_store_is_settled_by_the_rotary_kernel(m, H, KV, hd, rot):
     torch.testing.assert_close(got_v, ref_v, rtol=1.6e-2, atol=1.6e-2)
 
 
+@pytest.mark.parametrize("hd", [128, 64])
 @pytest.mark.parametrize("H,KV", [(4, 2), (32, 8), (3, 1)])
 @pytest.mark.parametrize("window", [None, 37, 100])
-def test_attention_prefill_tcgen05(H, KV, window):
-    """The tcgen05 prefill kernel (head size 128): ragged lengths around its 128-row and 64-key tiles, sequences
-    that go on after cached positions, pages in shuffled order, unowned rows poisoned with NaN."""
-    hd = 128
+def test_attention_prefill_tcgen05(H, KV, window, hd):
+    """The tcgen05 prefill kernel (head sizes 128 and 64): ragged lengths around its 128-row and 64-key tiles,
+    sequences that go on after cached positions, pages in shuffled order, unowned rows poisoned with NaN."""
     lens_q, pos0 = [1, 45, 128, 129, 300, 33, 130], [0, 0, 0, 0, 0, 70, 200]
     B, S = len(lens_q), 384
     k = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=10)
