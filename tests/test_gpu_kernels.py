@@ -265,6 +265,13 @@ def test_attention_finds_one_far_key(decode, window):
         ops.attn_prefill_tc(q[:, 0], kc, vc, bt, torch.tensor([0, 1], dtype=torch.int32, device=DEV), 0 * one,
                             pos * one, 1, 1, H, KV, hd, 1.0, window, out2)
         torch.testing.assert_close(out2.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
+        # and the tcgen05 prefill kernel, which takes the packed [q | k | v] rows
+        packed = torch.cat([q[:, 0], torch.zeros(1, 2 * KV * hd, dtype=q.dtype, device=DEV)], -1).contiguous()
+        out3 = torch.zeros_like(out)
+        ops.attn_prefill_t5(packed, kc, vc, bt, torch.tensor([0, 1], dtype=torch.int32, device=DEV), 0 * one,
+                            pos * one, 1, 1, H, KV, hd, 1.0, window, out3)
+        assert ops.attn_prefill_t5_status() == 0
+        torch.testing.assert_close(out3.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
         return
     if decode:
         po, pml = torch.zeros(H * 4 * hd, device=DEV), torch.zeros(H * 4 * 2, device=DEV)
@@ -274,6 +281,80 @@ def test_attention_finds_one_far_key(decode, window):
         ops.attn_prefill_generic(q[:, 0], kc, vc, bt, torch.tensor([0, 1], dtype=torch.int32, device=DEV), 0 * one,
                                  pos * one, 1, 1, H, KV, hd, 1.0, window, out)
     torch.testing.assert_close(out.double(), ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("kernel,hd", [("generic", 32), ("mma", 64), ("tcgen05", 64), ("tcgen05", 128)])
+@pytest.mark.parametrize("window", [None, 37, 64, 100])
+@pytest.mark.parametrize("edge", ["newest", "oldest"])
+def test_prompt_attention_edges_at_every_row(kernel, hd, window, edge):
+    """Every row of a prompt is made to look at exactly one key: its own position (scores that grow with the key's
+    position) or the oldest position it may see (scores that fall): the start, or the window's far edge.  The value
+    of position j holds j, so the output names the key each row really used; one position off anywhere (a tile's
+    border, a block's border, the window's edge) shows as a wrong number."""
+    if edge == "oldest" and window is None:
+        window_eff, first = None, lambda i: 0
+    else:
+        window_eff, first = window, (lambda i: max(0, i - window + 1)) if window else (lambda i: 0)
+    H, KV, n, gap = 2, 1, 250, 10.0
+    dtype = torch.float32 if kernel == "generic" else torch.bfloat16
+    k = torch.zeros(1, n, KV, hd, dtype=dtype, device=DEV)
+    v = torch.zeros(1, n, KV, hd, dtype=dtype, device=DEV)
+    j = torch.arange(n, device=DEV, dtype=torch.float32)
+    k[0, :, 0, 0] = (j if edge == "newest" else -j).to(dtype)          # whole numbers up to 256: exact in bfloat16
+    v[0, :, 0, 0] = j.to(dtype)
+    v[0, :, 0, 1] = 1.0
+    packed = torch.zeros(n, (H + 2 * KV) * hd, dtype=dtype, device=DEV)
+    packed[:, 0] = gap                                                   # both heads ask the same
+    packed[:, hd] = gap
+    kc, vc, bt = paged_from_dense(k, v, [n], seed=6)
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    zero = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((n, H * hd), float("nan"), dtype=dtype, device=DEV)
+    if kernel == "generic":
+        ops.attn_prefill_generic(packed, kc, vc, bt, cu, zero, zero, 1, n, H, KV, hd, 1.0, window_eff, out)
+    elif kernel == "mma":
+        ops.attn_prefill_tc(packed, kc, vc, bt, cu, zero, zero, 1, n, H, KV, hd, 1.0, window_eff, out)
+    else:
+        ops.attn_prefill_t5(packed, kc, vc, bt, cu, zero, zero, 1, n, H, KV, hd, 1.0, window_eff, out)
+        assert ops.attn_prefill_t5_status() == 0
+    want = torch.tensor([float(i if edge == "newest" else first(i)) for i in range(n)], device=DEV, dtype=torch.float64)
+    for h in range(H):
+        got = out[:, h * hd].double()
+        # the next key weighs e^-10 of the chosen one, and positions are whole numbers: half a position is a fault
+        assert float((got - want).abs().max()) < 0.3, (h, int((got - want).abs().argmax()), got[:8], want[:8])
+        torch.testing.assert_close(out[:, h * hd + 1].double(), torch.ones(n, device=DEV, dtype=torch.float64), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("kernel,hd", [("generic", 32), ("mma", 64), ("mma", 128)])
+@pytest.mark.parametrize("window,splits", [(None, 1), (None, 3), (37, 1), (64, 4), (100, 2)])
+@pytest.mark.parametrize("edge", ["newest", "oldest"])
+def test_decode_attention_edges_at_every_length(kernel, hd, window, splits, edge):
+    """The same for one-token steps: sequences of many lengths around the tiles' and pages' borders, each made to
+    look at its newest position or at the oldest it may see."""
+    lens = list(range(1, 36)) + [47, 48, 49, 63, 64, 65, 66, 100, 101, 127, 128, 129, 130, 191, 192, 193, 250]
+    B, S, H, KV, gap = len(lens), 256, 2, 1, 10.0
+    dtype = torch.float32 if kernel == "generic" else torch.bfloat16
+    k = torch.zeros(B, S, KV, hd, dtype=dtype, device=DEV)
+    v = torch.zeros(B, S, KV, hd, dtype=dtype, device=DEV)
+    j = torch.arange(S, device=DEV, dtype=torch.float32)
+    k[:, :, 0, 0] = (j if edge == "newest" else -j).to(dtype)
+    v[:, :, 0, 0] = j.to(dtype)
+    q = torch.zeros(B, H * hd, dtype=dtype, device=DEV)
+    q[:, 0] = gap
+    q[:, hd] = gap
+    kc, vc, bt = paged_from_dense(k, v, lens, seed=8)
+    out = torch.full((B, H * hd), float("nan"), dtype=dtype, device=DEV)
+    po = torch.full((B * H * splits * hd,), float("nan"), device=DEV)
+    pml = torch.full((B * H * splits * 2,), float("nan"), device=DEV)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    dev_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    fn = ops.attn_decode_generic if kernel == "generic" else ops.attn_decode_tc
+    fn(q, kc, vc, bt, slots, dev_lens, B, H, KV, hd, 1.0, window, splits, out, po, pml)
+    want = torch.tensor([float(n - 1 if edge == "newest" else (max(0, n - window) if window else 0)) for n in lens],
+                        device=DEV, dtype=torch.float64)
+    for h in range(H):
+        got = out[:, h * hd].double()
+        assert float((got - want).abs().max()) < 0.3, (h, lens[int((got - want).abs().argmax())], got, want)
 
 
 def test_argmax_first_on_ties_and_nan():
