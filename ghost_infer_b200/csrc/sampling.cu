@@ -12,6 +12,13 @@
 // picks the next byte.  Weights are 41-bit fixed point and summed as integers, so the result does not
 // depend on the order in which threads add.  Equal logits are ordered by token id (lower first), with
 // a second descent over the ids.  One block per row.
+//
+// The usual case, a top_k of at most 2048, takes a shorter way to the same pick: one sweep counts the keys by their
+// distance below the highest key (4096 bins of 2^16 key steps: the seven upper bits of the mantissa, 32 octaves),
+// which names the bin the k-th highest key lies in; a second sweep collects the keys down to that bin (top_k and
+// a few more) into shared memory, where they are sorted (key descending, token id ascending) and the cut and the
+// draw are made over at most top_k entries with the same fixed-point weights and the same rules.  Some twenty
+// sweeps over the row, with an exponential per logit in half of them, become two sweeps and top_k exponentials.
 #include <math.h>
 
 #include "api.h"
@@ -37,7 +44,13 @@ __device__ __forceinline__ u64 fixed_weight(float logit, float lmax, float tempe
   return __float2ull_rn(expf((logit - lmax) / temperature) * FIXED_ONE);
 }
 
+constexpr int FAST_BINS = 4096;      // keys by their distance below the highest key, in steps of 2^16
+constexpr int FAST_CAP = 2048;       // candidates the short way can hold
+
 struct Shared {
+  unsigned bins[FAST_BINS];
+  u64 list[FAST_CAP];                // (key << 32) | ~id: descending order = key descending, id ascending
+  int n_list, first_bin;
   u64 hist[256];
   u64 red64[32];
   float redv[32];
@@ -226,6 +239,120 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, 
     s ^= s >> 27;
     rng_state[si] = s;
     sh.u = (float)((s * 0x2545F4914F6CDD1DULL) >> 40) / 16777216.0f;
+  }
+
+  // ---- the short way (see the head of this file)
+  if (top_k > 0 && top_k < n && top_k <= FAST_CAP) {
+    for (int b = tid; b < FAST_BINS; b += blockDim.x) sh.bins[b] = 0;
+    if (tid == 0) sh.n_list = 0;
+    __syncthreads();
+    // (eight loads in flight per thread: one at a time, a sweep waits for the L2 cache 125 times in a row)
+    const unsigned top_key = order_key(lmax);
+    for (int i0 = 0; i0 < n; i0 += 8 * blockDim.x) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * blockDim.x + tid;
+        v[u] = i < n ? row[i] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * blockDim.x + tid;
+        const unsigned below = (top_key - order_key(v[u])) >> 16;       // a NaN's key is 0: far below
+        if (i < n && below < FAST_BINS) atomicAdd(&sh.bins[below], 1u);
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      // from the highest key's bin downwards until top_k keys are covered (or the bins end: then the long way)
+      unsigned covered = 0;
+      int b = 0;
+      for (; b < FAST_BINS; ++b) {
+        covered += sh.bins[b];
+        if (covered >= (unsigned)top_k) break;
+      }
+      sh.first_bin = b;
+      sh.n_list = b < FAST_BINS ? (int)covered : FAST_CAP + 1;
+    }
+    __syncthreads();
+    const int total_c = sh.n_list;
+    const unsigned last_bin = (unsigned)sh.first_bin;
+    __syncthreads();
+    if (total_c <= FAST_CAP) {
+      if (tid == 0) sh.n_list = 0;
+      __syncthreads();
+      for (int i0 = 0; i0 < n; i0 += 8 * blockDim.x) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * blockDim.x + tid;
+          v[u] = i < n ? row[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * blockDim.x + tid;
+          const unsigned key = order_key(v[u]);
+          if (i < n && ((top_key - key) >> 16) <= last_bin) {
+            const int at = atomicAdd(&sh.n_list, 1);
+            sh.list[at] = ((u64)key << 32) | (u64)(~(unsigned)i);
+          }
+        }
+      }
+      __syncthreads();
+      // bitonic sort, descending, over the next power of two (the padding, zeros, sorts to the end)
+      int m = 1;
+      while (m < total_c) m <<= 1;
+      for (int i = total_c + tid; i < m; i += blockDim.x) sh.list[i] = 0;
+      __syncthreads();
+      for (int size = 2; size <= m; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+          for (int t = tid; t < m / 2; t += blockDim.x) {
+            const int lo = 2 * t - (t & (stride - 1)), hi = lo + stride;
+            const bool down = (lo & size) == 0;                  // this run sorts descending
+            const u64 a = sh.list[lo], b = sh.list[hi];
+            if ((a < b) == down) {
+              sh.list[lo] = b;
+              sh.list[hi] = a;
+            }
+          }
+          __syncthreads();
+        }
+      }
+      if (tid == 0) {
+        const int k = top_k < total_c ? top_k : total_c;
+        auto weight_at = [&](int j) { return fixed_weight(key_value((unsigned)(sh.list[j] >> 32)), lmax, temperature); };
+        u64 total = 0;
+        for (int j = 0; j < k; ++j) total += weight_at(j);
+        int kept = k;
+        u64 mass = total;
+        if (top_p < 1.0f && total > 0) {
+          u64 target = (u64)ceil((double)top_p * (double)total);
+          target = target < 1 ? 1 : (target > total ? total : target);
+          u64 run = 0;
+          for (int j = 0; j < k; ++j) {
+            run += weight_at(j);
+            if (run >= target) {
+              kept = j + 1;
+              mass = run;
+              break;
+            }
+          }
+        }
+        u64 target = (u64)ceil((double)sh.u * (double)mass);
+        target = target < 1 ? 1 : (target > mass ? mass : target);
+        int pick = kept - 1;
+        u64 run = 0;
+        for (int j = 0; j < kept; ++j) {
+          run += weight_at(j);
+          if (run >= target) {
+            pick = j;
+            break;
+          }
+        }
+        out[r] = mass > 0 ? (int)(~(unsigned)(sh.list[pick] & 0xffffffffu)) : sh.besti;
+      }
+      return;
+    }
   }
 
   const int ishift = index_start_shift(n);

@@ -380,6 +380,8 @@ def test_sampler_matches_the_plain_sampler(vocab, temp, top_k, top_p):
     logits = (torch.randn(rows, vocab, generator=g) * 2.0)
     logits[1, :50] = logits[1, 0]                       # ties, ordered by token id
     logits[2] = torch.round(logits[2])                  # many ties
+    logits[3, 7 % vocab] = 1e30                         # one logit far above all others (nothing else near its key)
+    logits[4] = -logits[4].abs() - 5.0                  # negative only
     dev = logits.to(DEV)
     seeds = [1, 2, 3, 99, 2 ** 40 + 7, 12345]
     state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
