@@ -20,6 +20,7 @@
 // draw are made over at most top_k entries with the same fixed-point weights and the same rules.  Some twenty
 // sweeps over the row, with an exponential per logit in half of them, become two sweeps and top_k exponentials.
 #include <math.h>
+#include <stddef.h>
 
 #include "api.h"
 #include "common.cuh"
@@ -49,7 +50,9 @@ constexpr int FAST_CAP = 2048;       // candidates the short way can hold
 
 struct Shared {
   unsigned bins[FAST_BINS];
-  u64 list[FAST_CAP];                // (key << 32) | ~id: descending order = key descending, id ascending
+  u64 list[FAST_CAP];                // (key << 32) | ~id: descending order = key descending, id ascending; the long way
+                                     // keeps sixteen copies of its histogram in `bins` and here (64-bit additions to
+                                     // shared memory are compare-and-swap loops: a copy per two warps spares them the crowd)
   int n_list, first_bin;
   u64 hist[256];
   u64 red64[32];
@@ -63,12 +66,13 @@ struct Shared {
   float u;
 };
 
-// Descends the bytes of `val` from `start_shift` down.  elem(i, val, wt) says whether element i takes
-// part and gives its ordering value and weight.  On return: `val_out` is the value at which the running
+// Descends the bytes of `val` from `start_shift` down.  elem(i, val) says whether element i takes part and
+// gives its ordering value; weight(i, val) its weight, asked only for elements that still match the bytes found
+// so far (an exponential each: after the first byte few elements are left).  On return: `val_out` is the value at which the running
 // sum (in descending order if DESC, else ascending) first reaches `target`; `before` is the weight
 // ordered strictly before it; `equal` the weight of the elements equal to it.
-template <bool DESC, typename F>
-__device__ void radix_descend(Shared& sh, int n, int start_shift, u64 target, F elem, unsigned& val_out, u64& before_out,
+template <bool DESC, typename F, typename W>
+__device__ void radix_descend(Shared& sh, int n, int start_shift, u64 target, F elem, W weight, unsigned& val_out, u64& before_out,
                               u64& equal_out) {
   const int tid = threadIdx.x;
   if (tid == 0) {
@@ -76,27 +80,39 @@ __device__ void radix_descend(Shared& sh, int n, int start_shift, u64 target, F 
     sh.before = 0;
     sh.equal = 0;
   }
+  constexpr int COPIES = 16;                               // over `bins` and `list`, which lie one after the other
+  static_assert(offsetof(Shared, list) == sizeof(unsigned) * FAST_BINS, "the copies span bins and list");
+  u64* copies = reinterpret_cast<u64*>(sh.bins);           // [COPIES][256]
+  u64* my_hist = copies + ((tid >> 5) % COPIES) * 256;
   for (int shift = start_shift; shift >= 0; shift -= 8) {
-    for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0;
+    for (int b = tid; b < COPIES * 256; b += blockDim.x) copies[b] = 0;
     __syncthreads();
     const unsigned prefix = sh.prefix;
     const bool check = shift != start_shift;
     int cur = -1;
     u64 run = 0;
+#pragma unroll 8
     for (int i = tid; i < n; i += blockDim.x) {
       unsigned val;
-      u64 wt;
-      if (!elem(i, val, wt)) continue;
+      if (!elem(i, val)) continue;
       if (check && (val >> (shift + 8)) != prefix) continue;
+      const u64 wt = weight(i, val);
       const int bin = (int)((val >> shift) & 255u);
       if (bin != cur) {
-        if (run) atomicAdd(&sh.hist[cur], run);
+        if (run) atomicAdd(&my_hist[cur], run);
         cur = bin;
         run = 0;
       }
       run += wt;
     }
-    if (run) atomicAdd(&sh.hist[cur], run);
+    if (run) atomicAdd(&my_hist[cur], run);
+    __syncthreads();
+    for (int b = tid; b < 256; b += blockDim.x) {
+      u64 t = 0;
+#pragma unroll
+      for (int c = 0; c < COPIES; ++c) t += copies[c * 256 + b];
+      sh.hist[b] = t;
+    }
     __syncthreads();
     if (tid == 0) {
       u64 acc = sh.before;
@@ -363,14 +379,13 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, 
   unsigned kth = 0;
   int kth_last = n;  // ids <= kth_last with key == kth are candidates
   if (top_k > 0 && top_k < n) {
-    radix_descend<true>(sh, n, 24, (u64)top_k,
-                        [&](int i, unsigned& v, u64& w) { v = order_key(row[i]); w = 1; return true; }, val, before, equal);
+    radix_descend<true>(sh, n, 24, (u64)top_k, [&](int i, unsigned& v) { v = order_key(row[i]); return true; },
+                        [&](int, unsigned) { return (u64)1; }, val, before, equal);
     kth = val;
     const u64 need = (u64)top_k - before;
     if (need < equal) {
-      radix_descend<false>(sh, n, ishift, need,
-                           [&](int i, unsigned& v, u64& w) { v = (unsigned)i; w = 1; return order_key(row[i]) == kth; }, val,
-                           before, equal);
+      radix_descend<false>(sh, n, ishift, need, [&](int i, unsigned& v) { v = (unsigned)i; return order_key(row[i]) == kth; },
+                           [&](int, unsigned) { return (u64)1; }, val, before, equal);
       kth_last = (int)val;
     }
   }
@@ -378,6 +393,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, 
 
   // ---- total weight of the candidates
   u64 mine = 0;
+#pragma unroll 8
   for (int i = tid; i < n; i += blockDim.x) {
     const float v = row[i];
     if (candidate(i, order_key(v))) mine += fixed_weight(v, lmax, temperature);
@@ -391,14 +407,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, 
   if (top_p < 1.0f && total > 0) {
     u64 target = (u64)ceil((double)top_p * (double)total);
     target = target < 1 ? 1 : (target > total ? total : target);
-    radix_descend<true>(sh, n, 24, target,
-                        [&](int i, unsigned& v, u64& w) {
-                          const float x = row[i];
-                          v = order_key(x);
-                          w = fixed_weight(x, lmax, temperature);
-                          return candidate(i, v);
-                        },
-                        val, before, equal);
+    radix_descend<true>(sh, n, 24, target, [&](int i, unsigned& v) { v = order_key(row[i]); return candidate(i, v); },
+                        [&](int, unsigned v) { return fixed_weight(key_value(v), lmax, temperature); }, val, before, equal);
     cut = val;
     const u64 wc = fixed_weight(key_value(cut), lmax, temperature);
     if (wc > 0) {
@@ -408,12 +418,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, 
       mass = before + j * wc;
       if (j < n_eq) {
         radix_descend<false>(sh, n, ishift, j,
-                             [&](int i, unsigned& v, u64& w) {
-                               v = (unsigned)i;
-                               w = 1;
-                               return order_key(row[i]) == cut && candidate(i, cut);
-                             },
-                             val, before, equal);
+                             [&](int i, unsigned& v) { v = (unsigned)i; return order_key(row[i]) == cut && candidate(i, cut); },
+                             [&](int, unsigned) { return (u64)1; }, val, before, equal);
         cut_last = (int)val;
       }
     } else {
@@ -425,14 +431,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, 
   // ---- the draw: the first kept candidate, in descending order, at which the running sum reaches u * mass
   u64 target = (u64)ceil((double)sh.u * (double)mass);
   target = target < 1 ? 1 : (target > mass ? mass : target);
-  radix_descend<true>(sh, n, 24, target,
-                      [&](int i, unsigned& v, u64& w) {
-                        const float x = row[i];
-                        v = order_key(x);
-                        w = fixed_weight(x, lmax, temperature);
-                        return kept(i, v);
-                      },
-                      val, before, equal);
+  radix_descend<true>(sh, n, 24, target, [&](int i, unsigned& v) { v = order_key(row[i]); return kept(i, v); },
+                      [&](int, unsigned v) { return fixed_weight(key_value(v), lmax, temperature); }, val, before, equal);
   const unsigned sel = val;
   const u64 ws = fixed_weight(key_value(sel), lmax, temperature);
   u64 jj = 1;
@@ -441,13 +441,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, 
     jj = (target - before + ws - 1) / ws;
     jj = jj < 1 ? 1 : (jj > n_eq ? n_eq : jj);
   }
-  radix_descend<false>(sh, n, ishift, jj,
-                       [&](int i, unsigned& v, u64& w) {
-                         v = (unsigned)i;
-                         w = 1;
-                         return order_key(row[i]) == sel && kept(i, sel);
-                       },
-                       val, before, equal);
+  radix_descend<false>(sh, n, ishift, jj, [&](int i, unsigned& v) { v = (unsigned)i; return order_key(row[i]) == sel && kept(i, sel); },
+                       [&](int, unsigned) { return (u64)1; }, val, before, equal);
   if (tid == 0) out[r] = equal > 0 ? (int)val : sh.besti;
 }
 
