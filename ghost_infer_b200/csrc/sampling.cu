@@ -163,6 +163,51 @@ __device__ u64 block_sum_u64(Shared& sh, u64 v) {
   return sh.total;
 }
 
+// The first place j < count (count <= 2 * blockDim.x) at which base + item(0) + ... + item(j) reaches `target`, found by
+// the whole block: every thread takes two neighbouring items, a scan over the threads gives each the sum before its
+// pair.  Returns the place (-1: the sum never gets there), `before_out` = base + the items before it, `total_out` =
+// the sum of all items.  Sums are integers: no order of additions can change them.
+template <typename F>
+__device__ int first_reaching(Shared& sh, int count, u64 base, u64 target, F item, u64& before_out, u64& total_out) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int j0 = 2 * tid;
+  const u64 a = j0 < count ? item(j0) : 0, b = j0 + 1 < count ? item(j0 + 1) : 0;
+  u64 incl = a + b;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const u64 up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  __syncthreads();
+  if (lane == 31) sh.red64[warp] = incl;
+  if (tid == 0) sh.first_bin = 0x7fffffff;
+  __syncthreads();
+  if (warp == 0) {
+    u64 t = lane < (int)(blockDim.x >> 5) ? sh.red64[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const u64 up = __shfl_up_sync(0xffffffffu, t, o);
+      if (lane >= o) t += up;
+    }
+    sh.red64[lane] = t;                               // inclusive over the warps
+  }
+  __syncthreads();
+  const u64 mine_before = base + (warp > 0 ? sh.red64[warp - 1] : 0) + (incl - a - b);
+  int found = 0x7fffffff;
+  if (j0 < count && mine_before + a >= target) found = j0;
+  else if (j0 + 1 < count && mine_before + a + b >= target) found = j0 + 1;
+  if (found != 0x7fffffff) atomicMin(&sh.first_bin, found);
+  __syncthreads();
+  const int first = sh.first_bin;
+  if (found != 0x7fffffff && first == found) sh.before = (found == j0) ? mine_before : mine_before + a;
+  __syncthreads();
+  before_out = sh.before;
+  total_out = sh.red64[(blockDim.x >> 5) - 1];
+  const int result = first == 0x7fffffff ? -1 : first;
+  __syncthreads();
+  return result;
+}
+
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, int n, float temperature, int top_k,
               float top_p, u64* __restrict__ rng_state, const int* __restrict__ state_index) {
@@ -334,41 +379,154 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, 
           __syncthreads();
         }
       }
-      if (tid == 0) {
-        const int k = top_k < total_c ? top_k : total_c;
-        auto weight_at = [&](int j) { return fixed_weight(key_value((unsigned)(sh.list[j] >> 32)), lmax, temperature); };
-        u64 total = 0;
-        for (int j = 0; j < k; ++j) total += weight_at(j);
-        int kept = k;
-        u64 mass = total;
-        if (top_p < 1.0f && total > 0) {
-          u64 target = (u64)ceil((double)top_p * (double)total);
-          target = target < 1 ? 1 : (target > total ? total : target);
-          u64 run = 0;
-          for (int j = 0; j < k; ++j) {
-            run += weight_at(j);
-            if (run >= target) {
-              kept = j + 1;
-              mass = run;
-              break;
-            }
-          }
+      const int k = top_k < total_c ? top_k : total_c;
+      auto weight_at = [&](int j) { return fixed_weight(key_value((unsigned)(sh.list[j] >> 32)), lmax, temperature); };
+      u64 upto = 0, total = 0, unused = 0;
+      first_reaching(sh, k, 0, ~(u64)0, weight_at, upto, total);                      // (only the total is wanted here)
+      int kept = k;
+      u64 mass = total;
+      if (top_p < 1.0f && total > 0) {
+        u64 target = (u64)ceil((double)top_p * (double)total);
+        target = target < 1 ? 1 : (target > total ? total : target);
+        const int j = first_reaching(sh, k, 0, target, weight_at, upto, unused);
+        if (j >= 0) {
+          kept = j + 1;
+          mass = upto + weight_at(j);
         }
-        u64 target = (u64)ceil((double)sh.u * (double)mass);
-        target = target < 1 ? 1 : (target > mass ? mass : target);
-        int pick = kept - 1;
-        u64 run = 0;
-        for (int j = 0; j < kept; ++j) {
-          run += weight_at(j);
-          if (run >= target) {
-            pick = j;
-            break;
-          }
-        }
-        out[r] = mass > 0 ? (int)(~(unsigned)(sh.list[pick] & 0xffffffffu)) : sh.besti;
       }
+      u64 target = (u64)ceil((double)sh.u * (double)mass);
+      target = target < 1 ? 1 : (target > mass ? mass : target);
+      int pick = first_reaching(sh, kept, 0, target, weight_at, upto, unused);
+      if (pick < 0) pick = kept - 1;
+      if (tid == 0) out[r] = mass > 0 ? (int)(~(unsigned)(sh.list[pick] & 0xffffffffu)) : sh.besti;
       return;
     }
+  }
+
+  // ---- the short way without a top_k: every logit is a candidate.  Weights are summed by the logits' distance below
+  // the highest one, in 2048 equal steps over the 29 T within which a weight is not yet zero in fixed point (the
+  // step is monotone in the logit, so the bins keep the descending order); the bins say in which one the cut of
+  // top_p and the draw fall, and only that bin's logits are gathered and sorted.  If a bin holds more than the list
+  // takes, the long way below does the whole job.
+  if (!(top_k > 0 && top_k < n)) {
+    constexpr int WBINS = 2048;
+    // a bin's sum as two 32-bit words (additions of 32 bits to shared memory are one instruction, those of 64 bits a
+    // compare-and-swap loop): the low word's overflow is carried into the high word by whoever caused it
+    unsigned* wlo = sh.bins;
+    unsigned* whi = sh.bins + WBINS;
+    auto wb_at = [&](int b) { return ((u64)whi[b] << 32) | (u64)wlo[b]; };
+    const float per_logit = (float)WBINS / (29.0f * temperature);
+    auto bin_of = [&](float v) { return (int)fminf((lmax - v) * per_logit, 1.0e9f); };      // >= WBINS: weight 0
+    for (int b = tid; b < 2 * WBINS; b += blockDim.x) sh.bins[b] = 0;
+    __syncthreads();
+    u64 rest_mine = 0;
+    for (int i0 = 0; i0 < n; i0 += 8 * blockDim.x) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * blockDim.x + tid;
+        v[u] = i < n ? row[i] : __int_as_float(0x7fc00000);        // past the row: not a number, weight 0
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const u64 w = fixed_weight(v[u], lmax, temperature);
+        const int below = bin_of(v[u]);
+        if (w == 0) continue;
+        if (below < WBINS) {
+          const unsigned lo = (unsigned)w, hi = (unsigned)(w >> 32);
+          const unsigned old = atomicAdd(&wlo[below], lo);
+          const unsigned carry = (old + lo < old) ? 1u : 0u;
+          if (hi + carry) atomicAdd(&whi[below], hi + carry);
+        } else {
+          rest_mine += w;                                             // (none, by the choice of the steps)
+        }
+      }
+    }
+    const u64 rest = block_sum_u64(sh, rest_mine);                  // (synchronises)
+    // gathers bin `b` into the list, sorted; false if it does not fit
+    auto gather_sorted = [&](int b) -> bool {
+      __syncthreads();
+      if (tid == 0) sh.n_list = 0;
+      __syncthreads();
+      for (int i0 = 0; i0 < n; i0 += 8 * blockDim.x) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * blockDim.x + tid;
+          v[u] = i < n ? row[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * blockDim.x + tid;
+          const unsigned key = order_key(v[u]);
+          if (i < n && bin_of(v[u]) == b && fixed_weight(v[u], lmax, temperature) > 0) {
+            const int at = atomicAdd(&sh.n_list, 1);
+            if (at < FAST_CAP) sh.list[at] = ((u64)key << 32) | (u64)(~(unsigned)i);
+          }
+        }
+      }
+      __syncthreads();
+      const int c = sh.n_list;
+      if (c > FAST_CAP) return false;
+      int m = 1;
+      while (m < c) m <<= 1;
+      for (int i = c + tid; i < m; i += blockDim.x) sh.list[i] = 0;
+      __syncthreads();
+      for (int size = 2; size <= m; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+          for (int t = tid; t < m / 2; t += blockDim.x) {
+            const int lo = 2 * t - (t & (stride - 1)), hi = lo + stride;
+            const bool down = (lo & size) == 0;
+            const u64 a = sh.list[lo], bb = sh.list[hi];
+            if ((a < bb) == down) {
+              sh.list[lo] = bb;
+              sh.list[hi] = a;
+            }
+          }
+          __syncthreads();
+        }
+      }
+      return true;
+    };
+    auto weight_of = [&](int j) { return fixed_weight(key_value((unsigned)(sh.list[j] >> 32)), lmax, temperature); };
+    u64 before = 0, bins_total = 0, unused = 0;
+    first_reaching(sh, WBINS, 0, ~(u64)0, wb_at, before, bins_total);                 // (only the total is wanted here)
+    const u64 total = bins_total + rest;
+    bool fits = total > 0;
+    u64 mass = total;
+    int cut_bin = WBINS;                 // bins before this one are kept whole; of this one, the first cut_count entries
+    int cut_count = 0;
+    if (fits && top_p < 1.0f) {
+      u64 target = (u64)ceil((double)top_p * (double)total);
+      target = target < 1 ? 1 : (target > total ? total : target);
+      cut_bin = first_reaching(sh, WBINS, 0, target, wb_at, before, unused);
+      fits = cut_bin >= 0 && gather_sorted(cut_bin);
+      if (fits) {
+        u64 upto = 0;
+        const int j = first_reaching(sh, sh.n_list, before, target, weight_of, upto, unused);
+        fits = j >= 0;                   // (always: the bin's sum reaches the target)
+        if (fits) {
+          cut_count = j + 1;
+          mass = upto + weight_of(j);
+        }
+      }
+    }
+    if (fits) {
+      u64 target = (u64)ceil((double)sh.u * (double)mass);
+      target = target < 1 ? 1 : (target > mass ? mass : target);
+      const int draw_bin = first_reaching(sh, WBINS, 0, target, wb_at, before, unused);
+      fits = draw_bin >= 0;
+      if (fits && draw_bin != cut_bin) fits = gather_sorted(draw_bin);      // (the cut's bin is still in the list)
+      if (fits) {
+        const int limit = draw_bin == cut_bin ? cut_count : sh.n_list;
+        u64 upto = 0;
+        int pick = first_reaching(sh, limit, before, target, weight_of, upto, unused);
+        if (pick < 0) pick = limit - 1;
+        if (tid == 0) out[r] = pick >= 0 ? (int)(~(unsigned)(sh.list[pick] & 0xffffffffu)) : sh.besti;
+        return;
+      }
+    }
+    __syncthreads();
   }
 
   const int ishift = index_start_shift(n);

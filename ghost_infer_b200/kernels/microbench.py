@@ -126,7 +126,10 @@ def main() -> int:
         state = torch.arange(1, args.m + 1, dtype=torch.int64, device=dev)
         us_g = _time(lambda i: ops.sample(logits, 0.0, 0, 1.0), 1, args.iters, args.warmup)
         us_s = _time(lambda i: ops.sample(logits, 0.7, 40, 0.9, state), 1, args.iters, args.warmup)
-        out.update(shape=[args.m, args.n], us_greedy=round(us_g, 2), us_top_k_top_p=round(us_s, 2))
+        us_t = _time(lambda i: ops.sample(logits, 0.7, 0, 1.0, state), 1, args.iters, args.warmup)
+        us_p = _time(lambda i: ops.sample(logits, 0.7, 0, 0.9, state), 1, args.iters, args.warmup)
+        out.update(shape=[args.m, args.n], us_greedy=round(us_g, 2), us_top_k_top_p=round(us_s, 2), us_temperature=round(us_t, 2),
+                   us_top_p=round(us_p, 2))
     else:
         ap.error(f"unknown kernel {args.kernel}")
     print(json.dumps(out))
