@@ -407,6 +407,9 @@ def _next_weights(w: torch.Tensor, mode: int):
     global _last_streamed
     here = w.data_ptr()
     if _last_streamed is not None and _last_streamed != here:
+        if len(_followed_by) > 4096:                     # models come and go: forget the weights that are gone
+            for key in [k for k, (ref, _) in _followed_by.items() if ref() is None]:
+                del _followed_by[key]
         _followed_by[_last_streamed] = (weakref.ref(w), mode)
     _last_streamed = here
     ref, next_mode = _followed_by.get(here, (None, 0))
