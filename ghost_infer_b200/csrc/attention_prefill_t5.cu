@@ -23,7 +23,8 @@ using namespace gi::tc;
 
 constexpr int BQ = 128;          // queries per block = tensor-memory lanes
 constexpr int BKV = 64;          // keys per tile = one page
-constexpr int THREADS = 160;     // warps 0-3: one query row per thread; warp 4: TMA and MMA issue
+constexpr int THREADS = 192;     // warps 0-3: one query row per thread; warp 4: queries, keys and the score products;
+                                 // warp 5: values and the output products
 constexpr int TMEM_COLS = 256;   // S: columns 0..63, O: columns 64..64 + head size - 1
 constexpr uint32_t Q_HALF = BQ * 128, KV_HALF = BKV * 128;   // a 64-dimension half of a tile: rows of 128 bytes, swizzled
 constexpr uint32_t P_BYTES = BQ * BKV * 2;
@@ -131,69 +132,92 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
   gi::pdl_prologue();      // set-up overlapped the previous kernel's end; its results are visible from here on
 
+  // Two threads issue the products, each with its own loads, so that neither chain waits behind the other's
+  // barriers: S(j+1) = Q K(j+1)^T wants only the keys and the score buffer back (the rows of S(j) read into
+  // registers), O += P(j) V(j) wants the probabilities staged.  One thread for both spent half a tile's time in
+  // the one chain's waits while the other chain was ready.
+  auto row_of = [&](int tile) {        // where a tile's keys and values lie: the page comes from the sequence's page table
+    const int kt = kt_begin + tile * BKV;
+    const int page = block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS];
+    return (page * n_kv + kvh) * PAGE_TOKENS;
+  };
   if (warp == 4) {
     if (lane == 0) {
       bool ok = true;
-      auto load_kv = [&](int tile) {
-        const int s = tile & 1;
-        const int kt = kt_begin + tile * BKV;
-        const int page = block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS];
-        const int row0 = (page * n_kv + kvh) * PAGE_TOKENS;
+      auto load_k = [&](int tile) {
+        const int s = tile & 1, row0 = row_of(tile);
         mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
 #pragma unroll
         for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(smem_u32(k_s + s * KV_BYTES + hf * KV_HALF), &map_k, hf * 64, row0, k_full0 + 8 * s);
-        mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
-#pragma unroll
-        for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(smem_u32(v_s + s * KV_BYTES + hf * KV_HALF), &map_v, hf * 64, row0, v_full0 + 8 * s);
       };
       mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
       for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(smem_u32(q_s + hf * Q_HALF), &map_q, h * HD + hf * 64, tok0 + q0, q_full);
-      load_kv(0);
+      load_k(0);
+      if (n_tiles > 1) load_k(1);
       ok = mbar_wait(q_full, 0, 1, &g_attn_status);
-      // S = Q K^T of tile j into tensor memory (the keys are here; the rows of the previous S have been read)
-      auto scores = [&](int j) -> bool {
-        const int s = j & 1;
-        bool good = mbar_wait(k_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 2, &g_attn_status);
-        if (good && j >= 1) good = mbar_wait(s_free, (uint32_t)((j - 1) & 1), 2, &g_attn_status);
-        if (!good) return false;
-        tc_fence_after();
-        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + s * KV_BYTES);
+      // the operands' descriptors do not change from tile to tile (but for the stage): made once
+      uint64_t dq[HD / 16], dk[2][HD / 16];
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint64_t dq = smem_desc(qa + (ks / 4) * Q_HALF + (ks % 4) * 32);
-          const uint64_t dk = smem_desc(ka + (ks / 4) * KV_HALF + (ks % 4) * 32);
-          tc_mma(tmem_s, dq, dk, IDESC_S, ks > 0 ? 1u : 0u);
-        }
-        tc_commit(s_full);
-        return true;
-      };
-      if (ok) ok = scores(0);
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        dq[ks] = smem_desc(smem_u32(q_s) + (ks / 4) * Q_HALF + (ks % 4) * 32);
+        dk[0][ks] = smem_desc(smem_u32(k_s) + (ks / 4) * KV_HALF + (ks % 4) * 32);
+        dk[1][ks] = smem_desc(smem_u32(k_s) + KV_BYTES + (ks / 4) * KV_HALF + (ks % 4) * 32);
+      }
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
-        if (j + 1 < n_tiles) {
-          // the other stage was last used by tile j - 1, whose second product frees it
-          if (j >= 1) ok = mbar_wait(kv_empty0 + 8 * (s ^ 1), (uint32_t)(((j - 1) >> 1) & 1), 1, &g_attn_status);
+        // the keys are here, and the rows of the previous S have been read
+        ok = mbar_wait(k_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 2, &g_attn_status);
+        if (ok && j >= 1) ok = mbar_wait(s_free, (uint32_t)((j - 1) & 1), 2, &g_attn_status);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) tc_mma(tmem_s, dq[ks], s ? dk[1][ks] : dk[0][ks], IDESC_S, ks > 0 ? 1u : 0u);
+        tc_commit(s_full);
+        // keys two tiles ahead go into this tile's stage as soon as its scores are complete: a whole tile's softmax
+        // before they are wanted
+        if (j + 2 < n_tiles) {
+          ok = mbar_wait(s_full, (uint32_t)(j & 1), 2, &g_attn_status);
           if (!ok) break;
-          load_kv(j + 1);
-          // the next tile's scores are computed while the rows of this tile turn their scores into probabilities
-          ok = scores(j + 1);
-          if (!ok) break;
+          load_k(j + 2);
         }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      bool ok = true;
+      auto load_v = [&](int tile) {
+        const int s = tile & 1, row0 = row_of(tile);
+        mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(smem_u32(v_s + s * KV_BYTES + hf * KV_HALF), &map_v, hf * 64, row0, v_full0 + 8 * s);
+      };
+      load_v(0);
+      if (n_tiles > 1) load_v(1);
+      uint64_t dp[BKV / 16], dv[2][BKV / 16];
+#pragma unroll
+      for (int kk = 0; kk < BKV / 16; ++kk) {
+        dp[kk] = smem_desc(smem_u32(p_s) + kk * 32);
+        dv[0][kk] = smem_desc_mn(smem_u32(v_s) + kk * 2048, KV_HALF);
+        dv[1][kk] = smem_desc_mn(smem_u32(v_s) + KV_BYTES + kk * 2048, KV_HALF);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
         // O += P V once the probabilities are staged (which also says: O has been rescaled) and the values are here
         ok = mbar_wait(p_full, (uint32_t)(j & 1), 2, &g_attn_status);
         if (ok) ok = mbar_wait(v_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 2, &g_attn_status);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + s * KV_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          const uint64_t dp = smem_desc(pa + kk * 32);
-          const uint64_t dv = smem_desc_mn(va + kk * 2048, KV_HALF);
-          tc_mma(tmem_o, dp, dv, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < BKV / 16; ++kk) tc_mma(tmem_o, dp[kk], s ? dv[1][kk] : dv[0][kk], IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(kv_empty0 + 8 * s);
         tc_commit(o_full);
+        // values two tiles ahead go into this tile's stage once this product no longer reads it
+        if (j + 2 < n_tiles) {
+          ok = mbar_wait(kv_empty0 + 8 * s, (uint32_t)((j >> 1) & 1), 1, &g_attn_status);
+          if (!ok) break;
+          load_v(j + 2);
+        }
       }
     }
   } else {
