@@ -3,13 +3,14 @@
 //
 // Formula: src/model.rs:1320-1419.  The reference's prompt attention (attention_prefill_tc, src/cuda.rs:2408-2613)
 // keeps scores in registers of mma.sync fragments; on sm_100a the same algorithm is laid out around tensor memory:
-// a block takes 128 queries of one head.  One thread issues TMA loads (queries once, then 64-key tiles of K and V
-// fetched page by page through the sequence's page table) and the tcgen05.mma instructions: S = Q K^T into tensor
-// memory, and O += P V with V read in its stored (dimension-contiguous) layout.  Four warps own one query row per
-// thread: they read a row of S with tcgen05.ld, keep the running maximum and sum in 32-bit (base-2 exponentials),
-// write the probabilities as bfloat16 into a swizzled shared-memory tile that the second product reads, and rescale
-// the accumulator in tensor memory when a row's maximum moves.  Two blocks share an SM, so one block's softmax
-// overlaps the other's products.  Every wait has an iteration limit and reports through a status word.
+// a block takes 128 queries of one head.  One thread issues the TMA loads of the queries and of 64-key tiles of K
+// (fetched page by page through the sequence's page table, two tiles ahead) and the score products S = Q K^T into
+// one of two score buffers in tensor memory; another thread issues the loads of V and the output products
+// O += P V, with P read from tensor memory and V in its stored (dimension-contiguous) layout.  Four warps own one
+// query row per thread: they read a row of S with tcgen05.ld, keep the running maximum and sum in 32-bit (base-2
+// exponentials), write the probabilities as bfloat16 over the scores they have just read (tcgen05.st), and
+// rescale the accumulator in tensor memory when a row's reference point moves.  Two blocks share an SM, so one
+// block's softmax overlaps the other's products.  Every wait has an iteration limit and reports through a status word.
 #include <cuda.h>
 #include <math.h>
 
@@ -25,9 +26,9 @@ constexpr int BQ = 128;          // queries per block = tensor-memory lanes
 constexpr int BKV = 64;          // keys per tile = one page
 constexpr int THREADS = 192;     // warps 0-3: one query row per thread; warp 4: queries, keys and the score products;
                                  // warp 5: values and the output products
-constexpr int TMEM_COLS = 256;   // S: columns 0..63, O: columns 64..64 + head size - 1
+constexpr int TMEM_COLS = 256;   // two score buffers of 64 columns (tile j in buffer j & 1; its probabilities, two bfloat16 to a
+                                 // column, take the buffer's first 32 columns once the scores are read), then O: head size columns
 constexpr uint32_t Q_HALF = BQ * 128, KV_HALF = BKV * 128;   // a 64-dimension half of a tile: rows of 128 bytes, swizzled
-constexpr uint32_t P_BYTES = BQ * BKV * 2;
 
 __device__ int g_attn_status = 0;
 
@@ -47,6 +48,15 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// D (+)= A B with A read from tensor memory: 128 lanes = rows, each 32-bit column two neighbouring bfloat16 of K.
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -79,8 +89,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   unsigned char* q_s = smem;                              // [halves][128 rows][64 dims]
   unsigned char* k_s = q_s + Q_BYTES;                     // [2 stages][halves][64 keys][64 dims]
   unsigned char* v_s = k_s + 2 * KV_BYTES;                // the same
-  unsigned char* p_s = v_s + 2 * KV_BYTES;                // [128 rows][64 keys]
-  uint64_t* bars = (uint64_t*)(p_s + P_BYTES);            // q_full, k_full[2], v_full[2], kv_empty[2], s_full, s_free, p_full, o_full
+  uint64_t* bars = (uint64_t*)(v_s + 2 * KV_BYTES);       // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], p_full, o_full
   uint32_t* tmem_slot = (uint32_t*)(bars + 12);
 
   // Blocks start in the order x, y, z: heads fastest (the heads of a group read the same keys and values at the
@@ -106,7 +115,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = bar0 + 24, kv_empty0 = bar0 + 40;
-  const uint32_t s_full = bar0 + 56, s_free = bar0 + 64, p_full = bar0 + 72, o_full = bar0 + 80;
+  const uint32_t s_full0 = bar0 + 56, p_full = bar0 + 72, o_full = bar0 + 80;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -115,8 +124,8 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(v_full0 + 8 * s, 1);
       mbar_init(kv_empty0 + 8 * s, 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 4);
+    mbar_init(s_full0, 1);
+    mbar_init(s_full0 + 8, 1);
     mbar_init(p_full, 4);
     mbar_init(o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -129,7 +138,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
   gi::pdl_prologue();      // set-up overlapped the previous kernel's end; its results are visible from here on
 
   // Two threads issue the products, each with its own loads, so that neither chain waits behind the other's
@@ -166,18 +175,19 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
-        // the keys are here, and the rows of the previous S have been read
+        // the keys are here, and this score buffer is free: the output product of tile j - 2, which read its
+        // probabilities from it, is done (the barrier that frees that tile's values says so)
         ok = mbar_wait(k_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 2, &g_attn_status);
-        if (ok && j >= 1) ok = mbar_wait(s_free, (uint32_t)((j - 1) & 1), 2, &g_attn_status);
+        if (ok && j >= 2) ok = mbar_wait(kv_empty0 + 8 * s, (uint32_t)(((j - 2) >> 1) & 1), 2, &g_attn_status);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) tc_mma(tmem_s, dq[ks], s ? dk[1][ks] : dk[0][ks], IDESC_S, ks > 0 ? 1u : 0u);
-        tc_commit(s_full);
+        for (int ks = 0; ks < HD / 16; ++ks) tc_mma(tmem_s + (uint32_t)(s * 64), dq[ks], s ? dk[1][ks] : dk[0][ks], IDESC_S, ks > 0 ? 1u : 0u);
+        tc_commit(s_full0 + 8 * s);
         // keys two tiles ahead go into this tile's stage as soon as its scores are complete: a whole tile's softmax
         // before they are wanted
         if (j + 2 < n_tiles) {
-          ok = mbar_wait(s_full, (uint32_t)(j & 1), 2, &g_attn_status);
+          ok = mbar_wait(s_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 2, &g_attn_status);
           if (!ok) break;
           load_k(j + 2);
         }
@@ -194,10 +204,9 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       };
       load_v(0);
       if (n_tiles > 1) load_v(1);
-      uint64_t dp[BKV / 16], dv[2][BKV / 16];
+      uint64_t dv[2][BKV / 16];
 #pragma unroll
       for (int kk = 0; kk < BKV / 16; ++kk) {
-        dp[kk] = smem_desc(smem_u32(p_s) + kk * 32);
         dv[0][kk] = smem_desc_mn(smem_u32(v_s) + kk * 2048, KV_HALF);
         dv[1][kk] = smem_desc_mn(smem_u32(v_s) + KV_BYTES + kk * 2048, KV_HALF);
       }
@@ -209,7 +218,8 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) tc_mma(tmem_o, dp[kk], s ? dv[1][kk] : dv[0][kk], IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < BKV / 16; ++kk)      // 16 keys of the probabilities = 8 columns of the tile's score buffer
+          tc_mma_a_tmem(tmem_o, tmem_s + (uint32_t)(s * 64 + kk * 8), s ? dv[1][kk] : dv[0][kk], IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(kv_empty0 + 8 * s);
         tc_commit(o_full);
         // values two tiles ahead go into this tile's stage once this product no longer reads it
@@ -230,16 +240,14 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j & 1;
       const int kt = kt_begin + j * BKV;
-      ok = mbar_wait(s_full, (uint32_t)(j & 1), 3, &g_attn_status);
+      ok = mbar_wait(s_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 3, &g_attn_status);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t my_s = tmem_s + lane_base + (uint32_t)(s * 64);
       uint32_t sr[2][32];
-      tc_ld32(tmem_s + lane_base, sr[0]);
-      tc_ld32(tmem_s + lane_base + 32, sr[1]);
+      tc_ld32(my_s, sr[0]);
+      tc_ld32(my_s + 32, sr[1]);
       tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free);
       // scores -> probabilities.  A tile every row of the block sees in full needs no mask: one maximum, then one
       // fused multiply-add, one exponential and one addition per score.  Tiles on the diagonal (or at a window's
       // edge) take the masked path.
@@ -287,28 +295,27 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           pk[q * 16 + c / 2] = *reinterpret_cast<uint32_t*>(&pv);
         }
       l_run = l_run * alpha + psum;
-      if (j > 0) {
-        // the previous second product is done: O may be rescaled and the probability tile rewritten
+      // The accumulator is rescaled only when some row of the warp moved its reference point (rare): then the
+      // previous output product must be done first.  Nothing else here waits for it: the probabilities go into
+      // this tile's own score buffer, which no product reads before they are announced.
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
         ok = mbar_wait(o_full, (uint32_t)((j - 1) & 1), 3, &g_attn_status);
         if (!ok) break;
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
-            uint32_t orow[32];
-            tc_ld32(tmem_o + lane_base + c * 32, orow);
-            tc_wait_ld();
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t orow[32];
+          tc_ld32(tmem_o + lane_base + c * 32, orow);
+          tc_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * alpha);
-            tc_st32(tmem_o + lane_base + c * 32, orow);
-          }
-          tc_wait_st();
+          for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * alpha);
+          tc_st32(tmem_o + lane_base + c * 32, orow);
         }
+        tc_wait_st();
       }
-      // the row of probabilities: 64 bfloat16 = eight 16-byte chunks, swizzled like a TMA tile
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(p_s + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      // the row of probabilities: 64 bfloat16, two to a column, over the first 32 columns of the scores just read
+      tc_st32(my_s, pk);
+      tc_wait_st();
       // keys of this tile that no row of the block may see (past the block's last position, or before every window)
       // get zero values: their probabilities are zero, but zero times a stale non-number would still be a non-number
       const int lo = max(0, t_first - kt), hi = min(BKV, p_last + 1 - kt);
@@ -364,7 +371,7 @@ template <int HD>
 int launch_t5(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, __nv_bfloat16* out,
               long ldo, const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots, const int* seq_pos0,
               int n_heads, int n_kv, float scale, int window, int q_tiles) {
-  constexpr size_t smem = (HD / 64) * (Q_HALF + 4 * KV_HALF) + P_BYTES + 12 * 8 + 16;
+  constexpr size_t smem = (HD / 64) * (Q_HALF + 4 * KV_HALF) + 12 * 8 + 16;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_t5_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
