@@ -400,6 +400,8 @@ extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, 
   int rc = gi::tensor_map_2d_ex(&mq, q, q_rows, (long)(n_heads + 2 * n_kv) * hd, ldq, GI_BF16, 64, BQ);
   if (rc != GI_OK) return rc;
   const long cache_rows = cache_pages * n_kv * PAGE_TOKENS;
+  if (cache_rows > 0x7fffffffL || q_rows > 0x7fffffffL)       // TMA coordinates are 32-bit
+    return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tcgen05): more than 2^31 - 1 rows of queries or of cached keys");
   rc = gi::tensor_map_2d_ex(&mk, kcache, cache_rows, hd, hd, GI_BF16, 64, BKV);
   if (rc != GI_OK) return rc;
   rc = gi::tensor_map_2d_ex(&mv, vcache, cache_rows, hd, hd, GI_BF16, 64, BKV);
