@@ -8,7 +8,7 @@
 
 namespace {
 thread_local char g_last_error[512] = "";
-int g_pdl = 0;
+int g_pdl = 1;
 }
 
 namespace gi {

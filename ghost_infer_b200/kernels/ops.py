@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
+import os
 import weakref
 from ctypes import c_float, c_int, c_long, c_void_p
 from typing import Dict, Optional
@@ -69,6 +70,8 @@ def _bind():
         fn.argtypes = argtypes
         fn.restype = c_int
     lib.gi_gemm_stream_scratch_floats.restype = c_long
+    if os.environ.get("GHOST_INFER_PDL") in ("0", "1"):         # the process-wide default of set_pdl
+        lib.gi_set_pdl(int(os.environ["GHOST_INFER_PDL"]))
     _bound = lib
     return lib
 
@@ -338,7 +341,8 @@ USE_STREAM = True    # decode products through the persistent stream-K kernel (e
 
 def set_pdl(on: bool) -> None:
     """Programmatic dependent launch: consecutive kernels of a stream that support it overlap one's start with
-    the other's end (and the decode product prefetches weights meanwhile).  Process-wide."""
+    the other's end (and the decode product prefetches weights meanwhile).  Process-wide; on unless switched off
+    here or by GHOST_INFER_PDL=0 in the environment."""
     lib = _bind()
     lib.gi_set_pdl(int(bool(on)))
 

@@ -682,6 +682,7 @@ def test_prefill_kernels_chain_under_dependent_launch():
     cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
     zero = torch.zeros(1, dtype=torch.int32, device=DEV)
     outs = []
+    was = ops.get_pdl()
     for pdl in (False, True, True):
         ops.set_pdl(pdl)
         try:
@@ -698,7 +699,7 @@ def test_prefill_kernels_chain_under_dependent_launch():
             torch.cuda.synchronize()
             outs.append(x.clone())
         finally:
-            ops.set_pdl(False)
+            ops.set_pdl(was)
     assert ops.gemm_tc_status() == 0 and ops.attn_prefill_t5_status() == 0
     assert torch.isfinite(outs[0]).all() and float((outs[0] - x0).abs().max()) > 0
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])

@@ -196,6 +196,7 @@ def test_decoding_with_dependent_launch(model_dirs, tiny_configs, name):
     seqs = [tokens_for(tiny_configs[name], n, 40 + i) for i, n in enumerate((150, 90, 131))]
     refs = [plain_logits(d, s) for s in seqs]
     outs = {}
+    was = ops.get_pdl()
     for pdl in (False, True):
         ops.set_pdl(pdl)
         try:
@@ -210,7 +211,7 @@ def test_decoding_with_dependent_launch(model_dirs, tiny_configs, name):
                     got[i].append(lg[i])
             outs[pdl] = [np.stack(g) for g in got]
         finally:
-            ops.set_pdl(False)
+            ops.set_pdl(was)
     for i in range(len(seqs)):
         check_logits(outs[True][i], refs[i][60:90], "bfloat16", f"{name} dependent launch request {i}")
         assert np.array_equal(outs[True][i], outs[False][i])
