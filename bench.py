@@ -215,12 +215,12 @@ def main():
     V = cfg["vocab_size"]
     clocks = ClockSampler()
 
-    def decode_run(batch, steps, warmup):
-        """`steps` timed decode steps of `batch` sequences that each hold PROMPT tokens; device time."""
+    def decode_run(batch, steps, warmup, held=PROMPT):
+        """`steps` timed decode steps of `batch` sequences that each hold `held` tokens; device time."""
         slots = [cache.open_slot() for _ in range(batch)]
-        cache.reserve([(s, PROMPT) for s in slots])
+        cache.reserve([(s, held) for s in slots])
         for s in slots:
-            cache.commit(s, PROMPT)
+            cache.commit(s, held)
         toks = rng.integers(0, V, size=batch).tolist()
         runner = eng.decoder(slots)
         picked = torch.zeros(batch, dtype=torch.int32, device=dev)
@@ -275,6 +275,10 @@ def main():
         for b in (1, 64):
             ms, _, _ = decode_run(b, max(8, K // 2), W)
             points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+        # the same batch of 8 with the cache's whole length behind it: the last timed step reads 8,192 positions
+        n = max(8, K // 2)
+        ms, _, _ = decode_run(8, n, W, held=CONTEXT - (W + n + 1))
+        points[f"decode_b8_ctx{CONTEXT}"] = round(8 * 1000.0 / ms, 1)
 
     # prefill: one prompt of 2,048 tokens, logits for its last place
     prompt = rng.integers(0, V, size=PROMPT).tolist()
