@@ -66,7 +66,8 @@ def run_workload(key, args):
     llm = gi.LLM(w["config"], dtype="bfloat16", device="cuda:0", max_tokens=max_tokens, max_slots=w["batch"],
                  max_seq_len=hi + w["new"] + 64, seed=0)
     new = w["new"] if args.steps == 64 else max(2, args.steps)
-    llm.generate(prompts[:2], max_new=2, temperature=0.0, stop_token_ids=(), batch_size=w["batch"])      # warm-up
+    # warm-up with the whole batch: the first step of a shape obtains its device memory, which must not be timed
+    llm.generate(prompts, max_new=2, temperature=0.0, stop_token_ids=(), batch_size=w["batch"], max_step_tokens=w["step_tokens"])
     torch.cuda.synchronize()
     llm.generate(prompts, max_new=new, temperature=0.0, stop_token_ids=(), batch_size=w["batch"], max_step_tokens=w["step_tokens"])
     st = llm.last_stats
