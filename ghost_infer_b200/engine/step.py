@@ -106,7 +106,7 @@ class Engine:
         self.bytes_h2d = 0
         self._decode_graphs = {}
         mixers = [layer.block.mixer for layer in getattr(model, "layers", [])]
-        self._attn_shapes = sorted({(m.n_kv, m.n_heads // m.n_kv) for m in mixers if hasattr(m, "n_kv")})
+        self._attn_shapes = sorted({(m.n_kv, m.n_heads // m.n_kv, getattr(m, "head_dim", 128)) for m in mixers if hasattr(m, "n_kv")})
 
     # ---- host-side checks, before anything is launched (src/model.rs:974-982) -------------------
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -202,8 +202,8 @@ class Engine:
             return 1
         fast = self.model.rt.dtype == torch.bfloat16
         from ..kernels import ops
-        per_sm = (2 if (not fast or ops.TUNE["attn_tile_keys"] == 16) else 1) * ops.TUNE["attn_waves"]
-        return max(ctx.decode_splits(kv, group, 16 if fast else 8, per_sm) for kv, group in self._attn_shapes)
+        return max(ctx.decode_splits(kv, group, 16 if fast else 8, ops.attn_decode_blocks_per_sm(hd, fast))
+                   for kv, group, hd in self._attn_shapes)
 
     def decoder(self, slots: Sequence[int], use_graph: bool = True):
         """A runner of one-token steps for these slots (see engine.decode.DecodeRunner)."""

@@ -94,9 +94,10 @@ def main() -> int:
         if args.kernel == "attn_decode":
             q = torch.randn(B, (H + 2 * KV) * hd, device=dev, dtype=bf)
             lens = torch.full((B,), S, dtype=torch.int32, device=dev)
-            # the engine's choice (StepContext.decode_splits): one wave of two blocks per SM, slices of at least 128 keys
+            # the engine's choice (StepContext.decode_splits): one wave of as many blocks as an SM holds, slices of at least 128 keys
             sms = torch.cuda.get_device_properties(0).multi_processor_count
-            splits = args.splits or max(1, min(32, (2 * sms) // max(1, B * KV * ((H // KV + 15) // 16)), S // 128))
+            per_sm = ops.attn_decode_blocks_per_sm(hd, True)
+            splits = args.splits or max(1, min(32, int(per_sm * sms) // max(1, B * KV * ((H // KV + 15) // 16)), S // 128))
             o = torch.empty(B, H * hd, device=dev, dtype=bf)
             po = torch.empty(B * H * splits * hd, device=dev)
             pml = torch.empty(B * H * splits * 2, device=dev)

@@ -748,6 +748,19 @@ def swiglu_interleaved(h: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Te
     return silu_mul(gu, interleaved=True)
 
 
+def attn_decode_blocks_per_sm(head_dim: int, fast: bool) -> float:
+    """How many blocks of the decode attention one SM holds (its shared memory decides: a block's rings of key and
+    value tiles are 96 KB at head size 128 and 64 KB at head size 64 with 16-key tiles), times TUNE["attn_waves"]:
+    the slice count fills that many places once."""
+    if not fast:
+        per_sm = 2
+    elif TUNE["attn_tile_keys"] == 16:
+        per_sm = 3 if head_dim == 64 else 2
+    else:
+        per_sm = 1
+    return per_sm * TUNE["attn_waves"]
+
+
 def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim: int, scale: float,
               window: Optional[int], out: torch.Tensor) -> torch.Tensor:
     """Attention of a step's tokens over the cache (which already holds the step's own keys and values).
@@ -756,9 +769,8 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
         raise KernelError("attention needs a cache to read from")
     if step.is_decode:
         fast = attn_decode_tc_ok(qkv, memory.k, head_dim)
-        # the tensor-core kernel packs 16 heads of a group into a block and keeps one block per SM
-        per_sm = (2 if (not fast or TUNE["attn_tile_keys"] == 16) else 1) * TUNE["attn_waves"]
-        n_splits = step.decode_splits(n_kv, n_heads // n_kv, 16 if fast else 8, per_sm)
+        # the tensor-core kernel packs 16 heads of a group into a block
+        n_splits = step.decode_splits(n_kv, n_heads // n_kv, 16 if fast else 8, attn_decode_blocks_per_sm(head_dim, fast))
         part_o = part_ml = None
         if n_splits > 1:
             part_o = torch.empty((step.n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
