@@ -344,20 +344,22 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           // rows 16b..16b+7 gate j, 16b+8..16b+15 up j: the partner sits 8 lanes further
           const bool is_gate = (row & 15) < 8;
           const int fo = (f >> 4) * 8 + (f & 7);
-          // eight tokens at a time: their exchanges and exponentials overlap (one token per turn, each turn ending in
-          // a test of M, ran them one after the other: 4.5 us for a tile of 64 tokens)
+          // several tokens at a time (eight of a 16-token tile, sixteen of a wider one): their exchanges and
+          // exponentials overlap (one token per turn, each turn ending in a test of M, ran them one after the
+          // other: 4.5 us for a tile of 64 tokens)
+          constexpr int GROUP = NT >= 32 ? 16 : 8;
 #pragma unroll
-          for (int m0 = 0; m0 < NT; m0 += 8) {
+          for (int m0 = 0; m0 < NT; m0 += GROUP) {
             if (m0 >= M) break;                     // the same for every lane
-            float h[8];
+            float h[GROUP];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < GROUP; ++j) {
               const float up = __shfl_down_sync(0xffffffffu, v[m0 + j], 8);
               h[j] = gi::silu_mul_bf16(v[m0 + j], up);
             }
             if (is_gate && f < N) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
+              for (int j = 0; j < GROUP; ++j)
                 if (m0 + j < M) ((__nv_bfloat16*)out_)[(size_t)(m0 + j) * ldo + fo] = __float2bfloat16_rn(h[j]);
             }
           }
