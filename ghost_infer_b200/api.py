@@ -20,16 +20,19 @@ from .sampling import DeviceSampler, SamplingParams
 
 class LLM:
     def __init__(self, model, dtype: str = "bfloat16", device: str = "cuda:0", max_tokens: int = 8 * 2048,
-                 max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, seed: int = 0):
+                 max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, seed: int = 0,
+                 beyond_trained_positions: bool = False):
         """`model`: a model folder (config.json, model.safetensors), or a config mapping, for which random
-        weights are made on the device from `seed`."""
+        weights are made on the device from `seed`.  `max_seq_len` above the model's own
+        `max_position_embeddings` is lowered to it unless `beyond_trained_positions` is set."""
         if isinstance(model, Model):
             self.model = model
         elif isinstance(model, Mapping):
             self.model = Model.random(model, seed=seed, dtype=dtype, device=device)
         else:
             self.model = Model.from_pretrained(str(model), dtype=dtype, device=device)
-        self.cache = self.model.new_cache(max_tokens=max_tokens, max_slots=max_slots, max_seq_len=max_seq_len)
+        self.cache = self.model.new_cache(max_tokens=max_tokens, max_slots=max_slots, max_seq_len=max_seq_len,
+                                          beyond_trained_positions=beyond_trained_positions)
         self.engine = Engine(self.model, self.cache)
         self.last_stats: Optional[GenerationStats] = None
 

@@ -7,7 +7,8 @@ each group has its own pages, page tables and storage.  This mirrors the referen
 its caches by attention layers only and its state buffers by the other layers
 (src/model.rs:240-253, src/model.rs:738-741).  Fixed-size per-sequence state (the reference's
 `conv_state`/`ssm_state`, zeroed on reset, src/model.rs:692-695, src/model.rs:772-777) lives in a
-`[slot, ...]` tensor per schedule entry that asks for one; the Llama decoder asks for none.
+`[slot, ...]` tensor per schedule entry that asks for one (with one more row at the end, where the padding
+rows of fixed-size launches land); the Llama decoder asks for none.
 
 Storage of a group: K and V, each `[entry, page, kv_head, PAGE_TOKENS, head_dim]`.  One page of
 one kv head is a contiguous block, which is what the decode kernel streams.
@@ -54,7 +55,7 @@ class LayerMemory:
     block_table: Optional[torch.Tensor]   # device int32 [max_slots, max_pages_per_seq] of the entry's group
     window: Optional[int]
     writes: bool                          # False when the entry reads another entry's memory
-    state: Optional[torch.Tensor]         # [max_slots, *shape] or None
+    state: Optional[torch.Tensor]         # [max_slots + 1, *shape] or None; the last row (slot -1) is for padding rows
 
 
 class _Group:
@@ -95,8 +96,10 @@ class SequenceCache:
         self.device = torch.device(device)
         self.dtype = dtype
         self.max_tokens = int(max_tokens)
-        self.max_seq_len = int(min(max_seq_len, pages_for(max_tokens) * PAGE_TOKENS))
         self.n_pages = pages_for(max_tokens)
+        # a sequence whose every position stays cached cannot be longer than the pool; one that only keeps windows can
+        keeps_all = any(creq is not None and creq.kind == "full" and memory_of is None for _, creq, _, memory_of in requests)
+        self.max_seq_len = int(min(max_seq_len, self.n_pages * PAGE_TOKENS)) if keeps_all else int(max_seq_len)
         self.max_pages_per_seq = pages_for(self.max_seq_len)
         self.slots = SlotAllocator(max_slots)
         self.max_slots = max_slots
@@ -119,7 +122,9 @@ class SequenceCache:
                 self._group_of_entry[entry] = (g, len(g.entries))
                 g.entries.append(entry)
             if sreq is not None:
-                self._state[entry] = torch.zeros((max_slots,) + tuple(sreq.shape), dtype=sreq.dtype, device=self.device)
+                # one row more than there are slots: padding rows of a fixed-size launch carry slot -1, which
+                # indexes this last row, as they write keys and values to the trash page
+                self._state[entry] = torch.zeros((max_slots + 1,) + tuple(sreq.shape), dtype=sreq.dtype, device=self.device)
         for g in self._groups:
             g.allocate()
 

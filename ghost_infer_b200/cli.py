@@ -1,10 +1,10 @@
 """Command line in the reference's manner (src/main.rs:36-92, :120-203, :205-248).
 
     ghost-infer inspect <model dir>
-    ghost-infer top     <model dir> <token ids>             next-token probabilities after the ids
+    ghost-infer top     <model dir> <token ids> [--dtype <t>]   next-token probabilities after the ids
     ghost-infer bench   <model dir> [-n <gen tokens>] [--prompt-len <n>] [--batch <n>]
     ghost-infer run     <model dir> -p <token ids> [options]
-    ghost-infer kvcheck <model dir> <ids file> <out file> <tail>
+    ghost-infer kvcheck <model dir> <ids file> <out file> <tail> [--dtype <t>]
     ghost-infer random  <config.json> <out dir> [--seed <n>] [--dtype <t>]
 
 Options keep the reference's names, meanings and defaults where it has them: -p/--prompt, -n/--max [256],
@@ -26,10 +26,10 @@ USAGE = """ghost-infer_b200 - run Llama 3 models from a safetensors folder on an
 
 USAGE:
     ghost-infer inspect <model dir>
-    ghost-infer top     <model dir> <token ids>   (next-token probabilities after the ids)
+    ghost-infer top     <model dir> <token ids> [--dtype <t>]   (next-token probabilities after the ids)
     ghost-infer bench   <model dir> [-n <gen tokens>] [--prompt-len <n>] [--batch <n>]
     ghost-infer run     <model dir> -p <token ids> [options]
-    ghost-infer kvcheck <model dir> <ids file> <out file> <tail>
+    ghost-infer kvcheck <model dir> <ids file> <out file> <tail> [--dtype <t>]
     ghost-infer random  <config.json> <out dir> [--seed <n>] [--dtype <t>]
 
 OPTIONS:
@@ -124,10 +124,17 @@ def parse_ids(text: str) -> List[List[int]]:
     return prompts
 
 
-def _llm(o: Opts, max_tokens: int):
+def _llm(o: Opts, max_tokens: int, ctx: Optional[int] = None):
+    """`ctx`: the most tokens one sequence may hold; never more than the model's own positions, as the
+    reference clamps its context (`ctx.min(max_ctx)`, src/model.rs:732)."""
     from .api import LLM
+    from .engine.model import Model
     t = time.time()
-    llm = LLM(o.model, dtype=o.dtype, max_tokens=max_tokens)
+    model = Model.from_pretrained(o.model, dtype=o.dtype)
+    own = model.spec.max_positions
+    if ctx is not None and ctx > own:
+        print(f"[--ctx {ctx} is beyond the model's {own} positions: using {own}]", file=sys.stderr)
+    llm = LLM(model, dtype=o.dtype, max_tokens=max_tokens, max_seq_len=own if ctx is None else min(ctx, own))
     cfg = llm.model.config
     print(f"[loaded {getattr(cfg, 'architecture', 'model')} ({o.dtype}) in {time.time() - t:.2f}s]", file=sys.stderr)
     return llm
@@ -146,7 +153,7 @@ def cmd_run(o: Opts) -> None:
     prompts = parse_ids(o.prompt)
     ctx = o.ctx or 2048
     batch = o.batch or 8
-    llm = _llm(o, max_tokens=min(batch, len(prompts)) * ctx)
+    llm = _llm(o, max_tokens=min(batch, len(prompts)) * ctx, ctx=ctx)
     results = llm.generate(prompts, max_new=o.max_new, temperature=o.temp, top_k=o.top_k, top_p=o.top_p,
                            seed=o.seed, batch_size=batch)
     for r in results:
@@ -275,18 +282,35 @@ def cmd_random(args: List[str]) -> None:
     print(f"wrote {args[1]} (seed {seed}, {dtype})")
 
 
+def _take_dtype(rest: List[str]):
+    """Splits a trailing or embedded `--dtype <t>` off the positional arguments of `top` and `kvcheck`."""
+    dtype, pos = "bfloat16", []
+    it = iter(rest)
+    for a in it:
+        if a == "--dtype":
+            try:
+                dtype = next(it)
+            except StopIteration:
+                raise UsageError("--dtype needs a value") from None
+        else:
+            pos.append(a)
+    return pos, dtype
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     args = list(sys.argv[1:] if argv is None else argv)
     cmd, rest = (args[0] if args else None), args[1:]
     try:
+        if cmd in ("top", "kvcheck"):
+            rest, dtype = _take_dtype(rest)
         if cmd == "inspect" and len(rest) == 1:
             cmd_inspect(rest[0])
-        elif cmd == "top" and len(rest) in (2, 3):
-            cmd_top(rest[0], rest[1])
+        elif cmd == "top" and len(rest) == 2:
+            cmd_top(rest[0], rest[1], dtype)
         elif cmd == "bench" and rest:
             cmd_bench(parse_opts(rest))
         elif cmd == "kvcheck" and len(rest) == 4:
-            cmd_kvcheck(rest[0], rest[1], rest[2], int(rest[3]))
+            cmd_kvcheck(rest[0], rest[1], rest[2], int(rest[3]), dtype)
         elif cmd == "run" and rest:
             cmd_run(parse_opts(rest))
         elif cmd == "random":

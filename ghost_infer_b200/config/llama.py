@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import Any, Mapping, Optional, Tuple
+from typing import Any, ClassVar, Mapping, Optional, Tuple
 
 from .errors import ConfigError
 
@@ -25,7 +25,7 @@ class RopeScaling:
 
     The reference only consumes the result, a table `rope_freqs` of "what the
     plain frequency is divided by" (src/model.rs:30-31, src/model.rs:768); the
-    derivation from these four numbers is done by `parts.rope.llama3_inv_freq`.
+    derivation from these four numbers is done by `parts.rope.rotary_inv_freq`.
     """
 
     rope_type: str
@@ -80,6 +80,7 @@ class LlamaConfig:
     bos_token_id: Optional[int] = None
     torch_dtype: str = "bfloat16"
     extra: Mapping[str, Any] = field(default_factory=dict, compare=False, hash=False)
+    model_type: ClassVar[str] = "llama"      # what config.json calls this family; written into folders this library makes
 
     # ---- derived sizes (the reference's kv_dim / q_dim helpers, src/model.rs:255-281)
     @property
@@ -179,7 +180,7 @@ class LlamaConfig:
             "architectures", "hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads",
             "head_dim", "intermediate_size", "vocab_size", "max_position_embeddings", "rope_theta", "rope_scaling",
             "rms_norm_eps", "tie_word_embeddings", "eos_token_id", "bos_token_id", "torch_dtype", "dtype",
-            "attention_bias", "mlp_bias", "hidden_act",
+            "attention_bias", "mlp_bias", "hidden_act", "model_type",
         }
         cfg = cls(
             architecture=arch,
@@ -206,6 +207,7 @@ class LlamaConfig:
     def to_dict(self) -> dict:
         out = {
             "architectures": [self.architecture],
+            "model_type": self.model_type,
             "hidden_size": self.hidden_size,
             "num_hidden_layers": self.num_hidden_layers,
             "num_attention_heads": self.num_attention_heads,

@@ -172,7 +172,9 @@ int gi_attn_prefill_generic(void* out, long ldo, const void* q, long ldq, int dt
 int gi_attn_decode_generic(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, int dtype,
                            const void* kcache, const void* vcache, const int* block_table, int max_pages,
                            const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
-                           float scale, int window, int n_splits, void* stream);
+                           float scale, int window, int n_splits, int own_tiles, void* stream);
+// own_tiles > 0: slice s of a sequence holds tiles [s * own_tiles, (s + 1) * own_tiles) of 32 keys of its own span,
+// whatever n_splits is (which must cover the longest span); 0: each span is cut into n_splits equal slices.
 
 // bfloat16, head size 64 or 128: the same operation as gi_attn_prefill_generic, on tensor cores
 int gi_attn_prefill_tc(void* out, long ldo, const void* q, long ldq, const void* kcache, const void* vcache,

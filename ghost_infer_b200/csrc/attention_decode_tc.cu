@@ -24,7 +24,7 @@ constexpr int WARPS = 4;
 template <int HD, int KT, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restrict__ part_o, float* __restrict__ part_ml,
-                      const __nv_bfloat16* __restrict__ q, long ldq, const __nv_bfloat16* __restrict__ kcache,
+                      const __nv_bfloat16* q /* written by the kernel before: see gi::pdl_wait */, long ldq, const __nv_bfloat16* __restrict__ kcache,
                       const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_pages,
                       const int* __restrict__ seq_slots, const int* __restrict__ seq_lens, int n_heads, int n_kv,
                       float scale, int window, int n_splits) {
@@ -45,8 +45,8 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
   const int b = blockIdx.z, kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks, sp = blockIdx.x;
   const int g0 = chunk * 16, gcount = min(16, group - g0);
   const int h0 = kvh * group + g0;
-  const int slot = seq_slots[b];
-  const int len = seq_lens[b];
+  const int slot = gi::ld_step(seq_slots + b);
+  const int len = gi::ld_step(seq_lens + b);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
 
@@ -63,7 +63,7 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
   auto issue = [&](int tile, int stage) {
     // 32 keys x CH chunks for K and for V, 16 bytes per lane and instruction
     const int t0 = t_base + tile * KT;
-    const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + t0 / PAGE_TOKENS] : 0;
+    const int page = slot >= 0 ? gi::ld_step(block_table + (size_t)slot * max_pages + t0 / PAGE_TOKENS) : 0;
     const size_t base = (((size_t)page * n_kv + kvh) * PAGE_TOKENS + (t0 % PAGE_TOKENS)) * HD;
     unsigned char* ks = my_ring + (size_t)stage * STAGE_BYTES;
     unsigned char* vs = ks + TILE_BYTES;
@@ -270,11 +270,12 @@ int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, f
   constexpr size_t merge = (size_t)(WARPS * 16 * (HD + 8) + 2 * WARPS * 16) * sizeof(float);
   constexpr size_t smem = 16 * HD * 2 + (ring > merge ? ring : merge);
   auto kern = attn_decode_tc_kernel<HD, KT, STAGES>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[gi::MAX_DEVICES_SEEN] = {false};
+  int dev;
+  if (gi::unconfigured_here(configured, &dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention decode: %s", cudaGetErrorString(e));
-    configured = true;
+    if (dev >= 0) configured[dev] = true;
   }
   return gi::check(gi::launch(kern, grid, dim3(WARPS * 32), smem, s, out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV,
                               scale, window, n_splits), "attention decode (tensor cores)");

@@ -137,7 +137,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
                    const T* __restrict__ q, long ldq, const T* __restrict__ kcache, const T* __restrict__ vcache,
                    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slots,
                    const int* __restrict__ seq_lens, int n_heads, int n_kv, int hd, float scale, int window,
-                   int n_splits) {
+                   int n_splits, int own_tiles) {
   extern __shared__ float smem[];
   float* Qs = smem;                       // [GC][hd]
   float* Mo = Qs + GC * hd;               // [4][GC][hd] warp outputs
@@ -163,7 +163,9 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
   if (window > 0) t_first = max(0, len - window);
   const int t_base = (t_first / KT) * KT;
   const int tiles = len > t_base ? (len - t_base + KT - 1) / KT : 0;
-  const int per = (tiles + n_splits - 1) / n_splits;
+  // own_tiles > 0: a slice is that many tiles of the sequence's own span, so its sums do not depend on what else
+  // the launch holds (slices past the span stay empty); else the span is cut into n_splits equal slices
+  const int per = own_tiles > 0 ? own_tiles : (tiles + n_splits - 1) / n_splits;
   const int tile_lo = sp * per, tile_hi = min(tiles, tile_lo + per);
 
   float m[GC], l[GC], o[GC][DC];
@@ -337,7 +339,7 @@ int launch_prefill(int dpt, dim3 grid, size_t smem, cudaStream_t s, T* out, long
 template <typename T, int GC>
 int launch_decode_dc(int dc, dim3 grid, size_t smem, cudaStream_t s, T* out, long ldo, float* po, float* pml,
                      const T* q, long ldq, const T* kc, const T* vc, const int* bt, int max_pages, const int* slots,
-                     const int* lens, int H, int KV, int hd, float scale, int window, int n_splits) {
+                     const int* lens, int H, int KV, int hd, float scale, int window, int n_splits, int own_tiles) {
 #define GI_DECODE_CASE(D)                                                                                        \
   case D: {                                                                                                      \
     auto kern = attn_decode_kernel<T, GC, D>;                                                                    \
@@ -345,7 +347,7 @@ int launch_decode_dc(int dc, dim3 grid, size_t smem, cudaStream_t s, T* out, lon
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
       if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention decode: %s", cudaGetErrorString(e));         \
     }                                                                                                            \
-    kern<<<grid, 128, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, hd, scale, window, n_splits); \
+    kern<<<grid, 128, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, hd, scale, window, n_splits, own_tiles); \
     break;                                                                                                       \
   }
   switch (dc) {
@@ -401,8 +403,9 @@ extern "C" int gi_attn_decode_generic(void* out, long ldo, float* part_o, float*
                                       int dtype, const void* kcache, const void* vcache, const int* block_table,
                                       int max_pages, const int* seq_slots, const int* seq_lens, int n_seqs,
                                       int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
-                                      void* stream) {
+                                      int own_tiles, void* stream) {
   if (n_seqs <= 0) return GI_OK;
+  if (own_tiles < 0) return gi::fail(GI_ERR_ARG, "attention: tiles per slice cannot be negative");
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
     return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
   if (hd <= 0 || hd > 256) return gi::fail(GI_ERR_UNSUPPORTED, "attention: head size %d is outside 1..256", hd);
@@ -422,7 +425,7 @@ extern "C" int gi_attn_decode_generic(void* out, long ldo, float* part_o, float*
     GI_DISPATCH_DTYPE(dtype, T,                                                                                    \
         rc = (launch_decode_dc<T, G>(dc, grid, smem, s, (T*)out, ldo, part_o, part_ml, (const T*)q, ldq, (const T*)kcache, \
                                      (const T*)vcache, block_table, max_pages, seq_slots, seq_lens, n_heads, n_kv, hd, \
-                                     scale, window, n_splits)));                                                   \
+                                     scale, window, n_splits, own_tiles)));                                        \
     break;
   switch (gc) {
     GI_GC_CASE(1)

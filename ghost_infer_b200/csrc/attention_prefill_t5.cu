@@ -372,11 +372,12 @@ int launch_t5(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUten
               long ldo, const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots, const int* seq_pos0,
               int n_heads, int n_kv, float scale, int window, int q_tiles) {
   constexpr size_t smem = (HD / 64) * (Q_HALF + 4 * KV_HALF) + 12 * 8 + 16;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[gi::MAX_DEVICES_SEEN] = {false};
+  int dev;
+  if (gi::unconfigured_here(configured, &dev)) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_t5_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention prefill (tcgen05): %s", cudaGetErrorString(e));
-    configured = true;
+    if (dev >= 0) configured[dev] = true;
   }
   return gi::check(gi::launch(attn_prefill_t5_kernel<HD>, grid, dim3(THREADS), smem, stream, mq, mk, mv, out, ldo, block_table, max_pages,
                               cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles),

@@ -201,11 +201,12 @@ int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, const __nv_b
            float scale, int window, int q_tiles) {
   constexpr size_t smem = (size_t)BQ * HD * 2 + 2 * 2 * (size_t)BKV * HD * 2;
   auto kern = attn_prefill_tc_kernel<HD>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[gi::MAX_DEVICES_SEEN] = {false};
+  int dev;
+  if (gi::unconfigured_here(configured, &dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention prefill: %s", cudaGetErrorString(e));
-    configured = true;
+    if (dev >= 0) configured[dev] = true;
   }
   kern<<<grid, WARPS * 32, smem, s>>>(out, ldo, q, ldq, kc, vc, bt, max_pages, cu, slots, pos0, H, KV, scale, window, q_tiles);
   return gi::check_launch("attention prefill (tensor cores)");

@@ -34,7 +34,18 @@ __device__ __forceinline__ void pdl_prologue() {
 // The two halves on their own, for kernels that read data no kernel of the step writes (weights, tables the
 // host uploaded before the step's first kernel) between them: such loads overlap the predecessor's end.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// In a kernel that runs code before pdl_wait(), a pointer to data that an earlier kernel of the same stream writes
+// must not be declared `const __restrict__`: that promises the compiler that nothing writes the data while the
+// kernel runs, and it may then issue the loads above the wait (it did so for the decode attention's queries at head
+// size 64, which read the previous step's rows in a replayed graph).  Without the promise the wait's memory clobber
+// keeps the loads behind it.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// A read of what the host uploaded for this step (positions, slots, lengths, page tables, row selections) made
+// BEFORE the dependency wait.  A kernel that starts while its predecessor still runs finds the SM's L1 as earlier
+// kernels left it: a line that held the previous step's value of such an array may still be there, and a plain (or
+// read-only-path) load would return it.  These loads go to the L2 cache, which the upload went through.
+__device__ __forceinline__ int ld_step(const int* p) { return __ldcg(p); }
 
 __device__ __forceinline__ float ldf(const float* p) { return *p; }
 __device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
@@ -116,6 +127,14 @@ inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+// A kernel's attributes (its dynamic shared memory limit) belong to the kernel on one device.  `seen` is a table of
+// one flag per device that a launcher keeps per kernel; true when the attribute is still to be set on the current device.
+constexpr int MAX_DEVICES_SEEN = 64;
+inline bool unconfigured_here(bool (&seen)[MAX_DEVICES_SEEN], int* dev) {
+  *dev = -1;
+  if (cudaGetDevice(dev) != cudaSuccess || *dev < 0 || *dev >= MAX_DEVICES_SEEN) { *dev = -1; return true; }
+  return !seen[*dev];
 }
 inline int check(cudaError_t e, const char* what) {
   if (e != cudaSuccess) return fail(GI_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));

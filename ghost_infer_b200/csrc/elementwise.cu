@@ -53,7 +53,7 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, cons
   __shared__ float scratch[33];
   gi::pdl_launch_dependents();
   const int r = blockIdx.x;
-  const int m = rows ? rows[r] : r;         // the selection was uploaded before the step's first kernel
+  const int m = rows ? gi::ld_step(rows + r) : r;   // the selection was uploaded before the step's first kernel
   float* xr = x + (size_t)m * d;
   TO* o = out + (size_t)r * d;
   if (VEC > 0) {
@@ -171,7 +171,9 @@ int rmsnorm_impl(void* out, int out_dtype, float* x, const void* w, int w_dtype,
   // few rows (a decode step): many threads per row; many rows (a prompt): 256 threads with more values each, so that
   // an SM holds eight rows' loads in flight instead of four
   // (a settling norm has several loads per value: more threads, fewer values each)
-  const bool many = n_rows >= 512;
+  // (32-bit output is the path whose sums must not depend on the step's other rows: there the block's size, and
+  // with it the order of the row's sum, follows from the width alone)
+  const bool many = n_rows >= 512 && out_dtype != GI_F32;
   const int threads = settle ? (d >= 4096 ? 1024 : (d >= 2048 ? 512 : 256)) : ((d >= 2048 && !(many && d <= 4096)) ? 512 : 256);
   // the register path: rows that are a multiple of 4 wide, start on 16-byte boundaries, and fit 4 float4 per thread
   const bool vec = d % 4 == 0 && ((uintptr_t)x & 15) == 0 && d / 4 <= 4 * threads;

@@ -408,11 +408,12 @@ int launch(void* out, const CUtensorMap& mw, const CUtensorMap& ma, float* scrat
            int use_pdl, cudaStream_t s, const CUtensorMap& mn, Next next) {
   constexpr size_t smem = (size_t)STAGES * (TILE_ROWS * BK * 2 + NT * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
   auto kern = gemm_stream_kernel<NT, STAGES, MODE>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[gi::MAX_DEVICES_SEEN] = {false};
+  int dev;
+  if (gi::unconfigured_here(configured, &dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "streamed product: %s", cudaGetErrorString(e));
-    configured = true;
+    if (dev >= 0) configured[dev] = true;
   }
   const long units = (long)((N + TILE_ROWS - 1) / TILE_ROWS) * ((K + BK - 1) / BK);
   const int grid = (int)(units < sm_count() ? units : sm_count());

@@ -283,11 +283,12 @@ template <int BN, int STAGES, int MODE>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, int M, int N, int K, cudaStream_t s) {
   constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 2 * BM * 128 + (2 * STAGES + 4) * 8 + 16 + 1024;
   auto kern = gemm_tc_kernel<BN, STAGES, MODE>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[gi::MAX_DEVICES_SEEN] = {false};
+  int dev;
+  if (gi::unconfigured_here(configured, &dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "tensor-core product: %s", cudaGetErrorString(e));
-    configured = true;
+    if (dev >= 0) configured[dev] = true;
   }
   const long tiles = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());

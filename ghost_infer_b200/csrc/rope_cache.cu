@@ -24,6 +24,13 @@ __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restr
   table[idx] = make_float2(c, s);
 }
 
+// One pair's rotation with its roundings spelled out, so that both kernels below (and any other) give the same bits:
+// (a cos - b sin, a sin + b cos), each as one product rounded, then a fused multiply-add.
+__device__ __forceinline__ void rotate_pair(float a, float b, float2 cs, float* ra, float* rb) {
+  *ra = __fmaf_rn(a, cs.x, -__fmul_rn(b, cs.y));
+  *rb = __fmaf_rn(a, cs.y, __fmul_rn(b, cs.x));
+}
+
 // The value of column f of token t's packed row: what the product stored, or, for a tile of 128 columns that was cut
 // between blocks of a deferred product (`sp`, looked up before the dependency wait), the sum of the partial sums in
 // the order of the K ranges, rounded to T.
@@ -46,7 +53,8 @@ __device__ __forceinline__ gi_settle_span span_or_none(const gi_settle_t& st, in
 // One block per (token, head of the packed row): heads 0..H-1 are queries (rotated in place), H..H+KV-1 keys
 // (rotated into the cache), H+KV.. values (copied into the cache).  A thread handles one pair or one value pair.
 template <typename T>
-__global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* __restrict__ table, const int* __restrict__ positions,
+__global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* table /* written by a kernel of this step: see gi::pdl_wait */,
+                                  const int* __restrict__ positions,
                                   const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int n_heads, int n_kv, int hd, int rot,
                                   int adjacent, int write_cache, gi_settle_t st) {
@@ -62,9 +70,9 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* __
   T* dst = src;                                 // queries are rotated in place
   if (head >= n_heads) {
     if (!write_cache) return;
-    const int pos = positions[t], slot = slots[t];
+    const int pos = gi::ld_step(positions + t), slot = gi::ld_step(slots + t);
     // a padding row (slot < 0) writes to the trash page, which no live sequence reads
-    const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + pos / PAGE_TOKENS] : 0;
+    const int page = slot >= 0 ? gi::ld_step(block_table + (size_t)slot * max_pages + pos / PAGE_TOKENS) : 0;
     const int off = pos % PAGE_TOKENS;
     const bool is_k = head < n_heads + n_kv;
     dst = (is_k ? kcache : vcache) + (((size_t)page * n_kv + (head - n_heads - (is_k ? 0 : n_kv))) * PAGE_TOKENS + off) * hd;
@@ -84,8 +92,10 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, long ld, const float2* __
       const gi_settle_span sa = (i == i0) ? sp0 : span_or_none(st, col0 + ia), sb = (i == i0) ? sp1 : span_or_none(st, col0 + ib);
       const float a = row_value(row, st, sa, t, col0 + ia), b = row_value(row, st, sb, t, col0 + ib);
       const float2 f = table[(size_t)t * half + i];
-      gi::stf(dst + ia, a * f.x - b * f.y);
-      gi::stf(dst + ib, a * f.y + b * f.x);
+      float ra, rb;
+      rotate_pair(a, b, f, &ra, &rb);
+      gi::stf(dst + ia, ra);
+      gi::stf(dst + ib, rb);
     }
     // past the rotated part: as it is (queries only when they are still partial sums: the attention reads the row)
     if (head >= n_heads || st.partials != nullptr)
@@ -129,8 +139,10 @@ __global__ void rope_cache_rows_kernel(T* __restrict__ qkv, long ld, const float
     for (int e = 0; e < V; ++e) {
       const float2 f = cs[i0 + e];
       const float x = gi::ldf(a + e), y = gi::ldf(b + e);
-      gi::stf(a + e, x * f.x - y * f.y);
-      gi::stf(b + e, x * f.y + y * f.x);
+      float rx, ry;
+      rotate_pair(x, y, f, &rx, &ry);
+      gi::stf(a + e, rx);
+      gi::stf(b + e, ry);
     }
     *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(a);
     *reinterpret_cast<uint4*>(dst + i0 + half) = *reinterpret_cast<const uint4*>(b);

@@ -5,8 +5,9 @@ afterwards; kernels read the position from device memory and attention uses a fi
 one graph fits every position (src/cuda.rs:8690-8711, :8494-8495).  The same is done here for a batch:
 tokens, positions, slots and lengths live in a device buffer that one small host-to-device copy refreshes
 per step; the graph holds embedding, the layers, the final norm and the head.  A graph is kept per
-(rows, attention slices); rows beyond the live sequences are padding that writes to the cache's trash
-page and changes no live row.  Sampling runs after the replay, so one graph serves every sampling setting.
+(rows, what each mixer plans for that many rows and that length bucket); rows beyond the live sequences are
+padding with slot -1: they write to the cache's trash page and to the trash row of per-sequence state, and
+change no live row.  Sampling runs after the replay, so one graph serves every sampling setting.
 """
 from __future__ import annotations
 
@@ -35,11 +36,11 @@ def _bucket_len(n: int) -> int:
 
 
 class _DecodeGraph:
-    """Device buffers of one (rows, slices) shape and, once captured, the graph over them."""
+    """Device buffers of one (rows, mixers' plans) shape and, once captured, the graph over them."""
 
-    def __init__(self, engine, rows: int, splits: int):
+    def __init__(self, engine, rows: int, plans: dict, replayed: bool):
         dev = engine.device
-        self.rows, self.splits = rows, splits
+        self.rows, self.plans = rows, plans
         # [tokens | positions | token_slots | seq_lens] then the fixed [cu_seqlens | logit_rows]
         self.meta = torch.zeros(4 * rows, dtype=torch.int32, device=dev)
         fixed = np.concatenate([np.arange(rows + 1, dtype=np.int32), np.arange(rows, dtype=np.int32)])
@@ -60,7 +61,9 @@ class _DecodeGraph:
         ctx.logit_rows = self.fixed[rows + 1:]
         ctx.empty_f32 = engine._empty_f32
         ctx.sm_count = engine._sm_count
-        ctx.fixed_splits = splits
+        ctx.fixed_plans = plans
+        if replayed:
+            ctx._host_q_lens = ctx._host_slots = ctx._host_pos0 = None    # Python is not run again on replay
         self.ctx = ctx
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
@@ -76,19 +79,19 @@ class DecodeRunner:
         self.n = len(self.slots)
         if self.n == 0:
             raise ValueError("a decode runner needs at least one sequence")
-        self.rows = _bucket_rows(self.n)
-        self.use_graph = use_graph and engine.device.type == "cuda"
+        # a model with a part that plans its work in Python per step cannot be replayed: it decodes launch by
+        # launch, with exactly the live rows and the host-side lists filled in
+        self.use_graph = use_graph and engine.device.type == "cuda" and not engine.plans_on_host
+        self.rows = _bucket_rows(self.n) if self.use_graph else self.n
         self._g: Optional[_DecodeGraph] = None
 
     def _graph_for(self, max_len: int) -> _DecodeGraph:
         eng = self.engine
-        probe = StepContext()
-        probe.n_seqs, probe.max_kv_len, probe.sm_count = self.rows, _bucket_len(max_len), eng._sm_count
-        splits = eng.decode_splits_for(probe)
-        key = (self.rows, splits)
+        plans = eng.decode_plans(self.rows, _bucket_len(max_len))
+        key = (self.rows, self.use_graph, tuple(repr(plans[id(m)]) for m in eng._mixers))
         g = eng._decode_graphs.get(key)
         if g is None:
-            g = _DecodeGraph(eng, self.rows, splits)
+            g = _DecodeGraph(eng, self.rows, plans, self.use_graph)
             eng._decode_graphs[key] = g
         return g
 
@@ -129,6 +132,8 @@ class DecodeRunner:
         g.host_event = ev
         self.engine.bytes_h2d = g.host.numel() * 4
         g.ctx.max_kv_len = max(lens) + 1
+        if not self.use_graph:
+            g.ctx._host_q_lens, g.ctx._host_slots, g.ctx._host_pos0 = [1] * n, list(self.slots), list(lens)
         if g.graph is None:
             g.ctx.shared.clear()                       # per-step tables are made anew (inside the graph once captured)
         if not self.use_graph:

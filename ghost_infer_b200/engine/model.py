@@ -101,8 +101,12 @@ class Model:
             out.append((i, mixer.cache_request(), mixer.state_request(), e.memory_of))
         return out
 
-    def new_cache(self, max_tokens: int, max_slots: Optional[int] = None, max_seq_len: Optional[int] = None) -> SequenceCache:
-        """A cache for at most `max_tokens` live tokens (each sequence's count rounded up to whole pages)."""
+    def new_cache(self, max_tokens: int, max_slots: Optional[int] = None, max_seq_len: Optional[int] = None,
+                  beyond_trained_positions: bool = False) -> SequenceCache:
+        """A cache for at most `max_tokens` live tokens (each sequence's count rounded up to whole pages).
+        A sequence holds at most `max_seq_len` tokens, and never more than the model's own `max_positions`:
+        a larger value is lowered to it with a warning, as the reference clamps its context to the model's
+        (`ctx.min(max_ctx)`, src/model.rs:732), unless `beyond_trained_positions` asks to run past them."""
         if self.rt is None:
             raise RuntimeError("the model has no weights yet: bind it first")
         from ..cache.pages import pages_for
@@ -110,6 +114,11 @@ class Model:
         if max_slots is None:
             max_slots = max(1, min(n_pages, 4096))
         if max_seq_len is None:
+            max_seq_len = self.spec.max_positions
+        elif max_seq_len > self.spec.max_positions and not beyond_trained_positions:
+            import warnings
+            warnings.warn(f"max_seq_len {max_seq_len} is beyond the model's {self.spec.max_positions} positions and is "
+                          f"lowered to them (beyond_trained_positions=True runs past them)", stacklevel=2)
             max_seq_len = self.spec.max_positions
         return SequenceCache(self.memory_requests(), max_tokens=max_tokens, max_slots=max_slots,
                              max_seq_len=max_seq_len, dtype=self.rt.dtype, device=self.rt.device)

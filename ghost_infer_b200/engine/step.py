@@ -11,7 +11,7 @@ batch `[total tokens]` with per-sequence offsets; nothing is padded, so padding 
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -37,30 +37,49 @@ class StepContext:
         self.is_decode = False
         self.tokens: torch.Tensor = None        # int32 [T]
         self.positions: torch.Tensor = None     # int32 [T] position of each token in its sequence
-        self.token_slots: torch.Tensor = None   # int32 [T] slot of each token's sequence
+        self.token_slots: torch.Tensor = None   # int32 [T] slot of each token's sequence (-1: a padding row)
         self.cu_seqlens: torch.Tensor = None    # int32 [B + 1] offsets of the sequences' tokens
-        self.seq_slots: torch.Tensor = None     # int32 [B]
+        self.seq_slots: torch.Tensor = None     # int32 [B] (-1: a padding row)
         self.seq_pos0: torch.Tensor = None      # int32 [B] cached length before the step
         self.seq_lens: torch.Tensor = None      # int32 [B] cached length after the step
         self.logit_rows: Optional[torch.Tensor] = None   # int32 [R] flat token indices
         self.empty_f32: torch.Tensor = None
-        self.fixed_splits: Optional[int] = None
         self.shared: dict = {}                  # what parts compute once per step and share (e.g. rotary angles)
         self.sm_count = 148
-        # the same facts on the host, for parts that plan their work there
-        self.host_q_lens: List[int] = []
-        self.host_slots: List[int] = []
-        self.host_pos0: List[int] = []
+        # A step whose launches are recorded once and replayed (a CUDA graph) keeps the plans it was recorded
+        # with: id(mixer) -> what the mixer's `decode_plan` returned for the recording's shape.
+        self.fixed_plans: Optional[Dict[int, Any]] = None
+        # the same facts on the host, for parts that plan their work there (see `Part.plans_on_host`)
+        self._host_q_lens: Optional[List[int]] = []
+        self._host_slots: Optional[List[int]] = []
+        self._host_pos0: Optional[List[int]] = []
 
-    def decode_splits(self, n_kv: int, group: int, rows_per_block: int = 8, blocks_per_sm: float = 2) -> int:
-        """Into how many slices of its context the decode attention cuts a sequence: as many as fill the GPU
-        once (blocks that wait for a second wave cost more than longer slices), at least 128 positions each."""
-        if self.fixed_splits is not None:
-            return self.fixed_splits
-        chunks = (group + rows_per_block - 1) // rows_per_block
-        blocks = max(1, self.n_seqs * n_kv * chunks)
-        fit = int(blocks_per_sm * self.sm_count) // blocks
-        return int(max(1, min(fit, 32, self.max_kv_len // 128)))
+    def plan_of(self, mixer) -> Any:
+        """The mixer's plan for this step: the recorded one in a replayed step, else worked out for the step."""
+        if self.fixed_plans is not None and id(mixer) in self.fixed_plans:
+            return self.fixed_plans[id(mixer)]
+        return mixer.decode_plan(self.n_seqs, self.max_kv_len, self.sm_count) if self.is_decode else None
+
+    def _host(self, name: str):
+        v = getattr(self, name)
+        if v is None:
+            raise RuntimeError(
+                "this step is recorded once and replayed (a CUDA graph): Python that reads the step's host-side lists "
+                "would not run again.  A part that plans on the host sets `plans_on_host = True`; its model then "
+                "decodes without a graph")
+        return v
+
+    @property
+    def host_q_lens(self) -> List[int]:
+        return self._host("_host_q_lens")
+
+    @property
+    def host_slots(self) -> List[int]:
+        return self._host("_host_slots")
+
+    @property
+    def host_pos0(self) -> List[int]:
+        return self._host("_host_pos0")
 
 
 class _Staging:
@@ -105,8 +124,15 @@ class Engine:
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 148
         self.bytes_h2d = 0
         self._decode_graphs = {}
-        mixers = [layer.block.mixer for layer in getattr(model, "layers", [])]
-        self._attn_shapes = sorted({(m.n_kv, m.n_heads // m.n_kv, getattr(m, "head_dim", 128)) for m in mixers if hasattr(m, "n_kv")})
+        # the mixers in the order they run (a layer named twice appears once: its plan is the same both times)
+        self._mixers = []
+        layers = getattr(model, "layers", [])
+        for e in getattr(model.spec, "schedule", ()):
+            m = layers[e.layer].block.mixer
+            if all(m is not seen for seen in self._mixers):
+                self._mixers.append(m)
+        parts = [getattr(model, n, None) for n in ("embedding", "final_norm", "head")] + [p for layer in layers for p in layer.block.parts()]
+        self.plans_on_host = any(getattr(p, "plans_on_host", False) for p in parts)
 
     # ---- host-side checks, before anything is launched (src/model.rs:974-982) -------------------
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -121,9 +147,12 @@ class Engine:
                 raise ValueError(f"slot {e.slot} is not open")
             if len(e.tokens) == 0:
                 raise ValueError(f"slot {e.slot}: a step entry needs at least one token")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab):
-                    raise ValueError(f"token id {t} is outside the vocabulary ({self.vocab})")
+            ids = np.asarray(e.tokens)
+            if ids.ndim != 1 or ids.dtype.kind not in "iu":
+                raise ValueError(f"slot {e.slot}: tokens must be a flat list of integers")
+            bad = (ids < 0) | (ids >= self.vocab)
+            if bad.any():
+                raise ValueError(f"token id {int(ids[bad][0])} is outside the vocabulary ({self.vocab})")
             for w in e.want:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise ValueError(f"slot {e.slot}: wanted place {w} is outside this step's {len(e.tokens)} tokens")
@@ -176,17 +205,18 @@ class Engine:
         ctx.logit_rows = dev[o:o + R] if R else None
         ctx.empty_f32 = self._empty_f32
         ctx.sm_count = self._sm_count
-        ctx.host_q_lens, ctx.host_slots, ctx.host_pos0 = lens, [e.slot for e in entries], pos0
+        ctx._host_q_lens, ctx._host_slots, ctx._host_pos0 = lens, [e.slot for e in entries], pos0
         return ctx
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """The model over the tokens of `ctx`: embedding, the scheduled layers, then final norm and head on
         the wanted rows only (src/model.rs:1173-1188)."""
+        from ..kernels import ops
         model = self.model
-        x = model.embedding.forward(ctx.tokens)
+        # the residual stream: a tensor that a deferred product may leave partial sums for (they travel with it)
+        x = ops.as_carrier(model.embedding.forward(ctx.tokens))
         for i, e in enumerate(model.spec.schedule):
             model.layers[e.layer].block.forward(x, ctx, self.cache.memory(i))
-        from ..kernels import ops
         if ctx.logit_rows is None:
             ops.drop_pending(x)
             return None
@@ -196,14 +226,10 @@ class Engine:
         ops.drop_pending(x)
         return model.head.forward(h)
 
-    def decode_splits_for(self, ctx: StepContext) -> int:
-        """One slice count for a captured decode step: what the model's attention layers would choose."""
-        if not self._attn_shapes:
-            return 1
-        fast = self.model.rt.dtype == torch.bfloat16
-        from ..kernels import ops
-        return max(ctx.decode_splits(kv, group, 16 if fast else 8, ops.attn_decode_blocks_per_sm(hd, fast))
-                   for kv, group, hd in self._attn_shapes)
+    def decode_plans(self, n_seqs: int, max_kv_len: int) -> Dict[int, Any]:
+        """What every mixer plans for one-token steps of this shape: id(mixer) -> plan.  A recorded step is keyed
+        by these plans, so a mixer decides itself how its work is cut and when a new recording is needed."""
+        return {id(m): m.decode_plan(n_seqs, max_kv_len, self._sm_count) for m in self._mixers}
 
     def decoder(self, slots: Sequence[int], use_graph: bool = True):
         """A runner of one-token steps for these slots (see engine.decode.DecodeRunner)."""

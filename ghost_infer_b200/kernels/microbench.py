@@ -6,7 +6,7 @@
 Kernels: gemm_stream, gemm_skinny (decode products), gemm_tc (prefill product), attn_decode, attn_prefill (mma.sync),
 attn_prefill_t5 (tcgen05),
 rmsnorm, rope, sample.  Operands rotate through enough different buffers to exceed the L2 cache, so a bytes
-figure is a DRAM figure.  The same command under `ncu -k regex:<kernel> -c 3` profiles exactly these launches.
+figure is a DRAM figure.  The same command under `ncu --clock-control none -k regex:<kernel> -c 3` profiles exactly these launches.
 The reference times whole runs only (`bench`, src/main.rs:1241-1285) and, per operation, wall-clock buckets
 (src/profile.rs:7-46); per-kernel device timing is what a roofline needs.
 """

@@ -52,7 +52,7 @@ def _bind():
         "gi_rope_cache_write": [P, I, L, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P],
         "gi_rope_cache_write_settle": [P, I, L, P, P, P, P, I, P, P, I, I, I, I, I, I, I, SettleT, P],
         "gi_attn_prefill_generic": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
-        "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
+        "gi_attn_decode_generic": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P],
         "gi_gemm_stream_bf16": [P, I, P, P, P, P, I, I, I, I, L, L, L, I, P],
         "gi_gemm_stream_bf16_ex": [P, I, P, P, P, P, I, I, I, I, L, L, L, I, P, I, I, L, I, I, P],
         "gi_gemm_stream_status": [P],
@@ -97,9 +97,13 @@ def _dt(t: torch.Tensor, what: str) -> int:
         raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
 
 
-def _cuda(t: torch.Tensor, what: str) -> None:
+def _cuda(t: torch.Tensor, what: str, settles: bool = False) -> None:
+    """`settles`: the kernel about to read `t` adds pending partial sums itself; any other kernel must not meet them."""
     if not t.is_cuda:
         raise KernelError(f"{what} must live on a CUDA device; there is no CPU path")
+    if not settles and type(t) is Carrier and t.__dict__.get("_gi_pending") is not None:
+        raise KernelError(f"{what}: partial sums of a deferred product are pending for this tensor; "
+                          f"only a kernel that settles them (or ops.settle) may read it")
 
 
 def _rows(t: torch.Tensor, what: str) -> int:
@@ -135,7 +139,7 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor]
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
             rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     lib = _bind()
-    _cuda(x, "rmsnorm input")
+    _cuda(x, "rmsnorm input", settles=True)
     if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
         raise KernelError("rmsnorm input must be a contiguous float32 [rows, width] matrix")
     d = x.shape[1]
@@ -144,8 +148,13 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     n = x.shape[0] if rows is None else rows.numel()
     if out is None:
         out = torch.empty((n, d), dtype=out_dtype, device=x.device)
-    pending = _pending.pop(x.data_ptr(), None)
+    pending = _take_pending(x)
+    if pending is not None and (pending[1] or d % 4 != 0):
+        x.__dict__["_gi_pending"] = pending         # not this kernel's kind of sums: the plain way
+        settle(x)
+        pending = None
     if pending is not None:
+        pending = pending[0]
         # a deferred product left partial sums for this stream: add them while the rows are read anyway (and write
         # the settled rows back; with a selection of rows nothing is written back: the selection may name a row twice,
         # and the stream's other rows stay unsettled, so whoever selects rows must be the stream's last reader)
@@ -162,19 +171,57 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
 # The decode product cuts tiles of W between blocks; adding such a tile's partial sums into the residual
 # stream needs an exchange between blocks at the kernel's end.  When the stream's next reader is a norm, which
 # reads every row anyway, the product leaves the partial sums in scratch and the norm adds them (in a fixed
-# order).  `defer_into(x)` says that accumulations into x may be left pending; `settle(x)` adds what is pending.
-_pending: Dict[int, SettleT] = {}
+# order).  What is pending travels with the tensor itself: only a `Carrier` can have sums pending, the record
+# is an attribute of that object (so it dies with it and no other tensor at the same address inherits it),
+# any torch operation on it settles first, and a kernel wrapper that does not settle refuses it.
+_METADATA = frozenset((
+    "get:shape", "get:dtype", "get:device", "get:is_cuda", "get:ndim", "get:layout", "get:requires_grad", "get:is_cpu",
+    "get:is_meta", "get:names", "get:grad_fn", "get:is_leaf", "get:_base",
+    "data_ptr", "stride", "size", "dim", "numel", "nelement", "element_size", "storage_offset", "is_contiguous",
+    "is_floating_point", "is_complex", "get_device", "__len__", "ndimension", "__repr__", "__format__"))
+
+
+class Carrier(torch.Tensor):
+    """A device tensor that a deferred product may leave partial sums for (the residual stream of a step; the
+    q/k/v rows on their way to the kernel that rotates and stores).  Shares its storage with the plain tensor
+    it was made from.  Reading its sizes, strides and address is free; every other torch operation on it first
+    adds what is pending (one kernel launch), so that no reader can see rows without their sums."""
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        name = getattr(func, "__name__", "")
+        if name == "__get__":
+            name = "get:" + getattr(getattr(func, "__self__", None), "__name__", "")
+        if name not in _METADATA:
+            for a in args:
+                if type(a) is Carrier and a.__dict__.get("_gi_pending") is not None:
+                    settle(a)
+        with torch._C.DisableTorchFunctionSubclass():
+            return func(*args, **(kwargs or {}))
+
+
+def as_carrier(t: torch.Tensor) -> torch.Tensor:
+    """`t` as a tensor that deferred products may leave partial sums for (same storage)."""
+    return t if type(t) is Carrier else t.as_subclass(Carrier)
+
+
 _pending_scratch: Dict[int, torch.Tensor] = {}
-_defer_target: Optional[int] = None
+_defer_target: Optional[torch.Tensor] = None
+
+
+def _take_pending(x: torch.Tensor):
+    if type(x) is not Carrier:
+        return None
+    return x.__dict__.pop("_gi_pending", None)
 
 
 @contextlib.contextmanager
 def defer_into(x: torch.Tensor):
-    """Inside, a product accumulated into `x` may leave partial sums pending.  The caller promises that the next
-    reader of `x` is `rmsnorm` (which settles them) or that it calls `settle(x)` first."""
+    """Inside, a product accumulated into `x` (this very object, a `Carrier`) may leave partial sums pending.
+    Whoever reads `x` next settles them: `rmsnorm` while it reads the rows, anything else through `settle`."""
     global _defer_target
     prev = _defer_target
-    _defer_target = x.data_ptr() if (TUNE["defer_residual"] and x.is_cuda) else None
+    _defer_target = x if (TUNE["defer_residual"] and type(x) is Carrier and x.is_cuda) else None
     try:
         yield
     finally:
@@ -186,8 +233,8 @@ _defer_store = False
 
 @contextlib.contextmanager
 def defer_store():
-    """Inside, a decode product that stores bfloat16 rows may leave the tiles cut between blocks as partial sums.
-    The caller promises that the next reader of the rows is `rope_cache_write`, which adds them."""
+    """Inside, a decode product that stores bfloat16 rows may leave the tiles cut between blocks as partial sums
+    (its result is then a `Carrier`).  `rope_cache_write` adds them while it reads the rows."""
     global _defer_store
     prev = _defer_store
     _defer_store = bool(TUNE["defer_residual"])
@@ -198,27 +245,30 @@ def defer_store():
 
 
 def has_pending(x: torch.Tensor) -> bool:
-    return x.data_ptr() in _pending
+    return type(x) is Carrier and x.__dict__.get("_gi_pending") is not None
 
 
 def settle(x: torch.Tensor) -> None:
-    """Adds pending partial sums (if any) to every row of the float32 matrix `x`."""
-    pending = _pending.pop(x.data_ptr(), None)
+    """Adds pending partial sums (if any) to every row of the matrix `x`."""
+    pending = _take_pending(x)
     if pending is None:
         return
     lib = _bind()
-    _check(lib, lib.gi_settle(x.data_ptr(), pending, None, x.shape[0], x.shape[1], _stream()))
+    rec, store = pending
+    if store:
+        raise KernelError("partial sums of a stored product are pending: only rope_cache_write settles those")
+    _check(lib, lib.gi_settle(x.data_ptr(), rec, None, x.shape[0], x.shape[1], _stream()))
 
 
 def drop_pending(x: torch.Tensor) -> None:
     """Forgets partial sums pending for `x` (the stream is not read again)."""
-    _pending.pop(x.data_ptr(), None)
+    _take_pending(x)
 
 
 def _defer_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-    return (_defer_target is not None and out.data_ptr() == _defer_target and out.dtype == torch.float32
+    return (_defer_target is not None and out is _defer_target and out.dtype == torch.float32
             and out.is_contiguous() and out.shape[1] % 4 == 0 and out.shape[1] <= 8192 and out.data_ptr() % 16 == 0
-            and out.data_ptr() not in _pending)
+            and not has_pending(out))
 
 
 def _gemm_stream_deferred(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = 4) -> torch.Tensor:
@@ -236,7 +286,8 @@ def _gemm_stream_deferred(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m
     n_ctas, kb, nt = c_int(0), c_int(0), c_int(0)
     lib.gi_gemm_stream_geometry(m, n, k, ctypes.byref(n_ctas), ctypes.byref(kb), ctypes.byref(nt))
     tabs = _settle_tables(a.device, (n + 127) // 128, kb.value, n_ctas.value)
-    _pending[out.data_ptr()] = SettleT(scratch.data_ptr(), tabs[0].data_ptr(), tabs[1].data_ptr(), tabs[2].data_ptr(), nt.value)
+    out.__dict__["_gi_pending"] = (SettleT(scratch.data_ptr(), tabs[0].data_ptr(), tabs[1].data_ptr(), tabs[2].data_ptr(), nt.value),
+                                   mode == SKINNY_STORE_DEFER)
     return out
 
 
@@ -474,7 +525,7 @@ def _decode_product(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[t
                 return _gemm_stream_deferred(a, w, out)
             settle(out)          # something is pending for this stream already: add it before adding more
         if mode == SKINNY_STORE_BF16 and _defer_store and out is None and w.shape[0] % 8 == 0:
-            out = torch.empty((a.shape[0], w.shape[0]), dtype=torch.bfloat16, device=a.device)
+            out = as_carrier(torch.empty((a.shape[0], w.shape[0]), dtype=torch.bfloat16, device=a.device))
             return _gemm_stream_deferred(a, w, out, SKINNY_STORE_DEFER)
         return gemm_stream(a, w, mode, out)
     return gemm_skinny(a, w, mode, out)
@@ -552,7 +603,7 @@ def rope_cache_write(qkv: torch.Tensor, table: Optional[torch.Tensor], positions
     """Rotates the q and k parts of the packed rows by the angles of `table` (q in place, k into the cache)
     and copies v into the cache."""
     lib = _bind()
-    _cuda(qkv, "q/k/v rows")
+    _cuda(qkv, "q/k/v rows", settles=True)
     ld = _rows(qkv, "q/k/v rows")
     n = qkv.shape[0]
     if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
@@ -572,9 +623,11 @@ def rope_cache_write(qkv: torch.Tensor, table: Optional[torch.Tensor], positions
             _i32(positions, "positions"), _i32(slots, "slots"), _i32(block_table, "block table"), max_pages,
             kcache.data_ptr() if kcache is not None else None, vcache.data_ptr() if vcache is not None else None,
             n, n_heads, n_kv, head_dim, rotary_dim, int(adjacent), int(write_cache))
-    pending = _pending.pop(qkv.data_ptr(), None)
+    pending = _take_pending(qkv)
     if pending is not None:       # the product left partial sums instead of some of these rows' values
-        _check(lib, lib.gi_rope_cache_write_settle(*args, pending, _stream()))
+        if not pending[1]:
+            raise KernelError("rope_cache_write met partial sums of an accumulating product")
+        _check(lib, lib.gi_rope_cache_write_settle(*args, pending[0], _stream()))
     else:
         _check(lib, lib.gi_rope_cache_write(*args, _stream()))
 
@@ -599,7 +652,11 @@ def attn_prefill_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Te
 def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                         seq_slots: torch.Tensor, seq_lens: torch.Tensor, n_seqs: int, n_heads: int, n_kv: int,
                         head_dim: int, scale: float, window: Optional[int], n_splits: int, out: torch.Tensor,
-                        part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                        own_tiles: int = 0) -> torch.Tensor:
+    """`own_tiles` > 0: slice s of a sequence is tiles [s * own_tiles, (s + 1) * own_tiles) of its own span (32 keys a
+    tile), whatever `n_splits` is, which must then cover the longest sequence; 0: every span is cut into `n_splits`
+    equal slices."""
     lib = _bind()
     _cuda(q, "queries")
     ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
@@ -617,7 +674,7 @@ def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Ten
         part_ml.data_ptr() if part_ml is not None else None, q.data_ptr(), ldq, _dt(q, "queries"),
         kcache.data_ptr(), vcache.data_ptr(), _i32(block_table, "block table"), block_table.shape[1],
         _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"), n_seqs, n_heads, n_kv, head_dim, float(scale),
-        int(window or 0), int(n_splits), _stream()), 2 if n_splits > 1 else 1)
+        int(window or 0), int(n_splits), int(own_tiles), _stream()), 2 if n_splits > 1 else 1)
     return out
 
 
@@ -761,23 +818,56 @@ def attn_decode_blocks_per_sm(head_dim: int, fast: bool) -> float:
     return per_sm * TUNE["attn_waves"]
 
 
+OWN_LENGTH_TILES = 8      # 32-bit decode attention: a slice is this many 32-key tiles of the sequence's own span
+
+
+def attn_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, n_kv: int, head_dim: int,
+                     window: Optional[int], dtype: torch.dtype):
+    """How the decode attention cuts contexts into slices, as (slices in the launch, tiles per slice).
+
+    bfloat16: tiles per slice 0 = every sequence is cut into the same number of slices, as many as fill the GPU
+    once (blocks that wait for a second wave cost more than longer slices), at least 128 positions each.
+    float32: slices of a fixed length counted from the start of the sequence's own span, so that a sequence's
+    sums are formed in the same order whatever else the step holds (the reference sizes its slices from the
+    token's own span for the same reason, src/cuda.rs:1639-1644, :8432-8437); the launch holds as many slices as
+    the longest sequence needs, and shorter ones leave theirs empty."""
+    if dtype == torch.float32:
+        span = max_kv_len if not window else min(max_kv_len, int(window) + 31)
+        tiles = (span + 31) // 32 + (1 if window else 0)
+        return max(1, (tiles + OWN_LENGTH_TILES - 1) // OWN_LENGTH_TILES), OWN_LENGTH_TILES
+    fast = dtype == torch.bfloat16 and head_dim in (64, 128)
+    rows_per_block = 16 if fast else 8            # the tensor-core kernel packs 16 heads of a group into a block
+    group = n_heads // n_kv
+    chunks = (group + rows_per_block - 1) // rows_per_block
+    blocks = max(1, n_seqs * n_kv * chunks)
+    fit = int(attn_decode_blocks_per_sm(head_dim, fast) * sm_count) // blocks
+    return int(max(1, min(fit, 32, max_kv_len // 128))), 0
+
+
 def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim: int, scale: float,
-              window: Optional[int], out: torch.Tensor) -> torch.Tensor:
+              window: Optional[int], out: torch.Tensor, plan=None) -> torch.Tensor:
     """Attention of a step's tokens over the cache (which already holds the step's own keys and values).
-    The queries are the first n_heads * head_dim columns of the packed rows `qkv`."""
+    The queries are the first n_heads * head_dim columns of the packed rows `qkv`.  `plan`: what
+    `attn_decode_plan` gave for a decode step (worked out here when absent)."""
     if memory.k is None:
         raise KernelError("attention needs a cache to read from")
     if step.is_decode:
         fast = attn_decode_tc_ok(qkv, memory.k, head_dim)
-        # the tensor-core kernel packs 16 heads of a group into a block
-        n_splits = step.decode_splits(n_kv, n_heads // n_kv, 16 if fast else 8, attn_decode_blocks_per_sm(head_dim, fast))
+        if plan is None:
+            plan = attn_decode_plan(step.n_seqs, step.max_kv_len, step.sm_count, n_heads, n_kv, head_dim, window, qkv.dtype)
+        n_splits, own_tiles = plan
         part_o = part_ml = None
         if n_splits > 1:
             part_o = torch.empty((step.n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
-        kernel = attn_decode_tc if fast else attn_decode_generic
-        return kernel(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
-                      step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
+        if fast:
+            if own_tiles:
+                raise KernelError("the tensor-core decode attention cuts every sequence into the same number of slices")
+            return attn_decode_tc(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
+                                  step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
+        return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
+                                   step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml,
+                                   own_tiles=own_tiles)
     if attn_decode_tc_ok(qkv, memory.k, head_dim) and out.stride(0) % 2 == 0:
         # tcgen05 (scores and output in tensor memory); mma.sync when that is switched off or the rows do not suit TMA
         t5 = (TUNE["attn_prefill_tcgen05"] and head_dim in (64, 128) and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0

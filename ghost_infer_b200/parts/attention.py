@@ -5,6 +5,9 @@ matrices stacked by rows, as the reference's GPU path merges them: src/cuda.rs:7
 encoding on q and k; k and v appended to the cache; head h attends with kv head h / (H / KV) over every
 cached position up to its own (src/model.rs:1320-1419), scores scaled by `scale` (1/sqrt(head_dim) for
 Llama, src/model.rs:271); residual += Wo att.  With `window` = w a query sees only the last w positions.
+
+Tensor names: prefix + "self_attn.{q,k,v,o}_proj.weight" unless `params["tensor_names"]` gives others for the
+keys "q", "k", "v", "o".
 """
 from __future__ import annotations
 
@@ -35,7 +38,7 @@ class GqaAttention(Mixer):
         self.position = lookup("position", pos.kind)(pos.params, prefix) if pos is not None else None
         self.q_dim = self.n_heads * self.head_dim
         self.kv_dim = self.n_kv * self.head_dim
-        self.names = {k: f"{prefix}self_attn.{k}_proj.weight" for k in ("q", "k", "v", "o")}
+        self.names = {k: self.tensor_name(k, f"self_attn.{k}_proj.weight") for k in ("q", "k", "v", "o")}
 
     def weights(self) -> List[WeightSpec]:
         n = self.names
@@ -46,6 +49,15 @@ class GqaAttention(Mixer):
         if self.window:
             return CacheRequest("window", self.n_kv, self.head_dim, int(self.window))
         return CacheRequest("full", self.n_kv, self.head_dim)
+
+    @property
+    def plans_on_host(self) -> bool:
+        return bool(self.position is not None and self.position.plans_on_host)
+
+    def decode_plan(self, n_seqs: int, max_kv_len: int, sm_count: int):
+        """Into how many slices the decode attention cuts the contexts (the kernels' own rule)."""
+        return ops.attn_decode_plan(n_seqs, max_kv_len, sm_count, self.n_heads, self.n_kv, self.head_dim, self.window,
+                                    self.rt.dtype)
 
     def bind(self, tensors, rt) -> None:
         super().bind(tensors, rt)
@@ -73,5 +85,6 @@ class GqaAttention(Mixer):
                                  self.n_heads, self.n_kv, self.head_dim, 0, False,
                                  memory.writes and memory.k is not None)
         att = torch.empty((h.shape[0], self.q_dim), dtype=self.rt.dtype, device=h.device)
-        ops.attention(qkv, memory, step, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, att)
+        ops.attention(qkv, memory, step, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, att,
+                      plan=step.plan_of(self))
         linear(att, self.w_o, out=residual, accumulate=True)

@@ -8,10 +8,20 @@ Interfaces (a new kind of part implements one of them and registers under a name
   q and k parts of the packed rows as the encoding wants and writes k and v to the cache.
 * `Mixer.forward(h, residual, step, memory)`: adds the mixer's output to `residual` in place.
   `Mixer.cache_request()` / `Mixer.state_request()` say what memory it wants per sequence.
+  `Mixer.decode_plan(n_seqs, max_kv_len, sm_count)` says how it cuts the work of one-token steps of that shape
+  (anything hashable, or None); a recorded step keeps the plan it was recorded with (`step.plan_of(self)`).
 * `FeedForward.forward(h, residual, step)`: adds its output to `residual` in place.
 * `Block.forward(x, layer, step, memory)`: runs one layer's parts in its arrangement.
 
-No part knows which model it is in: sizes, constants and tensor names arrive as parameters.
+No part knows which model it is in: sizes, constants and tensor names arrive as parameters (a part's
+tensor names are its prefix plus sub-names that `params["tensor_names"]` may replace).
+
+The arrays of a step live on the device; a part that works from them alone can be recorded once and
+replayed (generation's one-token steps are).  A part whose `forward` plans in Python from the step's
+host-side lists (`step.host_slots`, `step.host_q_lens`, `step.host_pos0`) sets `plans_on_host = True`:
+a model with such a part decodes launch by launch instead.  Rows of a recorded step beyond the live
+sequences carry slot -1; for them the cache's page table gives the trash page and `memory.state[-1]` is a
+trash row, so indexing by the slot arrays needs no special case.
 """
 from __future__ import annotations
 
@@ -52,9 +62,17 @@ class Runtime:
 
 
 class Part:
+    plans_on_host = False      # True: forward() reads the step's host-side lists, so it must run in Python every step
+
     def __init__(self, params: Mapping[str, Any], prefix: str = ""):
         self.params = params
         self.prefix = prefix
+
+    def tensor_name(self, key: str, default: str) -> str:
+        """Full name of the tensor this part calls `key`: the prefix plus `params["tensor_names"][key]`, or plus
+        `default` when the specification does not rename it."""
+        names = self.params.get("tensor_names") if hasattr(self.params, "get") else None
+        return self.prefix + (names.get(key, default) if names else default)
 
     def weights(self) -> List[WeightSpec]:
         return []
@@ -79,6 +97,11 @@ class Mixer(Part):
         return None
 
     def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def decode_plan(self, n_seqs: int, max_kv_len: int, sm_count: int) -> Any:
+        """How this mixer cuts the work of a step of `n_seqs` one-token rows over contexts of up to `max_kv_len`
+        positions; hashable.  None: nothing about it depends on the shape."""
         return None
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, step, memory: LayerMemory) -> None:

@@ -23,11 +23,11 @@ class TokenEmbedding(Part):
         self.hidden = int(params["hidden_size"])
 
     def weights(self) -> List[WeightSpec]:
-        return [WeightSpec(self.prefix + "weight", (self.vocab, self.hidden))]
+        return [WeightSpec(self.tensor_name("weight", "weight"), (self.vocab, self.hidden))]
 
     def bind(self, tensors, rt) -> None:
         super().bind(tensors, rt)
-        self.weight = rt.place(tensors[self.prefix + "weight"])
+        self.weight = rt.place(tensors[self.tensor_name("weight", "weight")])
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         return ops.embed(self.weight, tokens)
@@ -43,11 +43,11 @@ class LinearHead(Part):
         self.weight: Optional[torch.Tensor] = None
 
     def weights(self) -> List[WeightSpec]:
-        return [] if self.tied else [WeightSpec(self.prefix + "weight", (self.vocab, self.hidden))]
+        return [] if self.tied else [WeightSpec(self.tensor_name("weight", "weight"), (self.vocab, self.hidden))]
 
     def ignorable(self) -> List[str]:
         """Names a file may carry without their being used (a tied model that still stores its head)."""
-        return [self.prefix + "weight"] if self.tied else []
+        return [self.tensor_name("weight", "weight")] if self.tied else []
 
     def bind(self, tensors, rt, embedding: Optional[TokenEmbedding] = None) -> None:
         super().bind(tensors, rt)
@@ -56,7 +56,7 @@ class LinearHead(Part):
                 raise ValueError("a tied head needs the embedding it is tied to")
             self.weight = embedding.weight
         else:
-            self.weight = rt.place(tensors[self.prefix + "weight"])
+            self.weight = rt.place(tensors[self.tensor_name("weight", "weight")])
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return linear(h, self.weight, out_dtype=torch.float32)

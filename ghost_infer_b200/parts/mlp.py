@@ -2,6 +2,9 @@
 
 No biases; gate and up are one product over the two matrices stacked by rows, as the reference's GPU
 path packs them (src/quant.rs:1135-1154, src/model.rs:1133-1147, src/cuda.rs:9238-9256).
+
+Tensor names: prefix + "mlp.{gate,up,down}_proj.weight" unless `params["tensor_names"]` gives others for the
+keys "gate", "up", "down".
 """
 from __future__ import annotations
 
@@ -21,7 +24,7 @@ class SwiGlu(FeedForward):
         super().__init__(params, prefix)
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
-        self.names = {k: f"{prefix}mlp.{k}_proj.weight" for k in ("gate", "up", "down")}
+        self.names = {k: self.tensor_name(k, f"mlp.{k}_proj.weight") for k in ("gate", "up", "down")}
 
     def weights(self) -> List[WeightSpec]:
         n = self.names

@@ -24,11 +24,11 @@ class RmsNorm(Norm):
         self.eps = float(params["eps"])
 
     def weights(self) -> List[WeightSpec]:
-        return [WeightSpec(self.prefix + "weight", (self.size,), "ones")]
+        return [WeightSpec(self.tensor_name("weight", "weight"), (self.size,), "ones")]
 
     def bind(self, tensors, rt) -> None:
         super().bind(tensors, rt)
-        self.weight = rt.place(tensors[self.prefix + "weight"])
+        self.weight = rt.place(tensors[self.tensor_name("weight", "weight")])
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, self.rt.dtype, rows=rows)

@@ -41,6 +41,8 @@ def write_random_model(model_dir: str, raw_config: Mapping[str, Any], seed: int 
     os.makedirs(model_dir, exist_ok=True)
     cfg = dict(raw_config)
     cfg["torch_dtype"] = "bfloat16" if t_dtype == torch.bfloat16 else "float32"
+    if hasattr(model.config, "model_type"):
+        cfg.setdefault("model_type", model.config.model_type)     # other readers of such folders look for it
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(cfg, f, indent=2)
     tensors = random_tensors(model.weight_manifest(), seed, t_dtype, std, norm_jitter)

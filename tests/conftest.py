@@ -20,7 +20,7 @@ TINY_A = {
 TINY_B = {
     "architectures": ["LlamaForCausalLM"], "hidden_size": 96, "num_hidden_layers": 3, "num_attention_heads": 3,
     "num_key_value_heads": 1, "head_dim": 32, "intermediate_size": 256, "vocab_size": 384,
-    "max_position_embeddings": 512, "rope_theta": 500000.0,
+    "max_position_embeddings": 256, "rope_theta": 500000.0,
     "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 32},
     "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "eos_token_id": [3, 5],

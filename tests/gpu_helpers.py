@@ -29,8 +29,11 @@ def plain_logits(model_dir, tokens):
 
 
 def make_engine(model_dir, dtype, max_tokens=64 * 48, max_seq_len=2048, max_slots=None):
+    """The tiny models' own `max_position_embeddings` are small (128 to 1,024); the tests run sequences past
+    them on purpose (pages, slices and buckets need length), which a cache only allows when asked."""
     model = gi.Model.from_pretrained(model_dir, dtype=dtype, device="cuda:0")
-    cache = model.new_cache(max_tokens=max_tokens, max_seq_len=max_seq_len, max_slots=max_slots)
+    cache = model.new_cache(max_tokens=max_tokens, max_seq_len=max_seq_len, max_slots=max_slots,
+                            beyond_trained_positions=True)
     return gi.Engine(model, cache)
 
 

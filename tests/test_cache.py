@@ -134,7 +134,7 @@ def test_groups_by_request_and_shared_memory():
     m0, m3, m4 = c.memory(0), c.memory(3), c.memory(4)
     assert m3.k.data_ptr() == m0.k.data_ptr() and m0.writes and not m3.writes      # entry 3 reads entry 0's cache
     assert c.memory(1).window == 32 and m0.window is None
-    assert m4.k is None and m4.state.shape == (4, 3, 2)
+    assert m4.k is None and m4.state.shape == (4 + 1, 3, 2)          # four slots and the padding rows' trash row
     assert c.bytes_per_token() == 2 * 3 * 2 * 16 * 4 and c.state_bytes_per_sequence() == 24
 
 

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 import ghost_infer_b200 as gi
-from gpu_helpers import oracle, tokens_for
+from gpu_helpers import check_logits, oracle, tokens_for
 import plain_llama as pl
 
 pytestmark = pytest.mark.gpu
@@ -34,7 +34,7 @@ def plain_greedy(model_dir, prompt, max_new, stop=()):
 def test_greedy_generation_matches_the_plain_implementation(model_dirs, tiny_configs, name, dtype):
     d = model_dirs(name, dtype)
     cfg = tiny_configs[name]
-    llm = gi.LLM(d, dtype=dtype, max_tokens=64 * 32, max_seq_len=512)
+    llm = gi.LLM(d, dtype=dtype, max_tokens=64 * 32)
     lens = [5, 9, 13] if name == "A" else [1, 7, 40, 64]
     prompts = [tokens_for(cfg, n, 50 + i) for i, n in enumerate(lens)]
     res = llm.generate(prompts, max_new=8, temperature=0.0, stop_token_ids=(), batch_size=3)
@@ -53,7 +53,7 @@ def test_greedy_generation_matches_the_plain_implementation(model_dirs, tiny_con
 
 def test_stop_token_from_the_configuration(model_dirs, tiny_configs):
     d = model_dirs("A", "float32")
-    llm = gi.LLM(d, dtype="float32", max_tokens=64 * 8, max_seq_len=256)
+    llm = gi.LLM(d, dtype="float32", max_tokens=64 * 8)
     prompt = tokens_for(tiny_configs["A"], 6, 3)
     free, _, _ = plain_greedy(d, prompt, 6)
     res = llm.generate([prompt], max_new=6, temperature=0.0, stop_token_ids=[free[3]])
@@ -65,7 +65,7 @@ def test_stop_token_from_the_configuration(model_dirs, tiny_configs):
 def test_sampling_is_reproducible_and_does_not_depend_on_batch_mates(model_dirs, tiny_configs):
     d = model_dirs("B", "float32")
     cfg = tiny_configs["B"]
-    llm = gi.LLM(d, dtype="float32", max_tokens=64 * 16, max_seq_len=512)
+    llm = gi.LLM(d, dtype="float32", max_tokens=64 * 16)
     prompts = [tokens_for(cfg, n, 70 + i) for i, n in enumerate([1, 7, 40, 64])]
     kw = dict(max_new=16, temperature=0.8, top_k=40, top_p=0.9, seed=11, stop_token_ids=())
     a = [r.tokens for r in llm.generate(prompts, batch_size=4, **kw)]
@@ -99,27 +99,41 @@ def test_command_line_top_kvcheck_and_bench(tmp_path, model_dirs, tiny_configs):
     exe = [sys.executable, os.path.join(ROOT, "bin", "ghost-infer")]
     # top: the ten most likely next tokens, and every logit as little-endian float32 when the variable is set
     dump = tmp_path / "logits.f32"
-    p = subprocess.run(exe + ["top", d, ",".join(map(str, ids))], capture_output=True, text=True, timeout=600,
-                       env=dict(os.environ, GHOST_INFER_LOGITS_OUT=str(dump)))
-    assert p.returncode == 0, p.stderr
     cfg, w = oracle(d)
     ref = pl.forward(cfg, w, ids)[-1]
-    got = np.fromfile(dump, dtype="<f4")
-    assert got.shape == ref.shape and np.abs(got - ref).max() < 0.05
-    lines = [l for l in p.stdout.splitlines() if "logprob" in l]
-    assert len(lines) == 10 and int(lines[0].split()[0]) in np.argsort(-ref)[:2]
+    for dtype in ("float32", "bfloat16"):
+        p = subprocess.run(exe + ["top", d, ",".join(map(str, ids)), "--dtype", dtype], capture_output=True, text=True,
+                           timeout=600, env=dict(os.environ, GHOST_INFER_LOGITS_OUT=str(dump)))
+        assert p.returncode == 0, p.stderr
+        got = np.fromfile(dump, dtype="<f4")
+        assert got.shape == ref.shape
+        check_logits(got, ref, dtype, f"top {dtype}")
+        lines = [l for l in p.stdout.splitlines() if "logprob" in l]
+        order = np.argsort(-ref, kind="stable")
+        assert len(lines) == 10
+        if dtype == "float32":
+            assert [int(l.split()[0]) for l in lines] == [int(i) for i in order[:10]]
+            lse = np.log(np.exp(ref - ref.max()).sum()) + ref.max()
+            for l, i in zip(lines, order[:10]):
+                assert abs(float(l.split()[-1]) - (ref[i] - lse)) < 2e-4      # four decimals are printed
+        else:
+            assert int(lines[0].split()[0]) in order[:2]
     # kvcheck: all but the last 4 ids as a prompt, those one at a time; pick and log-probability per token
     idf, out = tmp_path / "ids.txt", tmp_path / "kv.txt"
     idf.write_text(" ".join(map(str, ids)))
-    p = subprocess.run(exe + ["kvcheck", d, str(idf), str(out), "4"], capture_output=True, text=True, timeout=600)
-    assert p.returncode == 0, p.stderr
-    rows = [l.split() for l in out.read_text().splitlines()]
-    assert len(rows) == 4 and "mean NLL" in p.stderr
     full = pl.forward(cfg, w, ids)
-    for j, (pick, lp) in enumerate(rows):
-        l = full[len(ids) - 5 + j]
-        want = l[ids[len(ids) - 4 + j]] - (np.log(np.exp(l - l.max()).sum()) + l.max())
-        assert abs(float(lp) - want) < 0.02
+    for dtype, tol in (("float32", 5e-5), ("bfloat16", 0.02)):
+        p = subprocess.run(exe + ["kvcheck", d, str(idf), str(out), "4", "--dtype", dtype], capture_output=True, text=True,
+                           timeout=600)
+        assert p.returncode == 0, p.stderr
+        rows = [l.split() for l in out.read_text().splitlines()]
+        assert len(rows) == 4 and "mean NLL" in p.stderr
+        for j, (pick, lp) in enumerate(rows):
+            l = full[len(ids) - 5 + j]
+            want = l[ids[len(ids) - 4 + j]] - (np.log(np.exp(l - l.max()).sum()) + l.max())
+            assert abs(float(lp) - want) < tol            # the file keeps five decimals
+            if dtype == "float32":
+                assert int(pick) == int(np.argmax(l))
     # bench: the reference's fixed workload and its one-line result
     p = subprocess.run(exe + ["bench", d, "-n", "6", "--prompt-len", "20", "--batch", "2"], capture_output=True, text=True,
                        timeout=600, env=dict(os.environ, GHOST_INFER_BENCH_ROUNDS="2"))

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from ghost_infer_b200.kernels import ops
+from ghost_infer_b200.kernels.library import KernelError
 from gpu_helpers import paged_from_dense
 import plain_llama as pl
 
@@ -569,7 +570,7 @@ def test_deferred_accumulation_is_settled_by_the_norm(m, n, k):
     want_x = x0.double() + a.double() @ w.double().T
     want_h = want_x * torch.rsqrt((want_x ** 2).mean(-1, keepdim=True) + 1e-5) * wn.double()
     # through the norm
-    x = x0.clone()
+    x = ops.as_carrier(x0.clone())
     with ops.defer_into(x):
         ops.linear(a, w, out=x, accumulate=True)
     assert ops.has_pending(x)
@@ -578,7 +579,7 @@ def test_deferred_accumulation_is_settled_by_the_norm(m, n, k):
     torch.testing.assert_close(x.double(), want_x, rtol=1e-5, atol=1e-4)
     torch.testing.assert_close(h.double(), want_h, rtol=1.6e-2, atol=1.6e-2)
     # selected rows only (the final norm): those rows are settled
-    x = x0.clone()
+    x = ops.as_carrier(x0.clone())
     with ops.defer_into(x):
         ops.linear(a, w, out=x, accumulate=True)
     rows = torch.tensor([m - 1, 0], dtype=torch.int32, device=DEV)
@@ -587,7 +588,7 @@ def test_deferred_accumulation_is_settled_by_the_norm(m, n, k):
     # settled on its own, and twice the same bits
     outs = []
     for _ in range(2):
-        x = x0.clone()
+        x = ops.as_carrier(x0.clone())
         with ops.defer_into(x):
             ops.linear(a, w, out=x, accumulate=True)
         ops.settle(x)
@@ -595,17 +596,40 @@ def test_deferred_accumulation_is_settled_by_the_norm(m, n, k):
     torch.testing.assert_close(outs[0].double(), want_x, rtol=1e-5, atol=1e-4)
     assert torch.equal(outs[0], outs[1])
     # outside a deferring context nothing is left pending
-    x = x0.clone()
+    x = ops.as_carrier(x0.clone())
     ops.linear(a, w, out=x, accumulate=True)
     assert not ops.has_pending(x)
     torch.testing.assert_close(x.double(), want_x, rtol=1e-5, atol=1e-4)
     # a second accumulation while one is pending settles the first before it adds
-    x = x0.clone()
+    x = ops.as_carrier(x0.clone())
     with ops.defer_into(x):
         ops.linear(a, w, out=x, accumulate=True)
         ops.linear(a, w, out=x, accumulate=True)
     ops.settle(x)
     torch.testing.assert_close(x.double(), x0.double() + 2 * (a.double() @ w.double().T), rtol=1e-5, atol=2e-4)
+    # what is pending travels with the tensor: a plain tensor is never deferred into ...
+    plain = x0.clone()
+    with ops.defer_into(plain):
+        ops.linear(a, w, out=plain, accumulate=True)
+    assert not ops.has_pending(plain)
+    torch.testing.assert_close(plain.double(), want_x, rtol=1e-5, atol=1e-4)
+    # ... any torch operation on a carrier settles first (a reader that forgets cannot see rows without their sums) ...
+    x = ops.as_carrier(x0.clone())
+    with ops.defer_into(x):
+        ops.linear(a, w, out=x, accumulate=True)
+    pending_before = ops.has_pending(x)
+    got = x[:, :7] + 0.0
+    assert not ops.has_pending(x)
+    torch.testing.assert_close(got.double(), want_x[:, :7], rtol=1e-5, atol=1e-4)
+    # ... and a kernel that does not settle refuses a tensor with sums pending instead of reading it
+    x = ops.as_carrier(x0.clone())
+    with ops.defer_into(x):
+        ops.linear(a, w, out=x, accumulate=True)
+    if ops.has_pending(x):
+        assert pending_before
+        with pytest.raises(KernelError, match="pending"):
+            ops.gemm_generic(x, torch.zeros(8, n, device=DEV))
+        ops.drop_pending(x)
 
 
 @pytest.mark.parametrize("m", [1, 8, 20])
@@ -739,3 +763,60 @@ def test_rope_and_cache_write_for_a_prompt(dtype, hd, rot):
         np.testing.assert_allclose(kc[page, :, int(pos[i]) % 64].double().cpu().numpy().reshape(-1), k_ref[i], rtol=t["rtol"], atol=t["atol"])
         np.testing.assert_array_equal(vc[page, :, int(pos[i]) % 64].double().cpu().numpy().reshape(-1), v_ref[i])
     assert float(kc[0].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("H,KV,hd,lens,hidden,splits", [(4, 2, 64, [102, 102], 192, 2), (4, 2, 64, [140, 111, 7], 192, 3),
+                                                         (3, 1, 128, [102, 90], 264, 2), (32, 8, 64, [700] * 4, 2048, 4),
+                                                         (32, 8, 128, [513] * 3, 4096, 3)])
+def test_a_replayed_step_reads_what_its_own_kernels_wrote(H, KV, hd, lens, hidden, splits):
+    """Product, rotation + cache write and decode attention recorded in a CUDA graph with dependent launch: each
+    kernel starts while the one before it still runs and must not read that kernel's results before its dependency
+    wait.  The graph's buffers hold other values before the first replay (the queries' rows are filled with NaN, the
+    cache rows of the new position with zeros), so a read that comes too early shows.  Compared bit for bit with the
+    same three kernels launched one by one."""
+    B = len(lens)
+    S = ((max(lens) + 63) // 64) * 64
+    k = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=70)
+    v = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=71)
+    kc, vc, bt = paged_from_dense(k, v, lens, seed=1, poison=0.0)
+    w = rnd((H + 2 * KV) * hd, hidden, dtype=torch.bfloat16, seed=72, scale=0.05)
+    h = rnd(B, hidden, dtype=torch.bfloat16, seed=73)
+    inv = torch.rand(hd // 2, device=DEV)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    kept = {}
+
+    def layer():
+        with ops.defer_store():
+            qkv = ops.linear(h, w, out_dtype=torch.bfloat16)
+        table = ops.rope_table(pos, inv)
+        ops.rope_cache_write(qkv, table, pos, slots, bt, kc, vc, H, KV, hd, hd, False, True)
+        out = torch.empty(B, H * hd, dtype=torch.bfloat16, device=DEV)
+        po = torch.empty(B * H * splits * hd, device=DEV)
+        pml = torch.empty(B * H * splits * 2, device=DEV)
+        ops.attn_decode_tc(qkv, kc, vc, bt, slots, lens_t, B, H, KV, hd, 0.125, None, splits, out, po, pml)
+        kept.update(qkv=qkv, table=table, po=po, pml=pml)
+        return out
+
+    was = ops.get_pdl()
+    ops.set_pdl(True)
+    try:
+        want = layer().clone()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = layer()
+        for _ in range(2):
+            for t in kept.values():
+                t.fill_(float("nan"))
+            for b in range(B):
+                page, off = int(bt[b, (lens[b] - 1) // 64]), (lens[b] - 1) % 64
+                kc[page, :, off] = 0
+                vc[page, :, off] = 0
+            torch.cuda.synchronize()
+            g.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, want)
+    finally:
+        ops.set_pdl(was)

@@ -187,7 +187,7 @@ def test_host_checks_come_before_any_launch(engines):
     eng.cache.close_slot(s)
 
 
-@pytest.mark.parametrize("name", ["B", "C", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_decoding_with_dependent_launch(model_dirs, tiny_configs, name):
     """Programmatic dependent launch lets a kernel start while its predecessor drains; results must not move.
     A batch decodes through the graph runner with it on, against the plain implementation and against itself off."""

@@ -2,6 +2,7 @@
 import math
 
 import numpy as np
+import pytest
 
 import plain_llama as pl
 from conftest import TINY_A, TINY_B
@@ -66,6 +67,66 @@ def test_llama3_scaling_bands():
     # the product's table is the same numbers
     assert np.array_equal(rotary_inv_freq(32, 500000.0, sc).numpy(), pl.rotary_inv_freq(32, 500000.0, sc))
     assert np.array_equal(rotary_inv_freq(16, 10000.0, None).numpy(), pl.rotary_inv_freq(16, 10000.0, None))
+
+
+# Rotary frequencies as literals.  They were worked out apart from both codes, with 60-digit decimal arithmetic
+# (exp and ln of the decimal module, pi as a literal) from the rule itself: inv_freq_i = theta^(-2i/dim); with
+# wavelen = 2 pi / inv_freq, a pair keeps its frequency if wavelen < orig / high, has it divided by `factor` if
+# wavelen > orig / low, and otherwise takes ((1 - s) / factor + s) * inv_freq with s = (orig / wavelen - low) /
+# (high - low); then rounded to float32.  The reference consumes such a table as `rope_freqs` = plain / scaled
+# (src/model.rs:208-211, :768).  Tiny B (dim 32, theta 5e5, factor 8, low 1, high 4, orig 32) has one kept pair,
+# one blended and fourteen divided; the 8B configuration (dim 128, orig 8192) has 29, 6 and 29.
+INV_FREQ_TINY_B = [
+    "0x1.0000000000000p+0", "0x1.b7a3860000000p-3", "0x1.8d275e0000000p-6", "0x1.5dc95a0000000p-7",
+    "0x1.3411900000000p-8", "0x1.0f53860000000p-9", "0x1.ddee9c0000000p-11", "0x1.a4ee400000000p-12",
+    "0x1.72ba440000000p-13", "0x1.46831a0000000p-14", "0x1.1f91f00000000p-15", "0x1.fa8b840000000p-17",
+    "0x1.be21880000000p-18", "0x1.88ec220000000p-19", "0x1.5a0f4e0000000p-20", "0x1.30c94e0000000p-21"]
+INV_FREQ_LLAMA_8B = [
+    "0x1.0000000000000p+0", "0x1.a115820000000p-1", "0x1.53c38a0000000p-1", "0x1.14c7080000000p-1",
+    "0x1.c2ef760000000p-2", "0x1.6f56fa0000000p-2", "0x1.2b3dc60000000p-2", "0x1.e788c20000000p-3",
+    "0x1.8d275e0000000p-3", "0x1.4387400000000p-3", "0x1.078d3e0000000p-3", "0x1.ad63380000000p-4",
+    "0x1.5dc95a0000000p-4", "0x1.1cf1300000000p-4", "0x1.d03cd00000000p-5", "0x1.7a2d080000000p-5",
+    "0x1.3411900000000p-5", "0x1.f5ea7e0000000p-6", "0x1.98de920000000p-6", "0x1.4d12740000000p-6",
+    "0x1.0f53860000000p-6", "0x1.ba0dd80000000p-7", "0x1.681ad80000000p-7", "0x1.2558fe0000000p-7",
+    "0x1.ddee9c0000000p-8", "0x1.8554ea0000000p-8", "0x1.3d28040000000p-8", "0x1.025c6a0000000p-8",
+    "0x1.a4ee400000000p-9", "0x1.1bfa0e0000000p-9", "0x1.67a2380000000p-10", "0x1.c12f3a0000000p-11",
+    "0x1.132ba80000000p-11", "0x1.47e2160000000p-12", "0x1.765ba60000000p-13", "0x1.90d10c0000000p-14",
+    "0x1.46831a0000000p-14", "0x1.09fb7e0000000p-14", "0x1.b159020000000p-15", "0x1.6103320000000p-15",
+    "0x1.1f91f00000000p-15", "0x1.d484e00000000p-16", "0x1.7da9e80000000p-16", "0x1.36e8ea0000000p-16",
+    "0x1.fa8b840000000p-17", "0x1.9ca3ea0000000p-17", "0x1.5024d60000000p-17", "0x1.11d4200000000p-17",
+    "0x1.be21880000000p-18", "0x1.6b6d0e0000000p-18", "0x1.280d960000000p-18", "0x1.e257020000000p-19",
+    "0x1.88ec220000000p-19", "0x1.4014d20000000p-19", "0x1.04be680000000p-19", "0x1.a8d0100000000p-20",
+    "0x1.5a0f4e0000000p-20", "0x1.19e8020000000p-20", "0x1.cb4a9a0000000p-21", "0x1.76258e0000000p-21",
+    "0x1.30c94e0000000p-21", "0x1.f091840000000p-22", "0x1.9483600000000p-22", "0x1.4985fe0000000p-22"]
+LLAMA_8B_SCALING = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                    "original_max_position_embeddings": 8192}
+
+
+def _ulps(a, b):
+    a, b = np.asarray(a, dtype=np.float32), np.asarray(b, dtype=np.float32)
+    return np.abs(a.view(np.int32).astype(np.int64) - b.view(np.int32).astype(np.int64))
+
+
+@pytest.mark.parametrize("literals,dim,scaling", [(INV_FREQ_TINY_B, 32, TINY_B["rope_scaling"]),
+                                                  (INV_FREQ_LLAMA_8B, 128, LLAMA_8B_SCALING)])
+def test_rotary_frequencies_against_literals(literals, dim, scaling):
+    """Both writings of the rule, the product's and the plain implementation's, give the literal table to one unit
+    in the last place; so does the typed configuration's path to the product's part."""
+    want = np.array([float.fromhex(h) for h in literals], dtype=np.float32)
+    assert len(want) == dim // 2
+    assert _ulps(pl.rotary_inv_freq(dim, 500000.0, scaling), want).max() <= 1
+    assert _ulps(rotary_inv_freq(dim, 500000.0, scaling).numpy(), want).max() <= 1
+    # through config.json's keys, as a model would get them
+    from ghost_infer_b200.config import LlamaConfig
+    from ghost_infer_b200.config.llama_spec import llama_rope_spec
+    from ghost_infer_b200.parts.rope import Rotary
+    raw = dict(TINY_B, head_dim=dim, hidden_size=3 * dim, rope_scaling=scaling)
+    part = Rotary(llama_rope_spec(LlamaConfig.from_dict(raw)).params)
+    assert _ulps(part.inv_freq_host.numpy(), want).max() <= 1
+    # the literals themselves hold all three bands: kept pairs equal theta^(-2i/dim), divided ones an eighth of it
+    plain = np.array([500000.0 ** (-2.0 * i / dim) for i in range(dim // 2)])
+    ratio = plain / want.astype(np.float64)
+    assert (np.abs(ratio - 1) < 1e-6).any() and (np.abs(ratio - 8) < 1e-5).any() and ((ratio > 1.001) & (ratio < 7.99)).any()
 
 
 def test_attention_is_causal_and_grouped():

@@ -1,35 +1,52 @@
 """Host-side planning of a decode step: into how many slices of its context the attention cuts a sequence."""
-from ghost_infer_b200.engine.step import StepContext
+import torch
+
 from ghost_infer_b200.kernels import ops
 
+BF, F32 = torch.bfloat16, torch.float32
 
-def ctx(n_seqs, max_kv_len, sms=148):
-    c = StepContext()
-    c.n_seqs, c.max_kv_len, c.sm_count, c.is_decode = n_seqs, max_kv_len, sms, True
-    return c
+
+def plan(n_seqs, max_kv_len, n_heads, n_kv, head_dim, window=None, dtype=BF, sms=148):
+    return ops.attn_decode_plan(n_seqs, max_kv_len, sms, n_heads, n_kv, head_dim, window, dtype)
 
 
 def test_slices_fill_the_blocks_an_sm_holds():
     # 8 sequences x 8 kv heads = 64 blocks per slice; two blocks per SM at head size 128, three at 64
     assert ops.attn_decode_blocks_per_sm(128, True) == 2 * ops.TUNE["attn_waves"]
     assert ops.attn_decode_blocks_per_sm(64, True) == 3 * ops.TUNE["attn_waves"]
-    assert ctx(8, 2048).decode_splits(8, 4, 16, ops.attn_decode_blocks_per_sm(128, True)) == 4
-    assert ctx(8, 2048).decode_splits(8, 4, 16, ops.attn_decode_blocks_per_sm(64, True)) == 6
+    assert plan(8, 2048, 32, 8, 128) == (4, 0)
+    assert plan(8, 2048, 32, 8, 64) == (6, 0)
 
 
 def test_slices_are_never_shorter_than_128_positions_nor_more_than_32():
-    assert ctx(1, 100).decode_splits(8, 4, 16, 2) == 1
-    assert ctx(1, 300).decode_splits(8, 4, 16, 2) == 2
-    assert ctx(1, 1 << 20).decode_splits(1, 4, 16, 2) == 32
+    assert plan(1, 100, 32, 8, 128) == (1, 0)
+    assert plan(1, 300, 32, 8, 128) == (2, 0)
+    assert plan(1, 1 << 20, 4, 1, 128) == (32, 0)
 
 
-def test_a_full_gpu_takes_one_slice_and_a_fixed_count_wins():
-    assert ctx(64, 2048).decode_splits(8, 4, 16, 2) == 1
-    c = ctx(64, 2048)
-    c.fixed_splits = 3                     # a captured graph keeps the count it was captured with
-    assert c.decode_splits(8, 4, 16, 2) == 3
+def test_a_full_gpu_takes_one_slice():
+    assert plan(64, 2048, 32, 8, 128) == (1, 0)
 
 
 def test_wide_groups_take_several_blocks_per_kv_head():
     # 40 heads on one kv head: three blocks of 16 rows per sequence and slice
-    assert ctx(4, 4096).decode_splits(1, 40, 16, 2) == (2 * 148) // (4 * 3)
+    assert plan(4, 4096, 40, 1, 128) == ((2 * 148) // (4 * 3), 0)
+
+
+def test_head_sizes_the_tensor_core_kernel_declines_count_eight_rows_a_block():
+    # head size 48 in bfloat16 runs the plain kernel: 8 heads a block (two blocks for a group of 16), two blocks per SM
+    assert plan(4, 1 << 20, 32, 2, 48) == ((2 * 148) // (4 * 2 * 2), 0)
+    assert plan(4, 1 << 20, 32, 2, 128) == (32, 0)
+
+
+def test_32_bit_slices_follow_the_sequence_s_own_length():
+    """In the 32-bit path a slice is eight 32-key tiles of the sequence's own span; the launch holds as many slices
+    as the longest sequence needs, whatever the batch."""
+    assert ops.OWN_LENGTH_TILES == 8
+    assert plan(1, 256, 4, 2, 16, dtype=F32) == (1, 8)
+    assert plan(1, 257, 4, 2, 16, dtype=F32) == (2, 8)
+    assert plan(64, 257, 4, 2, 16, dtype=F32) == (2, 8)             # the batch does not matter
+    assert plan(3, 5000, 4, 2, 16, dtype=F32) == ((5000 + 255) // 256, 8)
+    # a window bounds the span: at most window + 31 keys from the tile the window starts in, plus that tile's head
+    assert plan(3, 5000, 4, 2, 16, window=100, dtype=F32) == (1, 8)
+    assert plan(3, 5000, 4, 2, 16, window=300, dtype=F32) == (2, 8)
