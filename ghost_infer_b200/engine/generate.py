@@ -39,7 +39,9 @@ class GenerationStats:
 
 class GenerationLoop:
     """`engine` needs `.cache` (open_slot, close_slot, length, free_pages, max_seq_len) and
-    `.step(entries) -> logits`; `sampler` needs `.start(n)` and `.pick(logits, request_ids) -> tokens`."""
+    `.step(entries) -> logits`; `sampler` needs `.start(n)` and `.pick(logits, request_ids) -> tokens`.
+    With `engine.decoder(slots)` (a runner of one-token steps) and `sampler.pick_device` the loop keeps the
+    sampled tokens on the device and looks at them one step late; it takes the same decisions either way."""
 
     def __init__(self, engine, sampler, stop_token_ids: Sequence[int] = (), batch_size: int = 8,
                  on_token: Optional[Callable[[int, int], None]] = None, max_step_tokens: Optional[int] = None):
@@ -139,7 +141,8 @@ class GenerationLoop:
         self.stats.batches += 1
         finished = {i: False for i in ids}
         n_sampled = {i: 0 for i in ids}
-        pinned = [torch.empty(len(ids), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        on_gpu = getattr(self.engine, "device", torch.device("cpu")).type == "cuda"
+        pinned = [torch.empty(len(ids), dtype=torch.int32, pin_memory=on_gpu) for _ in range(2)]
         flip = 0
 
         def to_host(dev_tokens, order):
@@ -147,18 +150,27 @@ class GenerationLoop:
             buf = pinned[flip][:len(order)]
             flip ^= 1
             buf.copy_(dev_tokens[:len(order)], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-            return buf, ev, list(order)
+            ev = None
+            if on_gpu:
+                ev = torch.cuda.Event()
+                ev.record()
+            # a token sampled when its sequence already fills the context is not taken: the reference's loop ends
+            # on `pos < ctx` before it samples again (src/main.rs:770)
+            at_end = {i for i in order if cache.length(slots[i]) >= cache.max_seq_len}
+            return buf, ev, list(order), at_end
 
-        def resolve(flight, fed_now):
+        def resolve(flight):
             """Host-side decisions on tokens sampled one step ago."""
-            buf, ev, order = flight
-            ev.synchronize()
+            buf, ev, order, at_end = flight
+            if ev is not None:
+                ev.synchronize()
             for i, tok in zip(order, buf.tolist()):
                 if finished[i]:
                     continue                                  # ended earlier; this token came from the extra step
                 res = results[i]
+                if i in at_end:
+                    res.finish_reason, finished[i] = "capacity", True
+                    continue
                 self.stats.gen_tokens += 1
                 if tok in self.stop:                          # counted, not kept, not fed (src/main.rs:772-776)
                     res.finish_reason, res.stopped_on, finished[i] = "stop", tok, True
@@ -168,8 +180,31 @@ class GenerationLoop:
                     self.on_token(i, tok)
                 if len(res.tokens) >= max_new:
                     res.finish_reason, finished[i] = "length", True
-                elif i not in fed_now:
-                    res.finish_reason, finished[i] = "capacity", True     # the reference's `pos < ctx` (src/main.rs:770)
+
+        def eligible(order):
+            return [i for i in order if not finished[i] and n_sampled[i] < max_new
+                    and cache.length(slots[i]) + 1 <= cache.max_seq_len]
+
+        runner = None
+
+        def launch(feed, order, cur):
+            """One more token for every sequence of `feed`, taken from the device copy of the last picks."""
+            nonlocal runner
+            if len(feed) == len(order):
+                tok_in = cur
+            else:
+                pos = {i: r for r, i in enumerate(order)}
+                rows = torch.tensor([pos[i] for i in feed], dtype=torch.int64).to(cur.device, non_blocking=True)
+                tok_in = cur.index_select(0, rows)
+            want = [slots[i] for i in feed]
+            if runner is None or runner.slots != want:
+                runner = self.engine.decoder(want)
+            logits = runner.forward(dev_tokens=tok_in)
+            self.stats.steps += 1
+            nxt = self.sampler.pick_device(logits, feed)
+            for i in feed:
+                n_sampled[i] += 1
+            return nxt, to_host(nxt, feed)
 
         try:
             t0 = time.perf_counter()
@@ -184,35 +219,35 @@ class GenerationLoop:
                 n_sampled[i] = 1
             flight = to_host(cur, order)
             self.stats.prompt_tokens += sum(len(prompts[i]) for i in order)
-            torch.cuda.current_stream().synchronize()
+            if on_gpu:
+                torch.cuda.current_stream().synchronize()
             t1 = time.perf_counter()
             self.stats.prompt_secs += t1 - t0
-            runner = None
             while True:
-                feed = [i for i in order if not finished[i] and n_sampled[i] < max_new
-                        and cache.length(slots[i]) + 1 <= cache.max_seq_len]
+                feed = eligible(order)
                 nxt = nxt_flight = None
+                resolved = False
                 if feed:
-                    if len(feed) == len(order):
-                        tok_in = cur
-                    else:
-                        pos = {i: r for r, i in enumerate(order)}
-                        rows = torch.tensor([pos[i] for i in feed], dtype=torch.int64).to(cur.device, non_blocking=True)
-                        tok_in = cur.index_select(0, rows)
-                    want = [slots[i] for i in feed]
-                    if runner is None or runner.slots != want:
-                        runner = self.engine.decoder(want)
                     try:
-                        logits = runner.forward(dev_tokens=tok_in)
+                        nxt, nxt_flight = launch(feed, order, cur)
                     except CacheFullError:
+                        # The pool is full.  The host learns of a sequence's end one step late: learn it now, and try once
+                        # more without those that have ended (the loop that decides at once would not have fed them).
+                        resolve(flight)
+                        resolved = True
+                        again = eligible(feed)
                         feed = []
-                    else:
-                        self.stats.steps += 1
-                        nxt = self.sampler.pick_device(logits, feed)
-                        for i in feed:
-                            n_sampled[i] += 1
-                        nxt_flight = to_host(nxt, feed)
-                resolve(flight, set(feed))
+                        if again:
+                            try:
+                                nxt, nxt_flight = launch(again, order, cur)
+                                feed = again
+                            except CacheFullError:
+                                pass
+                if not resolved:
+                    resolve(flight)
+                for i in order:
+                    if not finished[i] and i not in feed:
+                        results[i].finish_reason, finished[i] = "capacity", True     # no room to go on (src/main.rs:770)
                 if not feed:
                     break
                 order, cur, flight = feed, nxt, nxt_flight
@@ -242,6 +277,9 @@ class GenerationLoop:
                 feed = []
                 for i, tok in zip(live, picked):
                     res = results[i]
+                    if cache.length(slots[i]) >= cache.max_seq_len:
+                        res.finish_reason = "capacity"        # the reference's `pos < ctx` ends its loop before it samples again (src/main.rs:770)
+                        continue
                     self.stats.gen_tokens += 1
                     if tok in self.stop:                      # counted, not kept, not fed (src/main.rs:772-776)
                         res.finish_reason, res.stopped_on = "stop", tok
@@ -251,10 +289,8 @@ class GenerationLoop:
                         self.on_token(i, tok)
                     if len(res.tokens) >= max_new:
                         res.finish_reason = "length"
-                    elif cache.length(slots[i]) + 1 > cache.max_seq_len:
-                        res.finish_reason = "capacity"        # the reference's `pos < ctx` (src/main.rs:770)
                     else:
-                        feed.append((i, tok))
+                        feed.append((i, tok))                 # the context has room: checked above
                 if not feed:
                     break
                 try:

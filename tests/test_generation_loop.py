@@ -96,10 +96,13 @@ def test_last_token_is_not_fed_and_counts():
 
 
 def test_capacity_ends_a_sequence():
+    """The reference's loop runs `while pos < ctx` and so yields ctx - prompt tokens: the logits after the last
+    position of a full context are not sampled (src/main.rs:770)."""
     eng = FakeEngine(max_seq_len=8)
     loop = GenerationLoop(eng, ArgmaxSampler(), batch_size=2)
     res = loop.run([[1, 2, 3, 4, 5]], max_new=50)
-    assert res[0].finish_reason == "capacity" and len(res[0].tokens) == 8 - 5 + 1
+    assert res[0].finish_reason == "capacity" and res[0].tokens == expected([1, 2, 3, 4, 5], 8 - 5)[0]
+    assert loop.stats.gen_tokens == 3
     with pytest.raises(ValueError):
         loop.run([[1] * 8], max_new=2)                    # the prompt must leave room (src/main.rs:706)
     with pytest.raises(ValueError):
@@ -138,3 +141,64 @@ def test_prompts_read_in_several_steps():
     prompt_steps = [c for c in eng.calls if any(n > 1 for _, n in c)]
     assert all(sum(n for _, n in c) <= 16 for c in prompt_steps) and len(prompt_steps) == 3
     assert [n for c in prompt_steps for s, n in c if s == 0] == [16, 14]       # request 0 in two pieces
+
+
+# ---- the loop that looks at tokens one step late takes the same decisions -------------------------------------
+class FakeRunner:
+    def __init__(self, eng, slots):
+        self.eng, self.slots = eng, list(slots)
+
+    def forward(self, tokens=None, dev_tokens=None):
+        toks = dev_tokens.tolist() if tokens is None else list(tokens)
+        from ghost_infer_b200.engine.step import StepEntry
+        return self.eng.step([StepEntry(s, [int(t)], [0]) for s, t in zip(self.slots, toks)])
+
+
+class PipelinedFakeEngine(FakeEngine):
+    device = torch.device("cpu")
+
+    def decoder(self, slots, use_graph=True):
+        return FakeRunner(self, slots)
+
+
+class DeviceArgmaxSampler(ArgmaxSampler):
+    def pick_device(self, logits, ids):
+        return logits.argmax(-1).to(torch.int32)
+
+
+def run_both(prompts, max_new, stop=(), **kw):
+    out = []
+    for eng, sampler in ((FakeEngine(**kw), ArgmaxSampler()), (PipelinedFakeEngine(**kw), DeviceArgmaxSampler())):
+        loop = GenerationLoop(eng, sampler, stop_token_ids=stop, batch_size=8)
+        res = loop.run(prompts, max_new=max_new)
+        out.append([(r.tokens, r.finish_reason, r.stopped_on) for r in res])
+        assert eng.cache.free_pages == eng.cache.n_pages and eng.cache.slots.free_slots == eng.cache.max_slots
+        assert loop.stats.gen_tokens == sum(len(r.tokens) + (r.finish_reason == "stop") for r in res)
+    return out
+
+
+def test_both_loops_agree_on_stops_lengths_and_the_context_s_end():
+    prompts = [[1, 2, 3], [4], [20, 21], [7] * 5]
+    free = [expected(p, 9)[0] for p in prompts]
+    stop = {free[1][2], free[2][5]}
+    simple, late = run_both(prompts, 9, stop=stop)
+    assert simple == late
+    assert [(r[0], r[1], r[2]) for r in simple] == [expected(p, 9, stop) for p in prompts]
+    assert simple[1][1] == "stop" and simple[2][1] == "stop"
+    simple, late = run_both([[1, 2, 3, 4, 5], [9, 9]], 50, max_seq_len=8)
+    assert simple == late and [len(r[0]) for r in simple] == [3, 6] and all(r[1] == "capacity" for r in simple)
+
+
+def test_both_loops_agree_when_the_pool_runs_full():
+    """Three pages in all.  Two sequences of 60 tokens hold one page each and want a second one four steps on; only one
+    more page is free, so the step that would take both new pages is refused.  A sequence that stops right then is
+    known to the loop that looks at tokens at once, and late to the other, which must learn of it before it gives up."""
+    prompts = [[1] * 60, [2] * 60]
+    free = [expected(p, 12)[0] for p in prompts]
+    # nobody stops: the step at length 65 finds one free page for two sequences; both end with "capacity"
+    simple, late = run_both(prompts, 12, max_tokens=64 * 3)
+    assert simple == late and all(r[1] == "capacity" and len(r[0]) == 5 for r in simple)
+    # request 0 stops on the very token whose feeding would need the page: the other goes on and reaches its length
+    simple, late = run_both(prompts, 12, stop={free[0][4]}, max_tokens=64 * 3)
+    assert simple == late
+    assert simple[0][1] == "stop" and len(simple[0][0]) == 4 and simple[1][1] == "length" and len(simple[1][0]) == 12
