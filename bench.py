@@ -5,7 +5,10 @@ Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 from 2,04
 time over `--steps` decode steps, sampling included); `e2e` is the same through the Python entry point
 with host tokens in and out; `prefill` is one 2,048-token prompt; `points` holds decode at batch 1 and 64;
 `roofline` relates the decode step's bytes (every weight once, plus the cache of the live requests) to the
-measured copy bandwidth.  With --gpus N > 1 it says that this library runs on one GPU and exits with 2.
+measured copy bandwidth; `workloads` holds the baseline's other two shapes (Llama-3.2-1B: batch 64 with unequal
+prompts; Llama-3.2-3B: batch 8 with 16,384-token prompts) run end to end through the entry point, each with its
+own bytes per step and roofline fraction; `clocks_points` holds the SM clock seen during each timed point.
+With --gpus N > 1 it says that this library runs on one GPU and exits with 2.
 """
 import argparse
 import json
@@ -50,33 +53,71 @@ WORKLOADS = {
 }
 
 
-def run_workload(key, args):
-    """One of the other baseline workloads, end to end through the Python entry point; one JSON line."""
+def measure_workload(key, new_tokens=None, clocks=None, no_pdl=False):
+    """One of the other baseline workloads, end to end through the Python entry point (host token ids in and out,
+    sampling included); returns its record."""
     import numpy as np
     import torch
     import ghost_infer_b200 as gi
     from ghost_infer_b200.kernels import ops
     w = WORKLOADS[key]
-    ops.set_pdl(not args.no_pdl)
+    cfg = w["config"]
+    ops.set_pdl(not no_pdl)
     rng = np.random.default_rng(0)
     lo, hi = w["prompt"]
     lens = rng.integers(lo, hi + 1, size=w["batch"]).tolist()
-    prompts = [rng.integers(0, 128256, size=n).tolist() for n in lens]
-    max_tokens = sum(((n + w["new"] + 63) // 64) * 64 for n in lens) + 64 * w["batch"]
-    llm = gi.LLM(w["config"], dtype="bfloat16", device="cuda:0", max_tokens=max_tokens, max_slots=w["batch"],
-                 max_seq_len=hi + w["new"] + 64, seed=0)
-    new = w["new"] if args.steps == 64 else max(2, args.steps)
+    prompts = [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in lens]
+    new = new_tokens or w["new"]
+    max_tokens = sum(((n + new + 63) // 64) * 64 for n in lens) + 64 * w["batch"]
+    llm = gi.LLM(cfg, dtype="bfloat16", device="cuda:0", max_tokens=max_tokens, max_slots=w["batch"],
+                 max_seq_len=hi + new + 64, seed=0)
+    kw = dict(temperature=0.0, stop_token_ids=(), batch_size=w["batch"], max_step_tokens=w["step_tokens"])
     # warm-up with the whole batch: the first step of a shape obtains its device memory, which must not be timed
-    llm.generate(prompts, max_new=2, temperature=0.0, stop_token_ids=(), batch_size=w["batch"], max_step_tokens=w["step_tokens"])
+    llm.generate(prompts, max_new=4, **kw)
     torch.cuda.synchronize()
-    llm.generate(prompts, max_new=new, temperature=0.0, stop_token_ids=(), batch_size=w["batch"], max_step_tokens=w["step_tokens"])
+    t0 = time.time()
+    llm.generate(prompts, max_new=new, time_steps_every=8, **kw)
+    t1 = time.time()
     st = llm.last_stats
-    print(json.dumps({
-        "metric": f"{w['name']}: decode tok/s through LLM.generate", "value": round(st.gen_tokens / st.gen_secs, 1),
-        "unit": "tokens/s", "n_gpus": 1, "steps": new, "dtype": "bf16", "impl": "ours", "data": "synthetic",
+    layers = cfg["num_hidden_layers"]
+    nums = model_numbers(cfg, layers)
+    tied = bool(cfg.get("tie_word_embeddings"))
+    weight_bytes = 2 * (layers * nums["linear_params_per_layer"] + nums["head_params"] + nums["norm_params"])
+    steps = new - 1                     # every new token but the first (which the prompt step's logits give) costs a decode step
+    mean_cached = sum(lens) + w["batch"] * (new / 2.0)
+    step_bytes = weight_bytes + mean_cached * nums["kv_bytes_per_token"]
+    ms = st.gen_secs * 1e3 / max(1, steps)
+    pk = peaks()
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    dev_ms = sorted(st.step_ms)
+    rec = {
+        "name": w["name"], "value": round((st.gen_tokens - w["batch"]) / st.gen_secs, 1), "unit": "tokens/s", "ms_per_step": round(ms, 4),
+        "device_ms_per_step_median": round(dev_ms[len(dev_ms) // 2], 4) if dev_ms else None,
+        "steps": steps, "batch": w["batch"], "layers": layers, "layers_of_model": layers, "tied_head": tied,
+        "prompt_tokens": st.prompt_tokens, "prompt_min": min(lens), "prompt_max": max(lens), "new_tokens": new,
+        "bytes_per_step": int(step_bytes),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
         "prefill": {"value": round(st.prompt_tokens / st.prompt_secs, 1), "tokens": st.prompt_tokens, "ms": round(st.prompt_secs * 1e3, 1)},
-        "config": {"model": w["name"], "global_batch": w["batch"], "prompt_min": lo, "prompt_max": hi, "new_tokens": new},
-    }))
+        "through": "LLM.generate: wall clock of the decode loop, host tokens in and out",
+    }
+    if clocks is not None:
+        rec["clocks"] = clocks.window(t0, t1)
+    del llm
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return rec
+
+
+def run_workload(key, args):
+    """`--workload 1b|3b`: that workload alone, as one JSON line."""
+    clocks = ClockSampler()
+    clocks.start()
+    rec = measure_workload(key, None if args.steps == 64 else max(4, args.steps), clocks, args.no_pdl)
+    clocks.stop()
+    print(json.dumps(dict(rec, metric=f"{rec['name']}: decode tok/s through LLM.generate", n_gpus=1, dtype="bf16", impl="ours",
+                          data="synthetic")))
     return 0
 
 
@@ -92,34 +133,70 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the throttle reasons every 20 ms (NVML; nvidia-smi every 100 ms where NVML cannot be
+    loaded) with the wall-clock time of each sample, so that every timed region can be given the samples that fell
+    into it.  Reads only; no setting of the GPU is touched."""
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self):
-        self.rows = []
+        self.rows = []          # (time, sm MHz, max MHz, set of reasons)
         self.proc = None
+        self._stop = threading.Event()
+        self._thread = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(0)
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            masks = [pynvml.nvmlClocksEventReasonHwSlowdown, pynvml.nvmlClocksEventReasonHwThermalSlowdown,
+                     pynvml.nvmlClocksEventReasonSwThermalSlowdown, pynvml.nvmlClocksEventReasonSwPowerCap]
+
+            def loop():
+                while not self._stop.wait(0.02):
+                    try:
+                        sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                        bits = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                    except Exception:
+                        continue
+                    self.rows.append((time.time(), int(sm), int(mx), {n for n, m in zip(self.NAMES, masks) if bits & m}))
+
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            pass
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
+            self._thread = threading.Thread(target=self._read, daemon=True)
+            self._thread.start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            c = [x.strip() for x in line.split(",")]
+            if len(c) >= 6 and c[0].isdigit() and c[1].isdigit():
+                self.rows.append((time.time(), int(c[0]), int(c[1]),
+                                  {n for i, n in enumerate(self.NAMES) if c[2 + i].lower().startswith("active")}))
+
+    def window(self, t0=None, t1=None):
+        """Median SM clock, the highest clock the GPU offers and every reason seen among the samples of [t0, t1]."""
+        rows = [r for r in list(self.rows) if (t0 is None or r[0] >= t0) and (t1 is None or r[0] <= t1)]
+        sm = sorted(r[1] for r in rows)
+        reasons = sorted(set().union(*[r[3] for r in rows])) if rows else []
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max((r[2] for r in rows), default=None),
+                "reasons": reasons, "samples": len(sm)}
 
     def stop(self):
+        self._stop.set()
         if self.proc is not None:
             self.proc.terminate()
-        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
-        mx = max((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), default=None)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+        return self.window()
 
 
 def model_numbers(cfg, layers):
@@ -265,25 +342,35 @@ def main():
         return 0
 
     clocks.start()
-    ms8, launches8, ctx8 = decode_run(8, K, W)
+    windows = {}
+
+    def timed(name, fn):
+        t_a = time.time()
+        out = fn()
+        windows[name] = (t_a, time.time())
+        return out
+
+    ms8, launches8, ctx8 = timed("decode_b8", lambda: decode_run(8, K, W))
     value = 8 * 1000.0 / ms8
     weight_bytes = 2 * (layers * nums["linear_params_per_layer"] + nums["head_params"] + nums["norm_params"])
     step_bytes = weight_bytes + ctx8 * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms8 * 1e-3) / 1e9
 
-    points = {}
+    points, point_steps = {}, max(50, K)
+    point_frac = {}
     if not args.skip_points:
         for b in (1, 64):
-            ms, _, _ = decode_run(b, max(8, K // 2), W)
+            ms, _, ctx = timed(f"decode_b{b}", lambda: decode_run(b, point_steps, W))
             points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+            point_frac[f"decode_b{b}"] = round((weight_bytes + ctx * nums["kv_bytes_per_token"]) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         # the same batch of 8 with the cache's whole length behind it: the last timed step reads 8,192 positions
-        n = max(8, K // 2)
-        ms, _, _ = decode_run(8, n, W, held=CONTEXT - (W + n + 1))
+        ms, _, ctx = timed(f"decode_b8_ctx{CONTEXT}", lambda: decode_run(8, point_steps, W, held=CONTEXT - (W + point_steps + 1)))
         points[f"decode_b8_ctx{CONTEXT}"] = round(8 * 1000.0 / ms, 1)
+        point_frac[f"decode_b8_ctx{CONTEXT}"] = round((weight_bytes + ctx * nums["kv_bytes_per_token"]) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
 
     # prefill: one prompt of 2,048 tokens, logits for its last place
     prompt = rng.integers(0, V, size=PROMPT).tolist()
-    reps = 3
+    reps = 5
 
     def prefill_once():
         s = cache.open_slot()
@@ -291,16 +378,19 @@ def main():
         cache.close_slot(s)
         return out
 
-    for _ in range(3):
-        prefill_once()
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(reps):
-        prefill_once()
-    stop.record()
-    torch.cuda.synchronize()
-    pre_ms = start.elapsed_time(stop) / reps
+    def prefill_timed():
+        for _ in range(3):
+            prefill_once()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(reps):
+            prefill_once()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / reps
+
+    pre_ms = timed("prefill", prefill_timed)
     H, hd = cfg["num_attention_heads"], cfg["head_dim"]
     flops = 2.0 * PROMPT * layers * nums["linear_params_per_layer"] + 2.0 * nums["head_params"] \
         + layers * 4.0 * H * hd * (PROMPT * (PROMPT + 1) / 2)
@@ -308,16 +398,37 @@ def main():
 
     # end to end through the Python entry point: host token ids in, host token ids out, every step
     prompts = [rng.integers(0, V, size=PROMPT).tolist() for _ in range(8)]
-    # at least 128 steps: right after the 16k-token prefill the SM clock is power-capped for some tens of steps
     e2e_new = max(K, 128)
     llm.generate(prompts, max_new=3, temperature=0.0, stop_token_ids=(), batch_size=8)     # warm-up
-    llm.generate(prompts, max_new=e2e_new, temperature=0.0, stop_token_ids=(), batch_size=8)
-    st = llm.last_stats
-    e2e_steps = max(1, st.steps - 1)
+
+    def e2e_run():
+        llm.generate(prompts, max_new=e2e_new, temperature=0.0, stop_token_ids=(), batch_size=8, time_steps_every=8)
+        return llm.last_stats
+
+    st = timed("e2e", e2e_run)
+    dev = [round(x, 4) for x in st.step_ms]
     e2e = {"value": round((st.gen_tokens - 8) / st.gen_secs, 1) if st.gen_secs > 0 else None, "unit": "tokens/s",
            "h2d_bytes_per_step": int(eng.bytes_h2d), "d2h_bytes_per_step": 8 * 4,
+           "ms_per_step_wall": round(st.gen_secs * 1e3 / max(1, e2e_new - 1), 4),
+           # device time per step over stretches of 8 steps (CUDA events in the loop): the first, the median, the last
+           "ms_per_step_device": {"first": dev[0], "median": sorted(dev)[len(dev) // 2], "last": dev[-1], "stretches": len(dev)} if dev else None,
            "note": f"LLM.generate, batch 8, {PROMPT}-token prompts, {e2e_new} new tokens each; wall clock of the decode loop"}
-    clk = clocks.stop()
+
+    # the baseline's other two workloads, each a model of its own: this one's memory goes back first
+    workloads = {}
+    if not args.skip_points and not args.layers:
+        del llm, eng, cache, prefill_once, prefill_timed, e2e_run, decode_run
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        for key in ("1b", "3b"):
+            workloads[key] = measure_workload(key, None, clocks, args.no_pdl)
+    clocks.stop()
+    clk = clocks.window(*windows["decode_b8"])
+    clocks_points = {name: clocks.window(*w) for name, w in windows.items()}
+    for key, rec in workloads.items():
+        clocks_points[f"workload_{key}"] = rec.pop("clocks", None)
+    h2d_bytes = e2e["h2d_bytes_per_step"]
 
     line = {
         "metric": "Llama-3.1-8B bf16 decode tok/s @ batch 8 (2,048-token contexts)", "value": round(value, 1),
@@ -337,7 +448,11 @@ def main():
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
         "points": points,
+        "points_roofline_frac": point_frac,
+        "points_steps": point_steps,
+        "workloads": workloads,
         "clocks": clk,
+        "clocks_points": clocks_points,
     }
     print(json.dumps(line))
     return 0

@@ -43,14 +43,16 @@ class LLM:
     def generate(self, prompts: Sequence[Sequence[int]], max_new: int = 256, temperature: float = 0.7,
                  top_k: int = 40, top_p: float = 0.9, seed: Optional[int] = None,
                  stop_token_ids: Optional[Sequence[int]] = None, batch_size: int = 8,
-                 on_token=None, max_step_tokens: Optional[int] = None) -> List[GenerationResult]:
+                 on_token=None, max_step_tokens: Optional[int] = None,
+                 time_steps_every: Optional[int] = None) -> List[GenerationResult]:
         """Generates for every prompt, `batch_size` at a time, one batch after another.  `max_step_tokens`
-        bounds the prompt tokens a single step carries (long prompts are then read in several steps)."""
+        bounds the prompt tokens a single step carries (long prompts are then read in several steps).
+        `time_steps_every` = n records the device time of every stretch of n decode steps in `last_stats.step_ms`."""
         params = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p, seed=seed)
         sampler = DeviceSampler(params, self.model.rt.device)
         stop = self.stop_token_ids if stop_token_ids is None else stop_token_ids
         loop = GenerationLoop(self.engine, sampler, stop_token_ids=stop, batch_size=batch_size, on_token=on_token,
-                              max_step_tokens=max_step_tokens)
+                              max_step_tokens=max_step_tokens, time_steps_every=time_steps_every)
         results = loop.run(prompts, max_new)
         self.last_stats = loop.stats
         return results

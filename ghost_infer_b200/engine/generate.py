@@ -35,6 +35,9 @@ class GenerationStats:
     gen_secs: float = 0.0
     batches: int = 0
     steps: int = 0
+    # with `time_steps_every` = n: device time per decode step over each stretch of n steps, in milliseconds
+    # (CUDA events on the launching stream, read when a batch ends)
+    step_ms: List[float] = field(default_factory=list)
 
 
 class GenerationLoop:
@@ -44,7 +47,8 @@ class GenerationLoop:
     sampled tokens on the device and looks at them one step late; it takes the same decisions either way."""
 
     def __init__(self, engine, sampler, stop_token_ids: Sequence[int] = (), batch_size: int = 8,
-                 on_token: Optional[Callable[[int, int], None]] = None, max_step_tokens: Optional[int] = None):
+                 on_token: Optional[Callable[[int, int], None]] = None, max_step_tokens: Optional[int] = None,
+                 time_steps_every: Optional[int] = None):
         """`max_step_tokens`: the most prompt tokens one step carries; longer batches of prompts are read in
         several steps that attend to the cache (the reference reads prompts in passes of 1024 tokens,
         src/cuda.rs:8550).  None: all prompts of a batch in one step."""
@@ -53,6 +57,7 @@ class GenerationLoop:
         if max_step_tokens is not None and max_step_tokens < 1:
             raise ValueError("max_step_tokens must be at least 1")
         self.max_step_tokens = max_step_tokens
+        self.time_steps_every = time_steps_every
         self.engine = engine
         self.sampler = sampler
         self.stop = frozenset(int(t) for t in stop_token_ids)
@@ -186,6 +191,7 @@ class GenerationLoop:
                     and cache.length(slots[i]) + 1 <= cache.max_seq_len]
 
         runner = None
+        marks, n_decode = [], [0]
 
         def launch(feed, order, cur):
             """One more token for every sequence of `feed`, taken from the device copy of the last picks."""
@@ -199,6 +205,11 @@ class GenerationLoop:
             want = [slots[i] for i in feed]
             if runner is None or runner.slots != want:
                 runner = self.engine.decoder(want)
+            if on_gpu and self.time_steps_every and n_decode[0] % self.time_steps_every == 0:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((n_decode[0], ev))
+            n_decode[0] += 1
             logits = runner.forward(dev_tokens=tok_in)
             self.stats.steps += 1
             nxt = self.sampler.pick_device(logits, feed)
@@ -252,6 +263,10 @@ class GenerationLoop:
                     break
                 order, cur, flight = feed, nxt, nxt_flight
             self.stats.gen_secs += time.perf_counter() - t1
+            if len(marks) > 1:
+                torch.cuda.current_stream().synchronize()
+                for (a, ea), (b, eb) in zip(marks, marks[1:]):
+                    self.stats.step_ms.append(ea.elapsed_time(eb) / (b - a))
         finally:
             for s in slots.values():
                 cache.close_slot(s)
