@@ -249,6 +249,8 @@ def main():
                     help="run one phase alone and print its time (a short program for a launch list under a profiler; no bench "
                          "line).  timeline: a table of when the streamed products of a decode step start, wait, stream and end")
     ap.add_argument("--batch", type=int, default=8, help="sequences per decode step for --only decode|timeline (the bench line is always batch 8)")
+    ap.add_argument("--shape", default="8b", choices=["8b", "1b", "3b"], help="layer sizes for --only (the bench line is always the 8B shape)")
+    ap.add_argument("--held", type=int, default=PROMPT, help="tokens each sequence holds for --only decode|timeline")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another (no programmatic dependent launch)")
     args = ap.parse_args()
 
@@ -259,6 +261,11 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.tune:
+        from ghost_infer_b200.kernels import ops as _ops
+        for kv in filter(None, args.tune.split(",")):
+            k, v = kv.split("=")
+            _ops.TUNE[k] = type(_ops.TUNE[k])(float(v))
     if args.workload != "8b":
         return run_workload(args.workload, args)
     W = max(3, args.warmup)
@@ -271,10 +278,7 @@ def main():
 
     dev = "cuda:0"
     ops.set_pdl(not args.no_pdl)
-    for kv in filter(None, args.tune.split(",")):
-        k, v = kv.split("=")
-        ops.TUNE[k] = type(ops.TUNE[k])(float(v))
-    cfg = dict(CONFIG_8B)
+    cfg = dict(CONFIG_8B if not (args.only and args.shape != "8b") else WORKLOADS[args.shape]["config"])
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -325,8 +329,9 @@ def main():
     if args.only == "timeline":
         return decode_timeline(ops, decode_run, layers, K, W, args.batch)
     if args.only == "decode":
-        ms, n, _ = decode_run(args.batch, K, W)
-        print(json.dumps({"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": round(ms, 4), "launches_per_step": n // K}))
+        ms, n, _ = decode_run(args.batch, K, W, held=args.held)
+        print(json.dumps({"only": "decode", "shape": args.shape, "layers": layers, "batch": args.batch, "held": args.held,
+                          "ms_per_step": round(ms, 4), "launches_per_step": n // K}))
         return 0
     if args.only == "prefill":
         prompt = rng.integers(0, V, size=PROMPT).tolist()

@@ -198,6 +198,14 @@ int gi_attn_decode_tc_ex(void* out, long ldo, float* part_o, float* part_ml, con
                          const void* vcache, const int* block_table, int max_pages, const int* seq_slots,
                          const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd, float scale, int window,
                          int n_splits, int tile_keys, void* stream);
+// the same with the slices merged inside the kernel by the block that finishes last (counters: one int per sequence x
+// kv head x chunk of 16 heads, zero before the first use; nullptr: merged by a second kernel), and, with own_tiles > 0,
+// slices of that many tiles of each sequence's own span instead of n_splits equal ones
+int gi_attn_decode_tc_merged(void* out, long ldo, float* part_o, float* part_ml, int* counters, int n_counters, const void* q,
+                             long ldq, const void* kcache, const void* vcache, const int* block_table, int max_pages,
+                             const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd, float scale,
+                             int window, int n_splits, int own_tiles, int tile_keys, int stages, void* stream);
+// stages: depth of each warp's ring of tiles, 2 to 4 (0: the default for the head size)
 int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const float* part_ml, int n_seqs, int n_heads,
                     int hd, int n_splits, void* stream);
 

@@ -8,7 +8,12 @@
 // and the running rescale are 32-bit.  Each of the 4 warps walks its own tiles of 16 or 32 keys; keys and values
 // arrive by cp.async into a per-warp ring of shared-memory stages (16-byte chunks, XOR-swizzled for
 // ldmatrix), so the next tiles are in flight while one is used.  Warps are merged through shared memory in
-// warp order; slices are merged by the combine kernel in slice order.
+// warp order.  A context is cut either into a fixed number of equal slices (few sequences: one wave of blocks) or
+// into slices of a fixed number of tiles counted from the start of the sequence's own span (many or unequal
+// sequences: every block has the same work, short sequences use fewer blocks, and a launch's other slices leave at
+// once).  Slices are merged in slice order: by the block of a (sequence, kv head) that finishes last, which an atomic
+// counter tells (nobody waits; the role of the reference's attention_combine, src/cuda.rs:2806-2839), or, when the
+// caller gives no counters, by the combine kernel.
 #include <math.h>
 
 #include <mutex>
@@ -27,7 +32,7 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
                       const __nv_bfloat16* q /* written by the kernel before: see gi::pdl_wait */, long ldq, const __nv_bfloat16* __restrict__ kcache,
                       const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_pages,
                       const int* __restrict__ seq_slots, const int* __restrict__ seq_lens, int n_heads, int n_kv,
-                      float scale, int window, int n_splits) {
+                      float scale, int window, int n_splits, int own_tiles, int* __restrict__ counters) {
   constexpr int CH = HD / 8;                     // 16-byte chunks per row
   constexpr int TILE_BYTES = KT * HD * 2;        // one K or V tile
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;    // K then V
@@ -54,8 +59,22 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
   if (window > 0) t_first = max(0, len - window);
   const int t_base = (t_first / KT) * KT;
   const int tiles = len > t_base ? (len - t_base + KT - 1) / KT : 0;
-  const int per = (tiles + n_splits - 1) / n_splits;
+  // own_tiles > 0: a slice is that many tiles of the sequence's own span; else the span is cut into n_splits equal slices
+  const int per = own_tiles > 0 ? own_tiles : (tiles + n_splits - 1) / n_splits;
+  const int used = per > 0 ? max(1, (tiles + per - 1) / per) : 1;      // slices of this sequence that hold keys
   const int tile_lo = sp * per, tile_hi = min(tiles, tile_lo + per);
+  if (sp >= used) {
+    // nothing of this sequence lies in this slice.  With counters the merging block reads the `used` first slices
+    // only; without, the combine kernel reads every slice of the launch and must find this one marked empty.
+    if (counters == nullptr && n_splits > 1) {
+      for (int r = threadIdx.x; r < gcount; r += WARPS * 32) {
+        const size_t pi = ((size_t)b * n_heads + h0 + r) * n_splits + sp;
+        part_ml[pi * 2] = -INFINITY;
+        part_ml[pi * 2 + 1] = 0.f;
+      }
+    }
+    return;
+  }
 
   unsigned char* my_ring = ring + (size_t)warp * STAGES * STAGE_BYTES;
   const float sl2 = scale * 1.4426950408889634f;
@@ -249,7 +268,7 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
       }
     }
     const int h = h0 + r;
-    if (n_splits == 1) {
+    if (n_splits == 1 || (used == 1 && counters != nullptr)) {
       out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(tot > 0.f ? val / tot : 0.f);
     } else {
       const size_t pi = ((size_t)b * n_heads + h) * n_splits + sp;
@@ -260,12 +279,89 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
       }
     }
   }
+  if (counters == nullptr || used == 1 || n_splits == 1) return;
+
+  // The block of this (sequence, kv head, head chunk) that arrives last merges the slices, in slice order and from
+  // memory (its own slice too), so the result does not depend on which block that is.  Nobody waits for anybody.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* c = counters + (size_t)b * gridDim.y + blockIdx.y;
+    const int seen = atomicAdd(c, 1);
+    s_last = (seen == used - 1);
+    if (s_last) *c = 0;                                   // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // maxima and sums of every slice of the block's heads into shared memory (the ring is free by now): one round of
+  // loads for all of them; then each head's largest maximum and every slice's weight exp(m_s - m)
+  float* Wt = reinterpret_cast<float*>(ring);             // [gcount][used] weights, then [gcount] totals
+  float* Tot = Wt + 16 * n_splits;
+  if (32 * n_splits + 16 <= (int)(WARPS * STAGES * STAGE_BYTES / sizeof(float))) {
+    for (int i = tid; i < gcount * used; i += WARPS * 32) {
+      const int r = i / used, sl = i % used;
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + ((size_t)b * n_heads + h0 + r) * n_splits + sl);
+      Wt[r * n_splits + sl] = ml.x;
+      Wt[16 * n_splits + 16 + r * n_splits + sl] = ml.y;                  // sums, behind the totals
+    }
+    __syncthreads();
+    if (tid < gcount) {
+      float mm = -INFINITY;
+      for (int sl = 0; sl < used; ++sl) mm = fmaxf(mm, Wt[tid * n_splits + sl]);
+      float tot = 0.f;
+      for (int sl = 0; sl < used; ++sl) {
+        const float m = Wt[tid * n_splits + sl];
+        const float w = (m == -INFINITY || mm == -INFINITY) ? 0.f : expf(m - mm);
+        Wt[tid * n_splits + sl] = w;
+        tot += Wt[16 * n_splits + 16 + tid * n_splits + sl] * w;
+      }
+      Tot[tid] = tot;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < gcount * HD; idx += WARPS * 32) {
+      const int r = idx / HD, d = idx % HD;
+      const size_t p0 = ((size_t)b * n_heads + h0 + r) * n_splits;
+      float val = 0.f;
+      for (int s0 = 0; s0 < used; s0 += 8) {              // eight slices' loads together
+        float o8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o8[j] = (s0 + j < used) ? __ldcg(part_o + (p0 + s0 + j) * HD + d) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (s0 + j < used) val += o8[j] * Wt[r * n_splits + s0 + j];
+      }
+      const float tot = Tot[r];
+      out[(size_t)b * ldo + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(tot > 0.f ? val / tot : 0.f);
+    }
+    return;
+  }
+  for (int idx = tid; idx < gcount * HD; idx += WARPS * 32) {           // more slices than the table holds: the plain way
+    const int r = idx / HD, d = idx % HD;
+    const int h = h0 + r;
+    const size_t p0 = ((size_t)b * n_heads + h) * n_splits;
+    const float2* ml = reinterpret_cast<const float2*>(part_ml) + p0;
+    float mm = -INFINITY;
+    for (int sl = 0; sl < used; ++sl) mm = fmaxf(mm, __ldcg(ml + sl).x);
+    float tot = 0.f, val = 0.f;
+    if (mm != -INFINITY) {
+      for (int sl = 0; sl < used; ++sl) {
+        const float2 m = __ldcg(ml + sl);
+        if (m.x == -INFINITY) continue;
+        const float w = expf(m.x - mm);
+        tot += m.y * w;
+        val += __ldcg(part_o + (p0 + sl) * HD + d) * w;
+      }
+    }
+    out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(tot > 0.f ? val / tot : 0.f);
+  }
 }
 
 template <int HD, int KT, int STAGES>
 int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, float* pml, const __nv_bfloat16* q, long ldq,
            const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int max_pages, const int* slots, const int* lens,
-           int H, int KV, float scale, int window, int n_splits) {
+           int H, int KV, float scale, int window, int n_splits, int own_tiles, int* counters) {
   constexpr size_t ring = (size_t)WARPS * STAGES * 2 * KT * HD * 2;
   constexpr size_t merge = (size_t)(WARPS * 16 * (HD + 8) + 2 * WARPS * 16) * sizeof(float);
   constexpr size_t smem = 16 * HD * 2 + (ring > merge ? ring : merge);
@@ -278,7 +374,7 @@ int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, f
     if (dev >= 0) configured[dev] = true;
   }
   return gi::check(gi::launch(kern, grid, dim3(WARPS * 32), smem, s, out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV,
-                              scale, window, n_splits), "attention decode (tensor cores)");
+                              scale, window, n_splits, own_tiles, counters), "attention decode (tensor cores)");
 }
 
 }  // namespace
@@ -291,6 +387,11 @@ extern "C" int gi_attn_decode_tc_ex(void* out, long ldo, float* part_o, float* p
                                     const void* kcache, const void* vcache, const int* block_table, int max_pages,
                                     const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
                                     float scale, int window, int n_splits, int tile_keys, void* stream);
+extern "C" int gi_attn_decode_tc_merged(void* out, long ldo, float* part_o, float* part_ml, int* counters, int n_counters,
+                                        const void* q, long ldq, const void* kcache, const void* vcache,
+                                        const int* block_table, int max_pages, const int* seq_slots, const int* seq_lens,
+                                        int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
+                                        int own_tiles, int tile_keys, int stages, void* stream);
 
 extern "C" int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq,
                                  const void* kcache, const void* vcache, const int* block_table, int max_pages,
@@ -305,7 +406,23 @@ extern "C" int gi_attn_decode_tc_ex(void* out, long ldo, float* part_o, float* p
                                     const void* kcache, const void* vcache, const int* block_table, int max_pages,
                                     const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
                                     float scale, int window, int n_splits, int tile_keys, void* stream) {
+  return gi_attn_decode_tc_merged(out, ldo, part_o, part_ml, nullptr, 0, q, ldq, kcache, vcache, block_table, max_pages, seq_slots,
+                                  seq_lens, n_seqs, n_heads, n_kv, hd, scale, window, n_splits, 0, tile_keys, 0, stream);
+}
+
+// The same with the merge of the slices inside the kernel.  counters: one int per (sequence, kv head, chunk of 16
+// heads), zero before the first use (the kernel leaves them zero); nullptr: the slices are merged by a second kernel.
+// own_tiles > 0: slice s of a sequence holds tiles [s * own_tiles, (s + 1) * own_tiles) of `tile_keys` keys of its own
+// span, whatever n_splits is (which must cover the longest span); 0: each span is cut into n_splits equal slices.
+// stages: depth of each warp's ring of tiles (2, 3 or 4; 0: 3 at head size 128, 4 at head size 64).  Fewer stages
+// mean less shared memory per block and so more blocks per SM.
+extern "C" int gi_attn_decode_tc_merged(void* out, long ldo, float* part_o, float* part_ml, int* counters, int n_counters,
+                                        const void* q, long ldq, const void* kcache, const void* vcache,
+                                        const int* block_table, int max_pages, const int* seq_slots, const int* seq_lens,
+                                        int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
+                                        int own_tiles, int tile_keys, int stages, void* stream) {
   if (n_seqs <= 0) return GI_OK;
+  if (own_tiles < 0) return gi::fail(GI_ERR_ARG, "attention: tiles per slice cannot be negative");
   if (tile_keys != 16 && tile_keys != 32) return gi::fail(GI_ERR_ARG, "attention decode (tensor cores): tiles of %d keys, 16 or 32", tile_keys);
   if (hd != 64 && hd != 128) return gi::fail(GI_ERR_UNSUPPORTED, "attention decode (tensor cores): head size %d, only 64 and 128", hd);
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
@@ -317,20 +434,27 @@ extern "C" int gi_attn_decode_tc_ex(void* out, long ldo, float* part_o, float* p
   const int group = n_heads / n_kv;
   const int chunks = (group + 15) / 16;
   if ((long)n_kv * chunks > 65535 || n_seqs > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "attention: more than 65535 sequences or kv heads in one launch");
+  if (counters != nullptr && (long)n_seqs * n_kv * chunks > n_counters)
+    return gi::fail(GI_ERR_ARG, "attention: %ld counters are needed for the merge, %d were given", (long)n_seqs * n_kv * chunks, n_counters);
   dim3 grid(n_splits, n_kv * chunks, n_seqs);
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
 #define GI_DECODE_TC(HD_, KT_, ST_)                                                                                          \
   rc = launch<HD_, KT_, ST_>(grid, s, (__nv_bfloat16*)out, ldo, part_o, part_ml, (const __nv_bfloat16*)q, ldq,               \
                              (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table, max_pages, seq_slots, \
-                             seq_lens, n_heads, n_kv, scale, window, n_splits)
+                             seq_lens, n_heads, n_kv, scale, window, n_splits, own_tiles, counters)
+  if (stages == 0) stages = hd == 128 ? 3 : 4;
+  if (stages < 2 || stages > 4) return gi::fail(GI_ERR_ARG, "attention decode (tensor cores): rings of %d stages, 2 to 4", stages);
   if (hd == 128 && tile_keys == 32) GI_DECODE_TC(128, 32, 3);
+  else if (hd == 128 && stages == 2) GI_DECODE_TC(128, 16, 2);
   else if (hd == 128) GI_DECODE_TC(128, 16, 3);
   else if (tile_keys == 32) GI_DECODE_TC(64, 32, 4);
+  else if (stages == 2) GI_DECODE_TC(64, 16, 2);
+  else if (stages == 3) GI_DECODE_TC(64, 16, 3);
   else GI_DECODE_TC(64, 16, 4);
 #undef GI_DECODE_TC
   if (rc != GI_OK) return rc;
-  if (n_splits > 1) return gi_attn_combine(out, ldo, GI_BF16, part_o, part_ml, n_seqs, n_heads, hd, n_splits, stream);
+  if (n_splits > 1 && counters == nullptr) return gi_attn_combine(out, ldo, GI_BF16, part_o, part_ml, n_seqs, n_heads, hd, n_splits, stream);
   return GI_OK;
 }
 

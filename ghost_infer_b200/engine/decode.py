@@ -84,10 +84,16 @@ class DecodeRunner:
         self.use_graph = use_graph and engine.device.type == "cuda" and not engine.plans_on_host
         self.rows = _bucket_rows(self.n) if self.use_graph else self.n
         self._g: Optional[_DecodeGraph] = None
+        self._plans: Dict[int, dict] = {}
 
-    def _graph_for(self, max_len: int) -> _DecodeGraph:
+    def _graph_for(self, lens: Sequence[int]) -> _DecodeGraph:
+        """The recording for these rows and this length bucket.  The mixers' plans are asked for once per bucket, with
+        the lengths the sequences have then; they hold until a sequence outgrows the bucket."""
         eng = self.engine
-        plans = eng.decode_plans(self.rows, _bucket_len(max_len))
+        bucket = _bucket_len(max(lens) + 1)
+        plans = self._plans.get(bucket)
+        if plans is None:
+            plans = self._plans[bucket] = eng.decode_plans(self.rows, bucket, [n + 1 for n in lens])
         key = (self.rows, self.use_graph, tuple(repr(plans[id(m)]) for m in eng._mixers))
         g = eng._decode_graphs.get(key)
         if g is None:
@@ -106,7 +112,7 @@ class DecodeRunner:
         lens = [cache.length(s) for s in self.slots]
         cache.reserve([(s, l + 1) for s, l in zip(self.slots, lens)])
         cache.sync_tables()
-        g = self._graph_for(max(lens) + 1)
+        g = self._graph_for(lens)
         self._g = g
         if g.host_event is not None:
             g.host_event.synchronize()

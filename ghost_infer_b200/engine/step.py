@@ -58,7 +58,12 @@ class StepContext:
         """The mixer's plan for this step: the recorded one in a replayed step, else worked out for the step."""
         if self.fixed_plans is not None and id(mixer) in self.fixed_plans:
             return self.fixed_plans[id(mixer)]
-        return mixer.decode_plan(self.n_seqs, self.max_kv_len, self.sm_count) if self.is_decode else None
+        if not self.is_decode:
+            return None
+        lens = None
+        if self._host_pos0 is not None and len(self._host_pos0) == self.n_seqs:
+            lens = [p + n for p, n in zip(self._host_pos0, self._host_q_lens)]
+        return mixer.decode_plan(self.n_seqs, self.max_kv_len, self.sm_count, lens)
 
     def _host(self, name: str):
         v = getattr(self, name)
@@ -226,10 +231,10 @@ class Engine:
         ops.drop_pending(x)
         return model.head.forward(h)
 
-    def decode_plans(self, n_seqs: int, max_kv_len: int) -> Dict[int, Any]:
+    def decode_plans(self, n_seqs: int, max_kv_len: int, kv_lens=None) -> Dict[int, Any]:
         """What every mixer plans for one-token steps of this shape: id(mixer) -> plan.  A recorded step is keyed
         by these plans, so a mixer decides itself how its work is cut and when a new recording is needed."""
-        return {id(m): m.decode_plan(n_seqs, max_kv_len, self._sm_count) for m in self._mixers}
+        return {id(m): m.decode_plan(n_seqs, max_kv_len, self._sm_count, kv_lens) for m in self._mixers}
 
     def decoder(self, slots: Sequence[int], use_graph: bool = True):
         """A runner of one-token steps for these slots (see engine.decode.DecodeRunner)."""

@@ -59,6 +59,11 @@ def main() -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--own-tiles", type=int, default=0, help="attn_decode: slices of that many tiles of each sequence's own span")
+    ap.add_argument("--tile-keys", type=int, default=0, help="attn_decode: 16 or 32 keys per tile (default: the engine's)")
+    ap.add_argument("--merge-inside", type=int, default=-1, help="attn_decode: 1 = slices merged by the last block, 0 = by a second kernel")
+    ap.add_argument("--stages", type=int, default=0, help="attn_decode: depth of each warp's ring of tiles (2 to 4)")
+    ap.add_argument("--shortest", type=int, default=0, help="attn_decode: lengths uniform in [shortest, context] instead of all equal")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--pdl", action="store_true")
@@ -94,18 +99,27 @@ def main() -> int:
         if args.kernel == "attn_decode":
             q = torch.randn(B, (H + 2 * KV) * hd, device=dev, dtype=bf)
             lens = torch.full((B,), S, dtype=torch.int32, device=dev)
+            if args.shortest:
+                lens = torch.randint(args.shortest, S + 1, (B,), generator=torch.Generator().manual_seed(0)).to(torch.int32).to(dev)
             # the engine's choice (StepContext.decode_splits): one wave of as many blocks as an SM holds, slices of at least 128 keys
             sms = torch.cuda.get_device_properties(0).multi_processor_count
             per_sm = ops.attn_decode_blocks_per_sm(hd, True)
-            splits = args.splits or max(1, min(32, int(per_sm * sms) // max(1, B * KV * ((H // KV + 15) // 16)), S // 128))
+            splits, own = ops.attn_decode_plan(B, S, sms, H, KV, hd, None, bf, lens.tolist())
+            if args.splits or args.own_tiles:
+                splits, own = args.splits or 1, args.own_tiles
+            tile = args.tile_keys or int(ops.TUNE["attn_tile_keys"])
+            if own:
+                splits = max(splits, (S + own * tile - 1) // (own * tile))
+            inside = None if args.merge_inside < 0 else bool(args.merge_inside)
             o = torch.empty(B, H * hd, device=dev, dtype=bf)
             po = torch.empty(B * H * splits * hd, device=dev)
             pml = torch.empty(B * H * splits * 2, device=dev)
-            us = _time(lambda i: ops.attn_decode_tc(q, kc, vc, tables[i], slots, lens, B, H, KV, hd, scale, None, splits, o, po, pml),
+            us = _time(lambda i: ops.attn_decode_tc(q, kc, vc, tables[i], slots, lens, B, H, KV, hd, scale, None, splits, o, po, pml,
+                                                    tile_keys=tile, own_tiles=own, merge_inside=inside, stages=args.stages or None),
                        n_sets, args.iters, args.warmup)
-            nbytes = B * S * KV * hd * 2 * 2
-            out.update(shape=[B, S, H, KV, hd], splits=splits, us=round(us, 2), gbs=round(nbytes / us / 1e3, 1),
-                       frac_hbm=round(nbytes / us / 1e3 / hbm, 3))
+            nbytes = int(lens.sum()) * KV * hd * 2 * 2
+            out.update(shape=[B, S, H, KV, hd], shortest=args.shortest, splits=splits, own_tiles=own, tile_keys=tile,
+                       merge_inside=inside, stages=args.stages, us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), frac_hbm=round(nbytes / us / 1e3 / hbm, 3))
         else:
             q = torch.randn(B * S, (H + 2 * KV) * hd, device=dev, dtype=bf)
             cu = (torch.arange(B + 1, dtype=torch.int32, device=dev) * S)

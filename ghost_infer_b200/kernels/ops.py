@@ -63,6 +63,7 @@ def _bind():
         "gi_attn_prefill_t5_status": [P],
         "gi_attn_decode_tc": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_attn_decode_tc_ex": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P],
+        "gi_attn_decode_tc_merged": [P, L, P, P, P, I, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
     }
     for name, argtypes in sigs.items():
@@ -386,7 +387,8 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 
 
 # Choices measured on a B200; benchmarks may override them to try alternatives.
-TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16}
+TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16,
+        "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -730,12 +732,29 @@ def attn_decode_tc_ok(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> b
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
 
 
+_ATTN_COUNTERS = 1 << 16
+_attn_counters: Dict[int, torch.Tensor] = {}
+
+
+def _attn_merge_counters(device: torch.device) -> torch.Tensor:
+    """Arrival counters of the decode attention's merge, one set per device, allocated once (their address is baked
+    into recorded steps) and zero between launches (the kernel leaves them so)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _attn_counters:
+        _attn_counters[key] = torch.zeros(_ATTN_COUNTERS, dtype=torch.int32, device=device)
+    return _attn_counters[key]
+
+
 def attn_decode_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                    seq_slots: torch.Tensor, seq_lens: torch.Tensor, n_seqs: int, n_heads: int, n_kv: int,
                    head_dim: int, scale: float, window: Optional[int], n_splits: int, out: torch.Tensor,
                    part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                   tile_keys: Optional[int] = None) -> torch.Tensor:
-    """`tile_keys`: 32 (one block per SM, deep rings) or 16 (two blocks per SM); default TUNE["attn_tile_keys"]."""
+                   tile_keys: Optional[int] = None, own_tiles: int = 0, merge_inside: Optional[bool] = None,
+                   stages: Optional[int] = None) -> torch.Tensor:
+    """`tile_keys`: 32 (one block per SM, deep rings) or 16 (two blocks per SM); default TUNE["attn_tile_keys"].
+    `own_tiles` > 0: slices of that many tiles of each sequence's own span (`n_splits` must then cover the longest
+    sequence); 0: every span is cut into `n_splits` equal slices.  `merge_inside`: the slices are merged by the block
+    that finishes last instead of by a second kernel (default TUNE["attn_merge_inside"])."""
     lib = _bind()
     _cuda(q, "queries")
     ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
@@ -748,12 +767,23 @@ def attn_decode_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
             raise KernelError("attention scratch for outputs is too small")
         if part_ml.dtype != torch.float32 or part_ml.numel() < n_seqs * n_heads * n_splits * 2:
             raise KernelError("attention scratch for maxima and sums is too small")
-    _check(lib, lib.gi_attn_decode_tc_ex(
+    tile_keys = int(tile_keys or TUNE["attn_tile_keys"])
+    if own_tiles and n_splits * own_tiles * tile_keys < 1:
+        raise KernelError("attention: slices of no keys")
+    chunks = (n_heads // max(1, n_kv) + 15) // 16
+    inside = TUNE["attn_merge_inside"] if merge_inside is None else merge_inside
+    counters = None
+    if inside and n_splits > 1 and n_seqs * n_kv * chunks <= _ATTN_COUNTERS:
+        counters = _attn_merge_counters(q.device)
+    _check(lib, lib.gi_attn_decode_tc_merged(
         out.data_ptr(), ldo, part_o.data_ptr() if part_o is not None else None,
-        part_ml.data_ptr() if part_ml is not None else None, q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(),
+        part_ml.data_ptr() if part_ml is not None else None,
+        counters.data_ptr() if counters is not None else None, counters.numel() if counters is not None else 0,
+        q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(),
         _i32(block_table, "block table"), block_table.shape[1], _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"),
-        n_seqs, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(n_splits),
-        int(tile_keys or TUNE["attn_tile_keys"]), _stream()), 2 if n_splits > 1 else 1)
+        n_seqs, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(n_splits), int(own_tiles),
+        tile_keys, int(stages if stages is not None else attn_decode_stages(head_dim)), _stream()),
+        2 if (n_splits > 1 and counters is None) else 1)
     return out
 
 
@@ -805,6 +835,11 @@ def swiglu_interleaved(h: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Te
     return silu_mul(gu, interleaved=True)
 
 
+def attn_decode_stages(head_dim: int) -> int:
+    """Depth of each warp's ring of key/value tiles in the tensor-core decode attention."""
+    return int(TUNE["attn_stages_hd64"] if head_dim == 64 else TUNE["attn_stages_hd128"])
+
+
 def attn_decode_blocks_per_sm(head_dim: int, fast: bool) -> float:
     """How many blocks of the decode attention one SM holds (its shared memory decides: a block's rings of key and
     value tiles are 96 KB at head size 128 and 64 KB at head size 64 with 16-key tiles), times TUNE["attn_waves"]:
@@ -812,7 +847,10 @@ def attn_decode_blocks_per_sm(head_dim: int, fast: bool) -> float:
     if not fast:
         per_sm = 2
     elif TUNE["attn_tile_keys"] == 16:
-        per_sm = 3 if head_dim == 64 else 2
+        # a block's shared memory: 16 rows of queries, and four warps' rings of `stages` x (16 keys + 16 values)
+        smem = 16 * head_dim * 2 + 4 * attn_decode_stages(head_dim) * 2 * 16 * head_dim * 2 + 1152
+        regs = 5 if head_dim == 64 else 3          # blocks per SM that the registers allow (96 and 168 a thread)
+        per_sm = min(regs, (227 * 1024) // smem)
     else:
         per_sm = 1
     return per_sm * TUNE["attn_waves"]
@@ -822,11 +860,14 @@ OWN_LENGTH_TILES = 8      # 32-bit decode attention: a slice is this many 32-key
 
 
 def attn_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, n_kv: int, head_dim: int,
-                     window: Optional[int], dtype: torch.dtype):
+                     window: Optional[int], dtype: torch.dtype, kv_lens=None):
     """How the decode attention cuts contexts into slices, as (slices in the launch, tiles per slice).
 
-    bfloat16: tiles per slice 0 = every sequence is cut into the same number of slices, as many as fill the GPU
-    once (blocks that wait for a second wave cost more than longer slices), at least 128 positions each.
+    bfloat16, few sequences: tiles per slice 0 = every sequence is cut into the same number of slices, as many as
+    fill the GPU once (blocks that wait for a second round cost more than longer slices), at least 128 positions each.
+    bfloat16, so many sequences that one slice each fills more than half the GPU, and their lengths (`kv_lens`) known:
+    slices of a fixed number of tiles of each sequence's own span, the shortest for which all blocks still find a
+    place at once; long sequences are then cut and short ones are not, so that no block is much longer than the rest.
     float32: slices of a fixed length counted from the start of the sequence's own span, so that a sequence's
     sums are formed in the same order whatever else the step holds (the reference sizes its slices from the
     token's own span for the same reason, src/cuda.rs:1639-1644, :8432-8437); the launch holds as many slices as
@@ -840,8 +881,24 @@ def attn_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, 
     group = n_heads // n_kv
     chunks = (group + rows_per_block - 1) // rows_per_block
     blocks = max(1, n_seqs * n_kv * chunks)
-    fit = int(attn_decode_blocks_per_sm(head_dim, fast) * sm_count) // blocks
-    return int(max(1, min(fit, 32, max_kv_len // 128))), 0
+    places = int(attn_decode_blocks_per_sm(head_dim, fast) * sm_count)
+    if 2 * blocks <= places or not fast:
+        return int(max(1, min(places // blocks, 32, max_kv_len // 128))), 0
+    if kv_lens is not None and TUNE["attn_own_slices"] and blocks < places:
+        tile = int(TUNE["attn_tile_keys"])
+        span = (lambda n: n) if not window else (lambda n: min(n, int(window) + 2 * tile))
+        # the lengths a little ahead of now: the plan is kept while the sequences grow
+        lens = [span(min(int(n) + 64, max_kv_len)) for n in kv_lens]
+        idle = max(0, n_seqs - len(lens))                    # padding rows: one tile each
+        longest = span(max_kv_len)
+        unit = max(1, 256 // tile)
+        own = unit
+        while own * tile < longest:
+            need = (sum((n + own * tile - 1) // (own * tile) for n in lens) + idle) * n_kv * chunks
+            if need <= places:
+                return max(1, (longest + own * tile - 1) // (own * tile)), own
+            own += unit
+    return 1, 0
 
 
 def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim: int, scale: float,
@@ -861,10 +918,9 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
             part_o = torch.empty((step.n_seqs * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
         if fast:
-            if own_tiles:
-                raise KernelError("the tensor-core decode attention cuts every sequence into the same number of slices")
             return attn_decode_tc(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
-                                  step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml)
+                                  step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml,
+                                  own_tiles=own_tiles)
         return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
                                    step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml,
                                    own_tiles=own_tiles)

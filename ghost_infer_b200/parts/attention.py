@@ -54,10 +54,10 @@ class GqaAttention(Mixer):
     def plans_on_host(self) -> bool:
         return bool(self.position is not None and self.position.plans_on_host)
 
-    def decode_plan(self, n_seqs: int, max_kv_len: int, sm_count: int):
+    def decode_plan(self, n_seqs: int, max_kv_len: int, sm_count: int, kv_lens=None):
         """Into how many slices the decode attention cuts the contexts (the kernels' own rule)."""
         return ops.attn_decode_plan(n_seqs, max_kv_len, sm_count, self.n_heads, self.n_kv, self.head_dim, self.window,
-                                    self.rt.dtype)
+                                    self.rt.dtype, kv_lens)
 
     def bind(self, tensors, rt) -> None:
         super().bind(tensors, rt)

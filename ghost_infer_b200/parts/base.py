@@ -8,7 +8,7 @@ Interfaces (a new kind of part implements one of them and registers under a name
   q and k parts of the packed rows as the encoding wants and writes k and v to the cache.
 * `Mixer.forward(h, residual, step, memory)`: adds the mixer's output to `residual` in place.
   `Mixer.cache_request()` / `Mixer.state_request()` say what memory it wants per sequence.
-  `Mixer.decode_plan(n_seqs, max_kv_len, sm_count)` says how it cuts the work of one-token steps of that shape
+  `Mixer.decode_plan(n_seqs, max_kv_len, sm_count, kv_lens=None)` says how it cuts the work of one-token steps of that shape
   (anything hashable, or None); a recorded step keeps the plan it was recorded with (`step.plan_of(self)`).
 * `FeedForward.forward(h, residual, step)`: adds its output to `residual` in place.
 * `Block.forward(x, layer, step, memory)`: runs one layer's parts in its arrangement.
@@ -99,9 +99,11 @@ class Mixer(Part):
     def state_request(self) -> Optional[StateRequest]:
         return None
 
-    def decode_plan(self, n_seqs: int, max_kv_len: int, sm_count: int) -> Any:
+    def decode_plan(self, n_seqs: int, max_kv_len: int, sm_count: int, kv_lens=None) -> Any:
         """How this mixer cuts the work of a step of `n_seqs` one-token rows over contexts of up to `max_kv_len`
-        positions; hashable.  None: nothing about it depends on the shape."""
+        positions; hashable.  `kv_lens`: the live sequences' lengths where the caller knows them on the host (a plan
+        must stay right for any lengths up to `max_kv_len`; the lengths only help to make it a good one).
+        None: nothing about it depends on the shape."""
         return None
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, step, memory: LayerMemory) -> None:

@@ -228,6 +228,37 @@ def test_attention_decode_tensor_cores(tile_keys, H, KV, hd, window, splits):
     torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("H,KV,hd", [(8, 8, 64), (32, 8, 128), (5, 1, 64), (40, 2, 128)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("own_tiles,tile_keys", [(0, 16), (4, 16), (2, 32), (32, 16)])
+def test_attention_decode_merges_its_slices_itself(H, KV, hd, window, own_tiles, tile_keys):
+    """The slices merged by the block that finishes last, against the same launch merged by the second kernel: the same
+    bits (both add the slices in slice order), and both the operation in 64-bit.  Slices of a fixed number of tiles of
+    each sequence's own span: a sequence of one token uses one block, one of 700 many; the launch's other blocks
+    leave at once.  Three launches in a row: the counters must be back at zero each time."""
+    lens = [1, 31, 64, 65, 700, 333, 96, 129]
+    B, S = len(lens), 704
+    k = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=13)
+    v = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=14)
+    q = rnd(B, 1, H * hd, dtype=torch.bfloat16, seed=15)
+    kc, vc, bt = paged_from_dense(k, v, lens, seed=4)
+    slots, lens_t = torch.arange(B, dtype=torch.int32, device=DEV), torch.tensor(lens, dtype=torch.int32, device=DEV)
+    splits = 5 if own_tiles == 0 else (704 + own_tiles * tile_keys - 1) // (own_tiles * tile_keys) + 2     # two more than any sequence needs
+    ref = attention_ref(q, k, v, [1] * B, [n - 1 for n in lens], H, KV, hd, 0.17, window)[:, 0]
+    outs = []
+    for inside in (False, True, True, True):
+        out = torch.full((B, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        part_o = torch.full((B * H * splits * hd,), float("nan"), device=DEV)
+        part_ml = torch.full((B * H * splits * 2,), float("nan"), device=DEV)
+        ops.attn_decode_tc(q[:, 0], kc, vc, bt, slots, lens_t, B, H, KV, hd, 0.17, window, splits, out, part_o, part_ml,
+                           tile_keys=tile_keys, own_tiles=own_tiles, merge_inside=inside)
+        torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
+        outs.append(out)
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    assert int(ops._attn_merge_counters(torch.device(DEV)).abs().sum()) == 0
+
+
 @pytest.mark.parametrize("decode", [False, True, "tc"])
 @pytest.mark.parametrize("window", [None, 50])
 def test_attention_finds_one_far_key(decode, window):

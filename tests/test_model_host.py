@@ -54,7 +54,7 @@ def test_a_recorded_step_refuses_host_side_lists_in_words():
 
 def test_a_step_asks_the_mixer_for_its_plan_unless_one_was_recorded():
     class M:
-        def decode_plan(self, n_seqs, max_kv_len, sm_count):
+        def decode_plan(self, n_seqs, max_kv_len, sm_count, kv_lens=None):
             return ("plan", n_seqs, max_kv_len, sm_count)
 
     m, ctx = M(), StepContext()

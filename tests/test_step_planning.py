@@ -6,16 +6,16 @@ from ghost_infer_b200.kernels import ops
 BF, F32 = torch.bfloat16, torch.float32
 
 
-def plan(n_seqs, max_kv_len, n_heads, n_kv, head_dim, window=None, dtype=BF, sms=148):
-    return ops.attn_decode_plan(n_seqs, max_kv_len, sms, n_heads, n_kv, head_dim, window, dtype)
+def plan(n_seqs, max_kv_len, n_heads, n_kv, head_dim, window=None, dtype=BF, sms=148, kv_lens=None):
+    return ops.attn_decode_plan(n_seqs, max_kv_len, sms, n_heads, n_kv, head_dim, window, dtype, kv_lens)
 
 
 def test_slices_fill_the_blocks_an_sm_holds():
     # 8 sequences x 8 kv heads = 64 blocks per slice; two blocks per SM at head size 128, three at 64
     assert ops.attn_decode_blocks_per_sm(128, True) == 2 * ops.TUNE["attn_waves"]
-    assert ops.attn_decode_blocks_per_sm(64, True) == 3 * ops.TUNE["attn_waves"]
+    assert ops.attn_decode_blocks_per_sm(64, True) == 5 * ops.TUNE["attn_waves"]
     assert plan(8, 2048, 32, 8, 128) == (4, 0)
-    assert plan(8, 2048, 32, 8, 64) == (6, 0)
+    assert plan(8, 2048, 32, 8, 64) == (11, 0)
 
 
 def test_slices_are_never_shorter_than_128_positions_nor_more_than_32():
@@ -24,8 +24,33 @@ def test_slices_are_never_shorter_than_128_positions_nor_more_than_32():
     assert plan(1, 1 << 20, 4, 1, 128) == (32, 0)
 
 
-def test_a_full_gpu_takes_one_slice():
+def test_many_equal_sequences_take_one_slice_each():
+    # 64 sequences x 8 kv heads = 512 blocks for 296 places: cutting them would only add rounds
     assert plan(64, 2048, 32, 8, 128) == (1, 0)
+    assert plan(64, 2048, 32, 8, 128, kv_lens=[2048] * 64) == (1, 0)
+    # head size 64 with rings of two stages: five blocks per SM, 740 places; equal lengths still take one slice each
+    assert ops.attn_decode_blocks_per_sm(64, True) == 5 * ops.TUNE["attn_waves"]
+    assert plan(64, 1280, 32, 8, 64, kv_lens=[1200] * 64) == (1, 0)
+    assert plan(18, 2048, 32, 8, 128) == (2, 0)                     # 144 blocks: two equal slices still fit one round
+
+
+def test_many_unequal_sequences_are_cut_so_that_all_blocks_find_a_place_at_once():
+    """Lengths known: slices of a fixed number of tiles of each sequence's own span, the shortest (in steps of 256 keys)
+    with which the blocks of all sequences fit the GPU at once.  The long sequences are cut, the short ones are not."""
+    lens = [260 + 32 * i for i in range(64)]                        # 260 .. 2276
+    n, own = plan(64, 4096, 32, 8, 64, kv_lens=lens)
+    assert own > 0 and own % 16 == 0
+    blocks = lambda o: sum(-(-(l + 64) // (o * 16)) for l in lens) * 8
+    assert blocks(own) <= 740 < blocks(own - 16)                    # the shortest slice that fits
+    assert n == -(-4096 // (own * 16))                              # the launch covers the longest a sequence may get
+    assert max(lens) > own * 16                                     # the longest are cut
+    # without the lengths nothing is known about them: one slice each
+    assert plan(64, 4096, 32, 8, 64) == (1, 0)
+    # more blocks than places even uncut: one slice each
+    assert plan(64, 4096, 32, 8, 128, kv_lens=lens) == (1, 0)
+    # padding rows of a recorded step count as a block each
+    n2, own2 = plan(80, 4096, 32, 8, 64, kv_lens=lens)
+    assert own2 >= own
 
 
 def test_wide_groups_take_several_blocks_per_kv_head():
