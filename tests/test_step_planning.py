@@ -34,10 +34,13 @@ def test_many_equal_sequences_take_one_slice_each():
     assert plan(18, 2048, 32, 8, 128) == (2, 0)                     # 144 blocks: two equal slices still fit one round
 
 
-def test_many_unequal_sequences_are_cut_so_that_all_blocks_find_a_place_at_once():
-    """Lengths known: slices of a fixed number of tiles of each sequence's own span, the shortest (in steps of 256 keys)
-    with which the blocks of all sequences fit the GPU at once.  The long sequences are cut, the short ones are not."""
+def test_many_unequal_sequences_can_be_cut_so_that_all_blocks_find_a_place_at_once(monkeypatch):
+    """With TUNE["attn_own_slices"] and the lengths known: slices of a fixed number of tiles of each sequence's own span,
+    the shortest (in steps of 256 keys) with which the blocks of all sequences fit the GPU at once.  The long sequences
+    are cut, the short ones are not.  (Off by default: measured, the cut costs more than the evenness wins.)"""
     lens = [260 + 32 * i for i in range(64)]                        # 260 .. 2276
+    assert plan(64, 4096, 32, 8, 64, kv_lens=lens) == (1, 0)
+    monkeypatch.setitem(ops.TUNE, "attn_own_slices", True)
     n, own = plan(64, 4096, 32, 8, 64, kv_lens=lens)
     assert own > 0 and own % 16 == 0
     blocks = lambda o: sum(-(-(l + 64) // (o * 16)) for l in lens) * 8
