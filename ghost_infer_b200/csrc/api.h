@@ -151,6 +151,8 @@ int gi_settle(float* x, gi_settle_t settle, const int* rows, int n_rows, int d, 
 // tcgen05 / TMA product for many rows of activations; tile_n is 128 or 256
 int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
                     long ldo, int tile_n, void* stream);
+// narrower tiles for the columns of an unfilled last round of blocks: on (default) or off
+int gi_gemm_tc_tail_tiles(int on);
 int gi_gemm_tc_status(int* status);
 
 // table[t, i] = (cos, sin)(positions[t] * inv_freq[i]), float2 [n_tokens, rot / 2]
@@ -187,6 +189,9 @@ int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, long q_rows
                        long cache_pages, const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots,
                        const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd, float scale, int window,
                        void* stream);
+// query tiles two to a block (the i-th from the end with the i-th from the start): 0 never, 1 where the launch then
+// is one round of blocks (default), 2 always
+int gi_attn_prefill_t5_pairing(int mode);
 int gi_attn_prefill_t5_status(int* status);
 // bfloat16, head size 64 or 128: the same operation as gi_attn_decode_generic, on tensor cores
 int gi_attn_decode_tc(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, const void* kcache,

@@ -10,7 +10,12 @@
 // query row per thread: they read a row of S with tcgen05.ld, keep the running maximum and sum in 32-bit (base-2
 // exponentials), write the probabilities as bfloat16 over the scores they have just read (tcgen05.st), and
 // rescale the accumulator in tensor memory when a row's reference point moves.  Two blocks share an SM, so one
-// block's softmax overlaps the other's products.  Every wait has an iteration limit and reports through a status word.
+// block's softmax overlaps the other's products.  Where that makes the launch one round of blocks (a prompt of 2,048
+// tokens: 256 blocks on 296 places), a block takes two query tiles one after the other, the i-th from the end and
+// the i-th from the start: under the causal mask every block then visits the same number of key tiles, instead of
+// one full round and a ragged one.  Longer prompts keep one tile per block, longest first (measured: paired blocks
+// are 10% slower at 8,192 tokens, where the many rounds even out by themselves).
+// Every wait has an iteration limit and reports through a status word.
 #include <cuda.h>
 #include <math.h>
 
@@ -31,6 +36,7 @@ constexpr int TMEM_COLS = 256;   // two score buffers of 64 columns (tile j in b
 constexpr uint32_t Q_HALF = BQ * 128, KV_HALF = BKV * 128;   // a 64-dimension half of a tile: rows of 128 bytes, swizzled
 
 __device__ int g_attn_status = 0;
+int g_pairing = 1;      // two query tiles per block: 0 never, 1 when that gives one round of blocks, 2 always
 
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -75,7 +81,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, long ldo,
                        const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slots, const int* __restrict__ seq_pos0, int n_heads, int n_kv, float scale,
-                       int window, int q_tiles) {
+                       int window, int q_tiles, int paired) {
   constexpr int HALVES = HD / 64;
   constexpr uint32_t Q_BYTES = HALVES * Q_HALF, KV_BYTES = HALVES * KV_HALF;
   // instruction descriptors: float accumulator, bfloat16 operands, M 128; S = Q K^T has N 64 and both operands K-major,
@@ -97,8 +103,10 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // first, for every head and sequence of the launch, and the short ones fill the gaps at the end.
   const int h = blockIdx.x, b = blockIdx.y;
   const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
-  const int q0 = (q_tiles - 1 - (int)blockIdx.z) * BQ;
-  if (q0 >= qlen) return;
+  // the block's two query tiles: the later one first (it has the most keys to visit), then its mirror from the start
+  // (not paired: the later one only)
+  const int tile_a = q_tiles - 1 - (int)blockIdx.z, tile_b = paired ? (int)blockIdx.z : tile_a;
+  if (tile_b * BQ >= qlen) return;                         // the earlier tile lies past this sequence: so does the later one
   if (smem_u32(smem) & 1023u) {
     if (threadIdx.x == 0) atomicCAS(&g_attn_status, 0, 9);
     return;
@@ -106,18 +114,14 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int slot = seq_slots[b], pos0 = seq_pos0[b];
   const int kvh = h / (n_heads / n_kv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rows_here = min(BQ, qlen - q0);
-  const int p_last = pos0 + q0 + rows_here - 1;
-  int t_first = 0;
-  if (window > 0) t_first = max(0, pos0 + q0 - window + 1);
-  const int kt_begin = (t_first / BKV) * BKV;
-  const int n_tiles = (p_last - kt_begin) / BKV + 1;
 
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = bar0 + 24, kv_empty0 = bar0 + 40;
   const uint32_t s_full0 = bar0 + 56, p_full = bar0 + 72, o_full = bar0 + 80;
 
-  if (threadIdx.x == 0) {
+  auto init_barriers = [&](bool again) {
+    if (again)                                             // the objects of the tile before are no longer in use
+      for (int i = 0; i < 11; ++i) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * i) : "memory");
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full0 + 8 * s, 1);
@@ -129,7 +133,8 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(p_full, 4);
     mbar_init(o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
+  };
+  if (threadIdx.x == 0) init_barriers(false);
   if (warp == 4) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -140,6 +145,25 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
   gi::pdl_prologue();      // set-up overlapped the previous kernel's end; its results are visible from here on
+
+  bool first_pass = true;
+  for (int pass = 0; pass < 2; ++pass) {
+  const int q_tile = pass == 0 ? tile_a : tile_b;
+  if (pass == 1 && tile_b == tile_a) break;                // an odd count's middle tile has no mirror
+  const int q0 = q_tile * BQ;
+  if (q0 >= qlen) continue;                                // (uniform over the block)
+  if (!first_pass) {
+    // everybody is done with the tile before (its output is read out of tensor memory): fresh barriers for this one
+    if (threadIdx.x == 0) init_barriers(true);
+    __syncthreads();
+  }
+  first_pass = false;
+  const int rows_here = min(BQ, qlen - q0);
+  const int p_last = pos0 + q0 + rows_here - 1;
+  int t_first = 0;
+  if (window > 0) t_first = max(0, pos0 + q0 - window + 1);
+  const int kt_begin = (t_first / BKV) * BKV;
+  const int n_tiles = (p_last - kt_begin) / BKV + 1;
 
   // Two threads issue the products, each with its own loads, so that neither chain waits behind the other's
   // barriers: S(j+1) = Q K(j+1)^T wants only the keys and the score buffer back (the rows of S(j) read into
@@ -361,6 +385,10 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
   tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  }  // the block's two query tiles
+  tc_fence_before();
+  __syncthreads();
   if (warp == 4) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
@@ -370,7 +398,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int HD>
 int launch_t5(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, __nv_bfloat16* out,
               long ldo, const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots, const int* seq_pos0,
-              int n_heads, int n_kv, float scale, int window, int q_tiles) {
+              int n_heads, int n_kv, float scale, int window, int q_tiles, int paired) {
   constexpr size_t smem = (HD / 64) * (Q_HALF + 4 * KV_HALF) + 12 * 8 + 16;
   static bool configured[gi::MAX_DEVICES_SEEN] = {false};
   int dev;
@@ -380,7 +408,7 @@ int launch_t5(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUten
     if (dev >= 0) configured[dev] = true;
   }
   return gi::check(gi::launch(attn_prefill_t5_kernel<HD>, grid, dim3(THREADS), smem, stream, mq, mk, mv, out, ldo, block_table, max_pages,
-                              cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles),
+                              cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired),
                    "attention prefill (tcgen05)");
 }
 
@@ -408,12 +436,25 @@ extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, 
   rc = gi::tensor_map_2d_ex(&mv, vcache, cache_rows, hd, hd, GI_BF16, 64, BKV);
   if (rc != GI_OK) return rc;
   const int q_tiles = (max_q_len + BQ - 1) / BQ;
-  dim3 grid(n_heads, n_seqs, q_tiles);
+  // two query tiles per block where that makes the launch a single round of blocks (two blocks per SM)
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long paired_blocks = (long)n_heads * n_seqs * ((q_tiles + 1) / 2);
+  const int paired = (g_pairing != 0 && q_tiles > 1 && (g_pairing == 2 || paired_blocks <= 2L * (sms > 0 ? sms : 148))) ? 1 : 0;
+  dim3 grid(n_heads, n_seqs, paired ? (q_tiles + 1) / 2 : q_tiles);
   if (hd == 128)
     return launch_t5<128>(grid, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages, cu_seqlens, seq_slots,
-                          seq_pos0, n_heads, n_kv, scale, window, q_tiles);
+                          seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired);
   return launch_t5<64>(grid, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages, cu_seqlens, seq_slots,
-                       seq_pos0, n_heads, n_kv, scale, window, q_tiles);
+                       seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired);
+}
+
+// Query tiles two to a block: 0 never, 1 where the launch then is one round of blocks (default), 2 always; for
+// measurements and tests.
+extern "C" int gi_attn_prefill_t5_pairing(int mode) {
+  g_pairing = mode;
+  return GI_OK;
 }
 
 extern "C" int gi_attn_prefill_t5_status(int* status) {

@@ -10,7 +10,9 @@
 // or SwiGLU over gate/up rows interleaved in blocks of 8.  Stages are handed over with mbarriers:
 // TMA completes `full`, tcgen05.commit arrives on `empty` when the products that read a stage are done.
 // Rows and columns past M, N or K are zero-filled by TMA and masked at the store, so every size whose rows
-// are 16 bytes apart is taken.  Every wait has an iteration limit; a wait that runs out records a status
+// are 16 bytes apart is taken.  When the tiles do not fill the last round of blocks, the last columns are cut
+// into narrower tiles (their own TMA box and instruction width) that fit one round: 256 tiles of 128 x 256 on
+// 148 blocks cost two rounds of 256 columns, 144 of them plus 128 tiles of 128 x 224 cost 256 + 224.  Every wait has an iteration limit; a wait that runs out records a status
 // word and the block leaves through its normal exit (tensor memory freed).
 #include <cuda.h>
 
@@ -29,6 +31,7 @@ constexpr int BK = 64;       // k-columns per stage = one 128-byte swizzle row
 constexpr int THREADS = 192; // warp 0: TMA loads, warp 1: MMA and tensor-memory allocation, warps 2-5: epilogue
 
 __device__ int g_status = 0;   // 0 = fine; else which wait ran out (1 producer, 2 mma, 3 epilogue)
+bool g_tail_tiles = true;      // narrower tiles for an unfilled last round
 
 using namespace gi::tc;
 
@@ -37,10 +40,18 @@ __device__ __forceinline__ void stage_chunk(unsigned char* stg, int row, int j, 
   *reinterpret_cast<uint4*>(stg + row * 128 + ((j ^ (row & 7)) << 4)) = v;
 }
 
+// How the output is cut into tiles: `wide_cols` column tiles of BN, then column tiles of `narrow` (<= BN) columns.
+struct TilePlan {
+  int wide_cols;     // column tiles of full width
+  int narrow;        // width of the column tiles after them (0: none)
+  int n_tiles;       // all tiles
+};
+
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const __grid_constant__ CUtensorMap map_o, int M, int N, int K) {
+               const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_o, int M, int N, int K,
+               const TilePlan plan) {
   constexpr uint32_t A_BYTES = BM * BK * 2, W_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
   constexpr uint32_t STG_BYTES = BM * 128;     // a staging tile: 128 rows of 128 bytes
   // instruction descriptor: float accumulator (bits 4-5 = 1), bfloat16 A and B (bits 7-9, 10-12 = 1), both K-major,
@@ -55,9 +66,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int n_tiles = tiles_m * tiles_n;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int n_tiles = plan.n_tiles;
+  const int wide_tiles = plan.wide_cols * tiles_m;
   const int num_kb = (K + BK - 1) / BK;
+  // Tiles in an order that keeps a tile of W in use by neighbouring blocks: the row tile runs fastest.
+  auto geometry = [&](int tile, int& m0, int& n0, int& width) {
+    if (tile < wide_tiles) {
+      m0 = (tile % tiles_m) * BM;
+      n0 = (tile / tiles_m) * BN;
+      width = BN;
+    } else {
+      const int t = tile - wide_tiles;
+      m0 = (t % tiles_m) * BM;
+      n0 = plan.wide_cols * BN + (t / tiles_m) * plan.narrow;
+      width = plan.narrow;
+    }
+  };
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
   const uint32_t accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
 
@@ -82,21 +107,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem = *tmem_slot;
   gi::pdl_prologue();      // set-up overlapped the previous kernel's end; its results are visible from here on
 
-  // Tiles in an order that keeps a tile of W in use by neighbouring blocks: the row tile runs fastest.
   if (warp == 0) {
     if (lane == 0) {
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        int m0, n0, width;
+        geometry(tile, m0, n0, width);
+        const CUtensorMap* mw = width == BN ? &map_w : &map_w2;        // the box of W's rows is as tall as the tile is wide
+        const uint32_t bytes = A_BYTES + (uint32_t)width * BK * 2;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(empty0 + 8 * s, (((uint32_t)(it / STAGES)) & 1) ^ 1, 1, &g_status);   // a fresh barrier passes
           if (!ok) break;
-          mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+          mbar_expect_tx(full0 + 8 * s, bytes);
           const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
           tma_load_2d(dst, &map_a, kb * BK, m0, full0 + 8 * s);
-          tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full0 + 8 * s);
+          tma_load_2d(dst + A_BYTES, mw, kb * BK, n0, full0 + 8 * s);
         }
       }
     }
@@ -110,6 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
         const uint32_t d = tmem + (uint32_t)(buf * BN);
+        const uint32_t idesc = tile < wide_tiles ? IDESC : ((IDESC & ~(0x3fu << 17)) | ((uint32_t)(plan.narrow >> 3) << 17));
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(full0 + 8 * s, ((uint32_t)(it / STAGES)) & 1, 2, &g_status);
@@ -119,7 +147,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint64_t da = smem_desc(a_addr), dw = smem_desc(a_addr + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)     // 16 k-columns = 32 bytes further along the swizzled row
-            tc_mma(d, da + (uint64_t)(2 * k), dw + (uint64_t)(2 * k), IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_mma(d, da + (uint64_t)(2 * k), dw + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           tc_commit(empty0 + 8 * s);            // arrives when these products no longer read the stage
         }
         if (ok) tc_commit(accf0 + 8 * buf);     // arrives when the accumulator is complete
@@ -134,14 +162,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int seg = 0, chunk_no = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++seg) {
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      int m0, n0, width;
+      geometry(tile, m0, n0, width);
+      const int chunks = width / CW;
       const int buf = seg & 1;
       ok = mbar_wait(accf0 + 8 * buf, ((uint32_t)(seg >> 1)) & 1, 3, &g_status);
       if (!ok) break;
       tc_fence_after();
       const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / CW; ++c, ++chunk_no) {
+      for (int c = 0; c < chunks; ++c, ++chunk_no) {
         unsigned char* stg = staging + (chunk_no & 1) * STG_BYTES;
         // the TMA operation that last read this staging tile (two chunks ago) must be done with it
         if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -181,7 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int j = 0; j < 32; j += 4) stage_chunk(stg, row, j / 4, make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]));
           }
         }
-        if (c == BN / CW - 1) {
+        if (c == chunks - 1) {
           // the whole accumulator is in registers or staged: hand the buffer back to the MMA thread
           tc_fence_before();
           __syncwarp();
@@ -279,8 +309,31 @@ int sm_count() {
   return n;
 }
 
+// The cut of the output for BN-wide tiles on `sms` blocks.  Whole rounds of wide tiles first; if what is left would be
+// a round that is not full, its columns are cut into narrower tiles (a multiple of `gran` columns, the epilogue's
+// unit) of which one round holds all.
+TilePlan plan_tiles(int M, int N, int bn, int gran, int sms) {
+  const int tiles_m = (M + BM - 1) / BM, cols = (N + bn - 1) / bn;
+  TilePlan p = {cols, 0, tiles_m * cols};
+  const int per_round = sms / tiles_m;                  // column tiles one round of blocks holds
+  if (bn != 256 || per_round < 1 || p.n_tiles <= sms || p.n_tiles % sms == 0) return p;
+  const int rounds = p.n_tiles / sms;
+  const int wide = (int)((long)rounds * sms / tiles_m);
+  const int rest = N - wide * bn;
+  if (wide >= cols || rest <= 0) return p;
+  int narrow = ((rest + per_round - 1) / per_round + gran - 1) / gran * gran;
+  if (narrow < 32) narrow = 32;
+  if (narrow >= bn) return p;
+  const int narrow_cols = (rest + narrow - 1) / narrow;
+  p.wide_cols = wide;
+  p.narrow = narrow;
+  p.n_tiles = tiles_m * (wide + narrow_cols);
+  return p;
+}
+
 template <int BN, int STAGES, int MODE>
-int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, int M, int N, int K, cudaStream_t s) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mo, int M, int N, int K,
+           const TilePlan& plan, cudaStream_t s) {
   constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 2 * BM * 128 + (2 * STAGES + 4) * 8 + 16 + 1024;
   auto kern = gemm_tc_kernel<BN, STAGES, MODE>;
   static bool configured[gi::MAX_DEVICES_SEEN] = {false};
@@ -290,18 +343,19 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, 
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "tensor-core product: %s", cudaGetErrorString(e));
     if (dev >= 0) configured[dev] = true;
   }
-  const long tiles = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const long tiles = plan.n_tiles;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  return gi::check(gi::launch(kern, dim3(grid), dim3(THREADS), smem, s, ma, mw, mo, M, N, K), "tensor-core product");
+  return gi::check(gi::launch(kern, dim3(grid), dim3(THREADS), smem, s, ma, mw, mw2, mo, M, N, K, plan), "tensor-core product");
 }
 
 template <int BN, int STAGES>
-int launch_mode(int mode, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, int M, int N, int K, cudaStream_t s) {
+int launch_mode(int mode, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mo, int M, int N,
+                int K, const TilePlan& plan, cudaStream_t s) {
   switch (mode) {
-    case GI_TC_STORE_BF16: return launch<BN, STAGES, GI_TC_STORE_BF16>(ma, mw, mo, M, N, K, s);
-    case GI_TC_STORE_F32: return launch<BN, STAGES, GI_TC_STORE_F32>(ma, mw, mo, M, N, K, s);
-    case GI_TC_ACCUM_F32: return launch<BN, STAGES, GI_TC_ACCUM_F32>(ma, mw, mo, M, N, K, s);
-    case GI_TC_SWIGLU: return launch<BN, STAGES, GI_TC_SWIGLU>(ma, mw, mo, M, N, K, s);
+    case GI_TC_STORE_BF16: return launch<BN, STAGES, GI_TC_STORE_BF16>(ma, mw, mw2, mo, M, N, K, plan, s);
+    case GI_TC_STORE_F32: return launch<BN, STAGES, GI_TC_STORE_F32>(ma, mw, mw2, mo, M, N, K, plan, s);
+    case GI_TC_ACCUM_F32: return launch<BN, STAGES, GI_TC_ACCUM_F32>(ma, mw, mw2, mo, M, N, K, plan, s);
+    case GI_TC_SWIGLU: return launch<BN, STAGES, GI_TC_SWIGLU>(ma, mw, mw2, mo, M, N, K, plan, s);
   }
   return gi::fail(GI_ERR_ARG, "tensor-core product: unknown mode %d", mode);
 }
@@ -330,8 +384,21 @@ extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W
   rc = gi::tensor_map_2d_ex(&mo, out, M, out_cols, ldo, f32 ? GI_F32 : GI_BF16, f32 ? 32 : 64, BM);
   if (rc != GI_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  if (tile_n == 128) return launch_mode<128, 6>(mode, ma, mw, mo, M, N, K, s);
-  return launch_mode<256, 4>(mode, ma, mw, mo, M, N, K, s);
+  const int gran = mode == GI_TC_SWIGLU ? 128 : (mode == GI_TC_STORE_BF16 ? 64 : 32);
+  const TilePlan plan = g_tail_tiles ? plan_tiles(M, N, tile_n, gran, sm_count()) : plan_tiles(M, N, tile_n, gran, 0);
+  CUtensorMap mw2 = mw;
+  if (plan.narrow > 0) {
+    rc = gi::tensor_map_2d(&mw2, W, N, K, ldw, plan.narrow);
+    if (rc != GI_OK) return rc;
+  }
+  if (tile_n == 128) return launch_mode<128, 6>(mode, ma, mw, mw2, mo, M, N, K, plan, s);
+  return launch_mode<256, 4>(mode, ma, mw, mw2, mo, M, N, K, plan, s);
+}
+
+// Switches the narrower tiles of an unfilled last round on (the default) or off; for measurements.
+extern "C" int gi_gemm_tc_tail_tiles(int on) {
+  g_tail_tiles = on != 0;
+  return GI_OK;
 }
 
 // Reads and clears the status word of the tensor-core product (0 = every wait was met).  Synchronises the device.

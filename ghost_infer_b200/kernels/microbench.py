@@ -62,6 +62,7 @@ def main() -> int:
     ap.add_argument("--own-tiles", type=int, default=0, help="attn_decode: slices of that many tiles of each sequence's own span")
     ap.add_argument("--tile-keys", type=int, default=0, help="attn_decode: 16 or 32 keys per tile (default: the engine's)")
     ap.add_argument("--merge-inside", type=int, default=-1, help="attn_decode: 1 = slices merged by the last block, 0 = by a second kernel")
+    ap.add_argument("--tail", type=int, default=1, help="gemm_tc: 0 = full-width tiles only, 1 = narrower tiles in an unfilled last round")
     ap.add_argument("--stages", type=int, default=0, help="attn_decode: depth of each warp's ring of tiles (2 to 4)")
     ap.add_argument("--shortest", type=int, default=0, help="attn_decode: lengths uniform in [shortest, context] instead of all equal")
     ap.add_argument("--iters", type=int, default=20)
@@ -76,6 +77,7 @@ def main() -> int:
     out = {"kernel": args.kernel, "peaks": src}
     if args.kernel in ("gemm_stream", "gemm_skinny", "gemm_tc"):
         M, N, K = args.m, args.n, args.k
+        ops.gemm_tc_tail_tiles(bool(args.tail))
         n_rot = max(2, L2_BYTES * 2 // (N * K * 2) + 1)
         ws = [torch.randn(N, K, device=dev, dtype=bf) * 0.02 for _ in range(n_rot)]
         x = torch.randn(M, K, device=dev, dtype=bf)
@@ -84,7 +86,7 @@ def main() -> int:
         fn = {"gemm_stream": ops.gemm_stream, "gemm_skinny": ops.gemm_skinny, "gemm_tc": ops.gemm_tc}[args.kernel]
         us = _time(lambda i: fn(x, ws[i], mode, o), n_rot, args.iters, args.warmup)
         flops, nbytes = 2.0 * M * N * K, N * K * 2 + M * K * 2 + o.numel() * o.element_size()
-        out.update(shape=[M, N, K], mode=args.mode, us=round(us, 2), tflops=round(flops / us / 1e6, 1),
+        out.update(shape=[M, N, K], mode=args.mode, tail=args.tail, us=round(us, 2), tflops=round(flops / us / 1e6, 1),
                    gbs=round(nbytes / us / 1e3, 1), frac_hbm=round(nbytes / us / 1e3 / hbm, 3),
                    frac_tensor=round(flops / us / 1e6 / tflops, 3))
     elif args.kernel in ("attn_decode", "attn_prefill", "attn_prefill_t5"):

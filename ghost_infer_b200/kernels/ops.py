@@ -570,6 +570,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch.Ten
     return out
 
 
+def gemm_tc_tail_tiles(on: bool) -> None:
+    """The tensor-core product cuts the columns of an unfilled last round of blocks into narrower tiles that fit one
+    round (on by default); off, every tile has the full width.  Process-wide; for measurements and tests."""
+    lib = _bind()
+    lib.gi_gemm_tc_tail_tiles(int(bool(on)))
+
+
 def gemm_tc_status() -> int:
     """0 if every wait inside the tensor-core product was met since the last call; synchronises the device."""
     lib = _bind()
@@ -717,6 +724,12 @@ def attn_prefill_t5(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
         _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"), n_seqs, max_q_len, n_heads, n_kv, head_dim,
         float(scale), int(window or 0), _stream()))
     return out
+
+
+def attn_prefill_t5_pairing(mode: int) -> None:
+    """Query tiles two to a block in the tcgen05 prompt attention: 0 never, 1 where the launch then is one round of
+    blocks (the default), 2 always.  Process-wide; for measurements and tests."""
+    _bind().gi_attn_prefill_t5_pairing(int(mode))
 
 
 def attn_prefill_t5_status() -> int:

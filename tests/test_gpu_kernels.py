@@ -700,11 +700,15 @@ def test_deferred_store_is_settled_by_the_rotary_kernel(m, H, KV, hd, rot):
 @pytest.mark.parametrize("hd", [128, 64])
 @pytest.mark.parametrize("H,KV", [(4, 2), (32, 8), (3, 1)])
 @pytest.mark.parametrize("window", [None, 37, 100])
-def test_attention_prefill_tcgen05(H, KV, window, hd):
+@pytest.mark.parametrize("pairing", [0, 2])
+def test_attention_prefill_tcgen05(H, KV, window, hd, pairing, request):
     """The tcgen05 prefill kernel (head sizes 128 and 64): ragged lengths around its 128-row and 64-key tiles,
-    sequences that go on after cached positions, pages in shuffled order, unowned rows poisoned with NaN."""
-    lens_q, pos0 = [1, 45, 128, 129, 300, 33, 130], [0, 0, 0, 0, 0, 70, 200]
-    B, S = len(lens_q), 384
+    sequences that go on after cached positions, pages in shuffled order, unowned rows poisoned with NaN.  With one
+    query tile per block and with two (the block's barriers are made anew between them)."""
+    ops.attn_prefill_t5_pairing(pairing)
+    request.addfinalizer(lambda: ops.attn_prefill_t5_pairing(1))
+    lens_q, pos0 = [1, 45, 128, 129, 300, 33, 130, 520], [0, 0, 0, 0, 0, 70, 200, 10]
+    B, S = len(lens_q), 576
     k = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=10)
     v = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=11)
     q = rnd(B, max(lens_q), (H + 2 * KV) * hd, dtype=torch.bfloat16, seed=12)
@@ -851,3 +855,35 @@ def test_a_replayed_step_reads_what_its_own_kernels_wrote(H, KV, hd, lens, hidde
             assert torch.equal(out, want)
     finally:
         ops.set_pdl(was)
+
+
+@pytest.mark.parametrize("mode", ["store", "accum", "swiglu", "f32"])
+@pytest.mark.parametrize("m,n,k", [(2048, 4096, 256), (2048, 6144, 128), (2000, 4000, 264), (1100, 8192, 64), (300, 38400, 64)])
+def test_tensor_core_product_with_narrower_tiles_in_the_last_round(mode, m, n, k):
+    """Shapes whose 128 x 256 tiles do not fill the last round of blocks: the last columns are cut into narrower tiles
+    (another TMA box, another instruction width, fewer epilogue chunks).  Every element is still one sum in k order: the
+    same bits as with full-width tiles, and the product itself within the tolerance."""
+    a = rnd(m, k, dtype=torch.bfloat16, seed=80)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=81, scale=0.1)
+    code = {"store": ops.SKINNY_STORE_BF16, "accum": ops.SKINNY_ACCUM_F32, "swiglu": ops.SKINNY_SWIGLU, "f32": ops.SKINNY_STORE_F32}[mode]
+    base = rnd(m, n, seed=82) if mode == "accum" else None
+    outs = []
+    try:
+        for tail in (True, False):
+            ops.gemm_tc_tail_tiles(tail)
+            out = base.clone() if base is not None else None
+            outs.append(ops.gemm_tc(a, w, code, out))
+            assert ops.gemm_tc_status() == 0
+    finally:
+        ops.gemm_tc_tail_tiles(True)
+    assert torch.equal(outs[0], outs[1])
+    full = a.double() @ w.double().T
+    if mode == "swiglu":
+        g = full.view(m, n // 16, 2, 8)[:, :, 0].reshape(m, n // 2)
+        u = full.view(m, n // 16, 2, 8)[:, :, 1].reshape(m, n // 2)
+        ref = g / (1 + torch.exp(-g)) * u
+        torch.testing.assert_close(outs[0].double(), ref, rtol=2e-2, atol=1e-2 * float(ref.abs().max()))
+    elif mode == "accum":
+        torch.testing.assert_close(outs[0].double(), base.double() + full, rtol=1e-4, atol=1e-3)
+    else:
+        torch.testing.assert_close(outs[0].double(), full, rtol=1e-2 if mode == "store" else 1e-4, atol=1e-3 * float(full.abs().max()))
