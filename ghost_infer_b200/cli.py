@@ -44,6 +44,11 @@ OPTIONS:
         --batch <n>       sequences per batch                [run: 8, bench: 1]
         --dtype <t>       bfloat16 or float32                [bfloat16]
         --gpu             accepted for compatibility: there is no other backend
+
+ENVIRONMENT:
+    GHOST_INFER_PROFILE=1     run: device time per kind of operation (steps then run kernel by kernel)
+    GHOST_INFER_LOGITS_OUT=f  top: every logit of the last position as little-endian float32 into f
+    GHOST_INFER_BENCH_ROUNDS  bench: rounds to take the best of [3]
 """
 
 
@@ -147,6 +152,18 @@ def print_stats(st) -> None:
           file=sys.stderr)
 
 
+def _profile_wanted() -> bool:
+    return os.environ.get("GHOST_INFER_PROFILE", "") not in ("", "0")
+
+
+def print_profile(buckets, tokens: int) -> None:
+    """Device time per kind of operation and per token, in the reference's manner (src/profile.rs:36-46)."""
+    total = sum(buckets.values()) or 1.0
+    print(f"[profile over {tokens} tokens: device time per token, steps launched kernel by kernel]", file=sys.stderr)
+    for name, ms in buckets.items():
+        print(f"  {name:<12} {ms * 1e3 / max(1, tokens):>10.1f} us  {100.0 * ms / total:>5.1f}%", file=sys.stderr)
+
+
 def cmd_run(o: Opts) -> None:
     if o.prompt is None:
         raise UsageError("run needs -p <token ids>")
@@ -154,11 +171,17 @@ def cmd_run(o: Opts) -> None:
     ctx = o.ctx or 2048
     batch = o.batch or 8
     llm = _llm(o, max_tokens=min(batch, len(prompts)) * ctx, ctx=ctx)
+    if _profile_wanted():          # GHOST_INFER_PROFILE, as the reference's switch is called (src/profile.rs:20-29)
+        from .kernels import ops
+        ops.profile_start()
     results = llm.generate(prompts, max_new=o.max_new, temperature=o.temp, top_k=o.top_k, top_p=o.top_p,
                            seed=o.seed, batch_size=batch)
     for r in results:
         print(" ".join(str(t) for t in r.tokens))
     print_stats(llm.last_stats)
+    if _profile_wanted():
+        st = llm.last_stats
+        print_profile(ops.profile_stop(), st.prompt_tokens + st.gen_tokens)
 
 
 def cmd_top(model: str, ids_text: str, dtype: str = "bfloat16") -> None:

@@ -81,7 +81,8 @@ class DecodeRunner:
             raise ValueError("a decode runner needs at least one sequence")
         # a model with a part that plans its work in Python per step cannot be replayed: it decodes launch by
         # launch, with exactly the live rows and the host-side lists filled in
-        self.use_graph = use_graph and engine.device.type == "cuda" and not engine.plans_on_host
+        from ..kernels import ops
+        self.use_graph = use_graph and engine.device.type == "cuda" and not engine.plans_on_host and not ops.profiling()
         self.rows = _bucket_rows(self.n) if self.use_graph else self.n
         self._g: Optional[_DecodeGraph] = None
         self._plans: Dict[int, dict] = {}

@@ -123,6 +123,82 @@ def _i32(t: Optional[torch.Tensor], what: str):
     return t.data_ptr()
 
 
+# ---- time per kind of operation ----------------------------------------------------------------------------
+# The reference sums wall-clock time into eight named buckets ("embed", "norm+quant", "qkv matmul", "rope+cache",
+# "attention", "out matmul", "ffn matmul", "logits"), switched on by GHOST_INFER_PROFILE, synchronising after each
+# operation and running without its CUDA graph meanwhile (src/profile.rs:7-46, src/cuda.rs:8054-8063, :9993-9996).
+# Here the parts name the bucket of what they launch (`with ops.bucket("attention"):`), and while profiling is on a
+# pair of CUDA events brackets each such stretch on the launching stream: device time, no synchronisation inside a
+# step.  Steps are then launched kernel by kernel (no graph replay, no dependent launch, which would let one bucket's
+# kernels run inside another's stretch).  Off, `bucket` hands out one shared do-nothing context.
+BUCKETS = ("embed", "norm", "qkv matmul", "rope+cache", "attention", "out matmul", "ffn matmul", "logits", "sampling")
+
+
+class _NoBucket:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_BUCKET = _NoBucket()
+_profile_marks: Optional[list] = None      # (bucket, start event, end event) while profiling
+_profile_pdl_was: Optional[bool] = None
+
+
+class _Bucket:
+    __slots__ = ("name", "start")
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        self.start = torch.cuda.Event(enable_timing=True)
+        self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        end = torch.cuda.Event(enable_timing=True)
+        end.record()
+        if _profile_marks is not None:
+            _profile_marks.append((self.name, self.start, end))
+        return False
+
+
+def bucket(name: str):
+    """A context for the launches of one kind of operation; it costs nothing unless profiling is on."""
+    return _NO_BUCKET if _profile_marks is None else _Bucket(name)
+
+
+def profiling() -> bool:
+    return _profile_marks is not None
+
+
+def profile_start() -> None:
+    """From now on the device time of every bucketed stretch is recorded (steps run without graph and dependent launch)."""
+    global _profile_marks, _profile_pdl_was
+    if _profile_marks is None:
+        _profile_pdl_was = get_pdl()
+        set_pdl(False)
+    _profile_marks = []
+
+
+def profile_stop() -> Dict[str, float]:
+    """Stops recording.  Returns milliseconds of device time per bucket, in the order of BUCKETS (others after)."""
+    global _profile_marks, _profile_pdl_was
+    marks, _profile_marks = _profile_marks or [], None
+    if _profile_pdl_was is not None:
+        set_pdl(_profile_pdl_was)
+        _profile_pdl_was = None
+    torch.cuda.synchronize()
+    totals: Dict[str, float] = {}
+    for name, a, b in marks:
+        totals[name] = totals.get(name, 0.0) + a.elapsed_time(b)
+    order = [n for n in BUCKETS if n in totals] + sorted(n for n in totals if n not in BUCKETS)
+    return {n: totals[n] for n in order}
+
+
 # ------------------------------------------------------------------------------------------------
 def embed(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     lib = _bind()

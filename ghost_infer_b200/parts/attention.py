@@ -73,18 +73,22 @@ class GqaAttention(Mixer):
     def forward(self, h, residual, step, memory) -> None:
         # in a decode step the product may leave partial sums for the kernel that rotates and stores (it reads
         # every value anyway); an encoding that does not go through that kernel gets plain rows
-        if self.position is None or getattr(self.position, "settles_pending", False):
-            with ops.defer_store():
+        with ops.bucket("qkv matmul"):
+            if self.position is None or getattr(self.position, "settles_pending", False):
+                with ops.defer_store():
+                    qkv = linear(h, self.w_qkv, out_dtype=self.rt.dtype)
+            else:
                 qkv = linear(h, self.w_qkv, out_dtype=self.rt.dtype)
-        else:
-            qkv = linear(h, self.w_qkv, out_dtype=self.rt.dtype)
-        if self.position is not None:
-            self.position.encode_and_store(qkv, step, memory, self.n_heads, self.n_kv, self.head_dim)
-        else:
-            ops.rope_cache_write(qkv, None, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
-                                 self.n_heads, self.n_kv, self.head_dim, 0, False,
-                                 memory.writes and memory.k is not None)
-        att = torch.empty((h.shape[0], self.q_dim), dtype=self.rt.dtype, device=h.device)
-        ops.attention(qkv, memory, step, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, att,
-                      plan=step.plan_of(self))
-        linear(att, self.w_o, out=residual, accumulate=True)
+        with ops.bucket("rope+cache"):
+            if self.position is not None:
+                self.position.encode_and_store(qkv, step, memory, self.n_heads, self.n_kv, self.head_dim)
+            else:
+                ops.rope_cache_write(qkv, None, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
+                                     self.n_heads, self.n_kv, self.head_dim, 0, False,
+                                     memory.writes and memory.k is not None)
+        with ops.bucket("attention"):
+            att = torch.empty((h.shape[0], self.q_dim), dtype=self.rt.dtype, device=h.device)
+            ops.attention(qkv, memory, step, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, att,
+                          plan=step.plan_of(self))
+        with ops.bucket("out matmul"):
+            linear(att, self.w_o, out=residual, accumulate=True)

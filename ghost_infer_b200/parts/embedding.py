@@ -30,7 +30,8 @@ class TokenEmbedding(Part):
         self.weight = rt.place(tensors[self.tensor_name("weight", "weight")])
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
-        return ops.embed(self.weight, tokens)
+        with ops.bucket("embed"):
+            return ops.embed(self.weight, tokens)
 
 
 @register("head", "linear_head")
@@ -59,4 +60,5 @@ class LinearHead(Part):
             self.weight = rt.place(tensors[self.tensor_name("weight", "weight")])
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return linear(h, self.weight, out_dtype=torch.float32)
+        with ops.bucket("logits"):
+            return linear(h, self.weight, out_dtype=torch.float32)

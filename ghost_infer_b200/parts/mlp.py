@@ -50,9 +50,10 @@ class SwiGlu(FeedForward):
         self.w_down = rt.place(tensors[self.names["down"]])
 
     def forward(self, h, residual, step) -> None:
-        if self.interleaved:
-            act = ops.swiglu_interleaved(h, self.w_gate_up)
-        else:
-            gu = linear(h, self.w_gate_up, out_dtype=self.rt.dtype)
-            act = ops.silu_mul(gu)
-        linear(act, self.w_down, out=residual, accumulate=True)
+        with ops.bucket("ffn matmul"):
+            if self.interleaved:
+                act = ops.swiglu_interleaved(h, self.w_gate_up)
+            else:
+                gu = linear(h, self.w_gate_up, out_dtype=self.rt.dtype)
+                act = ops.silu_mul(gu)
+            linear(act, self.w_down, out=residual, accumulate=True)

@@ -31,4 +31,5 @@ class RmsNorm(Norm):
         self.weight = rt.place(tensors[self.tensor_name("weight", "weight")])
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return ops.rmsnorm(x, self.weight, self.eps, self.rt.dtype, rows=rows)
+        with ops.bucket("norm"):
+            return ops.rmsnorm(x, self.weight, self.eps, self.rt.dtype, rows=rows)

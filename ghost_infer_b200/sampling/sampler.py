@@ -69,10 +69,11 @@ class DeviceSampler:
         """One token for each row of `logits` (row r belongs to request `request_ids[r]`), left on the device
         as int32, so that the next step can be launched before the host has looked at the tokens."""
         p = self.params
-        if p.greedy:
-            return ops.sample(logits, 0.0, 0, 1.0)
-        idx = torch.tensor(list(request_ids), dtype=torch.int32).to(self.device, non_blocking=True)
-        return ops.sample(logits, p.temperature, p.top_k, p.top_p, self.states, idx)
+        with ops.bucket("sampling"):
+            if p.greedy:
+                return ops.sample(logits, 0.0, 0, 1.0)
+            idx = torch.tensor(list(request_ids), dtype=torch.int32).to(self.device, non_blocking=True)
+            return ops.sample(logits, p.temperature, p.top_k, p.top_p, self.states, idx)
 
     def pick(self, logits: torch.Tensor, request_ids: Sequence[int]) -> List[int]:
         """The same, brought to the host."""

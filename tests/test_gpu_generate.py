@@ -139,3 +139,30 @@ def test_command_line_top_kvcheck_and_bench(tmp_path, model_dirs, tiny_configs):
                        timeout=600, env=dict(os.environ, GHOST_INFER_BENCH_ROUNDS="2"))
     assert p.returncode == 0, p.stderr
     assert "prompt 20 tok x 2:" in p.stdout and "generate 6 tok x 2:" in p.stdout and p.stderr.count("round ") == 2
+
+
+def test_time_per_kind_of_operation(model_dirs, tiny_configs):
+    """The reference's profile buckets (src/profile.rs:7-46): with profiling on, every bucket the decoder uses has device
+    time, steps run without a graph, and the tokens are the ones generation gives without it."""
+    from ghost_infer_b200.kernels import ops
+    d = model_dirs("E", "bfloat16")
+    llm = gi.LLM(d, dtype="bfloat16", max_tokens=64 * 8)
+    prompts = [tokens_for(tiny_configs["E"], n, 90 + i) for i, n in enumerate([20, 5])]
+    plain = [r.tokens for r in llm.generate(prompts, max_new=6, temperature=0.0, stop_token_ids=(), batch_size=2)]
+    assert not ops.profiling()
+    was = ops.get_pdl()
+    ops.profile_start()
+    try:
+        assert ops.profiling() and not ops.get_pdl()
+        timed = [r.tokens for r in llm.generate(prompts, max_new=6, temperature=0.0, stop_token_ids=(), batch_size=2)]
+        assert not llm.engine.decoder([0]).use_graph
+    finally:
+        buckets = ops.profile_stop()
+    assert timed == plain and not ops.profiling() and ops.get_pdl() == was
+    assert list(buckets) == ["embed", "norm", "qkv matmul", "rope+cache", "attention", "out matmul", "ffn matmul", "logits", "sampling"]
+    assert all(ms > 0 for ms in buckets.values())
+    # the command line prints them per token
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "ghost-infer"), "run", d, "-p", "1,2,3", "-n", "4", "-t", "0"],
+                       capture_output=True, text=True, timeout=600, env=dict(os.environ, GHOST_INFER_PROFILE="1"))
+    assert p.returncode == 0, p.stderr
+    assert "[profile over" in p.stderr and "attention" in p.stderr and "ffn matmul" in p.stderr
