@@ -375,7 +375,7 @@ def main():
 
     # prefill: one prompt of 2,048 tokens, logits for its last place
     prompt = rng.integers(0, V, size=PROMPT).tolist()
-    reps = 5
+    reps = 9
 
     def prefill_once():
         s = cache.open_slot()
@@ -384,18 +384,20 @@ def main():
         return out
 
     def prefill_timed():
+        """Every repetition timed by its own pair of events; the median stands (the power cap makes single ones wander)."""
         for _ in range(3):
             prefill_once()
         torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(reps):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+        marks[0].record()
+        for i in range(reps):
             prefill_once()
-        stop.record()
+            marks[i + 1].record()
         torch.cuda.synchronize()
-        return start.elapsed_time(stop) / reps
+        each = sorted(a.elapsed_time(b) for a, b in zip(marks, marks[1:]))
+        return each[len(each) // 2], each[0], each[-1]
 
-    pre_ms = timed("prefill", prefill_timed)
+    pre_ms, pre_min, pre_max = timed("prefill", prefill_timed)
     H, hd = cfg["num_attention_heads"], cfg["head_dim"]
     flops = 2.0 * PROMPT * layers * nums["linear_params_per_layer"] + 2.0 * nums["head_params"] \
         + layers * 4.0 * H * hd * (PROMPT * (PROMPT + 1) / 2)
@@ -449,7 +451,8 @@ def main():
         "e2e": e2e,
         "gpu_launches": int(launches8),
         "prefill": {"value": round(PROMPT * 1000.0 / pre_ms, 1), "tokens": PROMPT, "ms": round(pre_ms, 3), "frac": round(pre_frac, 4),
-                    "peak_tflops": pk["bf16_tflops"]},
+                    "peak_tflops": pk["bf16_tflops"], "ms_min": round(pre_min, 3), "ms_max": round(pre_max, 3), "reps": reps,
+                    "frac_of_sustained": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
         "points": points,

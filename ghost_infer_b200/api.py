@@ -55,4 +55,7 @@ class LLM:
                               max_step_tokens=max_step_tokens, time_steps_every=time_steps_every)
         results = loop.run(prompts, max_new)
         self.last_stats = loop.stats
+        if self.model.rt.device.type == "cuda":
+            from .kernels import ops
+            ops.check_status()          # a kernel whose bounded wait ran out has said so: never hand out its tokens silently
         return results

@@ -95,7 +95,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   unsigned char* q_s = smem;                              // [halves][128 rows][64 dims]
   unsigned char* k_s = q_s + Q_BYTES;                     // [2 stages][halves][64 keys][64 dims]
   unsigned char* v_s = k_s + 2 * KV_BYTES;                // the same
-  uint64_t* bars = (uint64_t*)(v_s + 2 * KV_BYTES);       // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], p_full, o_full
+  uint64_t* bars = (uint64_t*)(v_s + 2 * KV_BYTES);       // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], p_full[2], o_full
   uint32_t* tmem_slot = (uint32_t*)(bars + 12);
 
   // Blocks start in the order x, y, z: heads fastest (the heads of a group read the same keys and values at the
@@ -117,11 +117,16 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = bar0 + 24, kv_empty0 = bar0 + 40;
-  const uint32_t s_full0 = bar0 + 56, p_full = bar0 + 72, o_full = bar0 + 80;
+  // The probabilities' barrier is one per score buffer, not one for both: a row warp may be a whole tile ahead of
+  // another (one that rescales the accumulator, or zeroes values at a tile's edge, while the others do not), and with
+  // one barrier its arrival for tile j + 1 would have counted as the slow warp's for tile j: the output product would
+  // have started without that warp's probabilities, and the count would have been one off from then on.  On the
+  // buffer's own barrier nobody can be a tile ahead: tile j + 2 needs the buffer back, which needs tile j's product.
+  const uint32_t s_full0 = bar0 + 56, p_full0 = bar0 + 72, o_full = bar0 + 88;
 
   auto init_barriers = [&](bool again) {
     if (again)                                             // the objects of the tile before are no longer in use
-      for (int i = 0; i < 11; ++i) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * i) : "memory");
+      for (int i = 0; i < 12; ++i) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * i) : "memory");
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full0 + 8 * s, 1);
@@ -130,7 +135,8 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     mbar_init(s_full0, 1);
     mbar_init(s_full0 + 8, 1);
-    mbar_init(p_full, 4);
+    mbar_init(p_full0, 4);
+    mbar_init(p_full0 + 8, 4);
     mbar_init(o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   };
@@ -237,7 +243,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
         // O += P V once the probabilities are staged (which also says: O has been rescaled) and the values are here
-        ok = mbar_wait(p_full, (uint32_t)(j & 1), 2, &g_attn_status);
+        ok = mbar_wait(p_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 2, &g_attn_status);
         if (ok) ok = mbar_wait(v_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 2, &g_attn_status);
         if (!ok) break;
         tc_fence_after();
@@ -355,7 +361,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full0 + 8 * s);
     }
     if (ok) ok = mbar_wait(o_full, (uint32_t)((n_tiles - 1) & 1), 3, &g_attn_status);
     tc_fence_after();

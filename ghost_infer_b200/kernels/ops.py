@@ -661,6 +661,20 @@ def gemm_tc_status() -> int:
     return status.value
 
 
+def check_status() -> None:
+    """Raises if any bounded wait inside the tensor-core kernels ran out since the last call (the kernel then left
+    through its normal exit with its work undone: the results of that launch are not to be trusted).  Reads and
+    clears the kernels' status words; synchronises the device."""
+    bad = []
+    for name, fn in (("prompt product", gemm_tc_status), ("decode product", gemm_stream_status),
+                     ("prompt attention", attn_prefill_t5_status)):
+        code = fn()
+        if code:
+            bad.append(f"{name} (wait {code})")
+    if bad:
+        raise KernelError("a wait inside a kernel ran out of tries: " + ", ".join(bad) + "; results since the last check are not to be trusted")
+
+
 def _tc_out_ok(out: Optional[torch.Tensor], mode: int, cols: int) -> bool:
     """The tensor-core product stores 16 bytes at a time: output rows must start on 16-byte boundaries."""
     align = 8 if mode in (SKINNY_STORE_BF16, SKINNY_SWIGLU) else 4
