@@ -887,3 +887,40 @@ def test_tensor_core_product_with_narrower_tiles_in_the_last_round(mode, m, n, k
         torch.testing.assert_close(outs[0].double(), base.double() + full, rtol=1e-4, atol=1e-3)
     else:
         torch.testing.assert_close(outs[0].double(), full, rtol=1e-2 if mode == "store" else 1e-4, atol=1e-3 * float(full.abs().max()))
+
+
+@pytest.mark.parametrize("hd", [128, 64])
+@pytest.mark.parametrize("slow_warp", [0, 3])
+def test_prompt_attention_with_one_row_warp_far_behind_the_others(hd, slow_warp):
+    """In the tcgen05 prompt attention four warps own 32 query rows each.  Here the rows of one warp meet a larger
+    maximum at every tile (their scores grow with the key's position: the accumulator is rescaled each time, which
+    waits for the output product before), while all other rows see equal scores and run ahead.  A warp a tile ahead
+    must not be counted for the one behind: the slow rows' outputs name the newest key (values hold their position),
+    the others the mean of what they see.  (With one barrier for both score buffers this case went wrong about once
+    in some ten thousand blocks, when the slow warp was also held up by the SM's other block: the test walks the path,
+    it cannot force the timing.)"""
+    H, KV, n, gap = 2, 1, 1536, 12.0
+    k = torch.zeros(1, n, KV, hd, device=DEV)
+    k[0, :, 0, 0] = torch.arange(n, device=DEV) * gap
+    v = torch.zeros(1, n, KV, hd, device=DEV)
+    v[0, :, 0, :] = (torch.arange(n, device=DEV, dtype=torch.float32) / 64.0)[:, None]
+    q = torch.zeros(1, n, (H + 2 * KV) * hd, device=DEV)
+    rows = torch.arange(n, device=DEV)
+    slow = (rows % 128) // 32 == slow_warp
+    for h in range(H):
+        q[0, slow, h * hd] = 1.0
+    k, v, q = k.to(torch.bfloat16), v.to(torch.bfloat16), q.to(torch.bfloat16)
+    kc, vc, bt = paged_from_dense(k, v, [n], seed=7)
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    zero = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ref = attention_ref(q[:, :, :H * hd], k, v, [n], [0], H, KV, hd, 1.0, None)[0]
+    for pairing in (0, 2, 1):
+        ops.attn_prefill_t5_pairing(pairing)
+        try:
+            for _ in range(3):
+                out = torch.full((n, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+                ops.attn_prefill_t5(q[0], kc, vc, bt, cu, zero, zero, 1, n, H, KV, hd, 1.0, None, out)
+                assert ops.attn_prefill_t5_status() == 0
+                torch.testing.assert_close(out.double(), ref, rtol=2e-2, atol=2e-2)
+        finally:
+            ops.attn_prefill_t5_pairing(1)
