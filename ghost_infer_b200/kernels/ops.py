@@ -952,7 +952,7 @@ def attn_decode_blocks_per_sm(head_dim: int, fast: bool) -> float:
     elif TUNE["attn_tile_keys"] == 16:
         # a block's shared memory: 16 rows of queries, and four warps' rings of `stages` x (16 keys + 16 values)
         smem = 16 * head_dim * 2 + 4 * attn_decode_stages(head_dim) * 2 * 16 * head_dim * 2 + 1152
-        regs = 5 if head_dim == 64 else 3          # blocks per SM that the registers allow (96 and 168 a thread)
+        regs = 4 if head_dim == 64 else 3          # blocks per SM that the registers allow (121 and 168 a thread)
         per_sm = min(regs, (227 * 1024) // smem)
     else:
         per_sm = 1
