@@ -64,3 +64,20 @@ def test_a_step_asks_the_mixer_for_its_plan_unless_one_was_recorded():
     assert ctx.plan_of(m) == "recorded"
     ctx.fixed_plans, ctx.is_decode = None, False
     assert ctx.plan_of(m) is None                                   # a prompt step has no decode plan
+
+
+def test_a_wait_that_ran_out_inside_a_kernel_is_never_silent(monkeypatch):
+    """The tensor-core kernels bound every wait and record which one ran out; the entry points read the records before
+    they hand anything back (`ops.check_status`)."""
+    from ghost_infer_b200.kernels import ops
+    from ghost_infer_b200.kernels.library import KernelError
+    codes = {"gemm_tc_status": 0, "gemm_stream_status": 0, "attn_prefill_t5_status": 0}
+    for name in codes:
+        monkeypatch.setattr(ops, name, lambda name=name: codes[name])
+    ops.check_status()                                              # nothing recorded: nothing said
+    codes["attn_prefill_t5_status"] = 2
+    with pytest.raises(KernelError, match="prompt attention \\(wait 2\\)"):
+        ops.check_status()
+    codes["gemm_stream_status"] = 3
+    with pytest.raises(KernelError, match="decode product \\(wait 3\\), prompt attention"):
+        ops.check_status()
