@@ -37,11 +37,18 @@ class Layer:
         self.spec = spec
         self.index = index
         p = spec.prefix
-        mixer_norm = lookup("norm", spec.mixer_norm.kind)(spec.mixer_norm.params, p + spec.mixer_norm_prefix)
-        mixer = lookup("mixer", spec.mixer.kind)(spec.mixer.params, p)
-        ffn_norm = lookup("norm", spec.ffn_norm.kind)(spec.ffn_norm.params, p + spec.ffn_norm_prefix)
-        ffn = lookup("feed_forward", spec.ffn.kind)(spec.ffn.params, p)
-        self.block = lookup("block", spec.block)(mixer_norm, mixer, ffn_norm, ffn)
+
+        def build(family, part, prefix):
+            return None if part is None else lookup(family, part.kind)(part.params, prefix)
+
+        mixer_norm = build("norm", spec.mixer_norm, p + spec.mixer_norm_prefix)
+        mixer = build("mixer", spec.mixer, p)
+        ffn_norm = build("norm", spec.ffn_norm, p + spec.ffn_norm_prefix)
+        ffn = build("feed_forward", spec.ffn, p)
+        extra = {e.name: build(e.family, e.spec, p + e.prefix) for e in getattr(spec, "extra", ())}
+        if mixer_norm is None and mixer is None and ffn_norm is None and ffn is None and not extra:
+            raise ValueError(f"layer {index} has no parts")
+        self.block = lookup("block", spec.block)(mixer_norm, mixer, ffn_norm, ffn, **extra)
 
     def weights(self) -> List[WeightSpec]:
         out: List[WeightSpec] = []
@@ -98,7 +105,10 @@ class Model:
         out = []
         for i, e in enumerate(self.spec.schedule):
             mixer = self.layers[e.layer].block.mixer
-            out.append((i, mixer.cache_request(), mixer.state_request(), e.memory_of))
+            if mixer is None:                                  # a layer without a mixer keeps nothing per sequence
+                out.append((i, None, None, e.memory_of))
+            else:
+                out.append((i, mixer.cache_request(), mixer.state_request(), e.memory_of))
         return out
 
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None, max_seq_len: Optional[int] = None,

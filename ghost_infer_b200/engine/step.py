@@ -134,7 +134,7 @@ class Engine:
         layers = getattr(model, "layers", [])
         for e in getattr(model.spec, "schedule", ()):
             m = layers[e.layer].block.mixer
-            if all(m is not seen for seen in self._mixers):
+            if m is not None and all(m is not seen for seen in self._mixers):
                 self._mixers.append(m)
         parts = [getattr(model, n, None) for n in ("embedding", "final_norm", "head")] + [p for layer in layers for p in layer.block.parts()]
         self.plans_on_host = any(getattr(p, "plans_on_host", False) for p in parts)

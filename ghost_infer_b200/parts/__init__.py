@@ -1,7 +1,7 @@
 from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (registers the built-in parts)
 from .base import Block, FeedForward, Mixer, Norm, Part, PositionEncoding, Runtime, WeightSpec
 from .registry import lookup, register, registered, unregister
-from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .spec import ExtraPart, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 __all__ = ["Block", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime", "WeightSpec",
-           "lookup", "register", "registered", "unregister", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry"]
+           "lookup", "register", "registered", "unregister", "ExtraPart", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry"]

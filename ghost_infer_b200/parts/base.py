@@ -11,7 +11,8 @@ Interfaces (a new kind of part implements one of them and registers under a name
   `Mixer.decode_plan(n_seqs, max_kv_len, sm_count, kv_lens=None)` says how it cuts the work of one-token steps of that shape
   (anything hashable, or None); a recorded step keeps the plan it was recorded with (`step.plan_of(self)`).
 * `FeedForward.forward(h, residual, step)`: adds its output to `residual` in place.
-* `Block.forward(x, layer, step, memory)`: runs one layer's parts in its arrangement.
+* `Block.forward(x, step, memory)`: runs one layer's parts in its arrangement.  A block is built from the usual
+  four parts (norm, mixer, norm, feed-forward; any may be None) and the extra parts its specification names.
 
 No part knows which model it is in: sizes, constants and tensor names arrive as parameters (a part's
 tensor names are its prefix plus sub-names that `params["tensor_names"]` may replace).
@@ -116,13 +117,17 @@ class FeedForward(Part):
 
 
 class Block:
-    """An arrangement of one layer's parts."""
+    """An arrangement of one layer's parts: the usual four (any of which an arrangement may lack: None) and whatever
+    else the layer's specification names (`self.extra[name]`)."""
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
+    def __init__(self, mixer_norm: Optional[Norm] = None, mixer: Optional[Mixer] = None, ffn_norm: Optional[Norm] = None,
+                 ffn: Optional[FeedForward] = None, **extra: Part):
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+        self.extra = dict(extra)
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        usual = tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
+        return usual + tuple(self.extra.values())
 
     def forward(self, x: torch.Tensor, step, memory: LayerMemory) -> None:
         raise NotImplementedError

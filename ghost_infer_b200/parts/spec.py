@@ -27,20 +27,34 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class ExtraPart:
+    """A part of a layer beyond the usual four (a norm after the mixer, a second feed-forward, ...): the block finds it
+    as `self.extra[name]`.  `family` is the registry it comes from ("norm", "feed_forward", "position", "mixer": an
+    extra mixer gets no cache or state of its own); `prefix` is where its tensors live under the layer's prefix."""
+    name: str
+    family: str
+    spec: PartSpec
+    prefix: str = ""
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One layer: how its parts are arranged (`block`) and which parts they are.
 
     `prefix` is where the layer's tensors live in the weights file
-    (e.g. "model.layers.3.").
+    (e.g. "model.layers.3.").  The usual arrangement has a norm before the mixer, the mixer, a norm before the
+    feed-forward and the feed-forward; an arrangement that lacks one of them leaves it None, and one that has more
+    names them in `extra`.  The registered block class decides what it does with them.
     """
     prefix: str
     block: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    mixer_norm: Optional[PartSpec] = None
+    mixer: Optional[PartSpec] = None
+    ffn_norm: Optional[PartSpec] = None
+    ffn: Optional[PartSpec] = None
     mixer_norm_prefix: str = "input_layernorm."            # under `prefix`
     ffn_norm_prefix: str = "post_attention_layernorm."     # under `prefix`
+    extra: Tuple[ExtraPart, ...] = ()
 
 
 @dataclass(frozen=True)
