@@ -211,6 +211,15 @@ int gi_attn_decode_tc_merged(void* out, long ldo, float* part_o, float* part_ml,
                              const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd, float scale,
                              int window, int n_splits, int own_tiles, int tile_keys, int stages, void* stream);
 // stages: depth of each warp's ring of tiles, 2 to 4 (0: the default for the head size)
+// The same on rows that are not rotated yet: `qkv` holds one packed [q | k | v] row per sequence as the q/k/v product
+// left it (`settle`: its pending partial sums), `table` [sequences][rot / 2] the (cos, sin) of each sequence's newest
+// position.  The kernel rotates q and k (pairs (i, i + rot / 2)) and stores k and v at position length - 1 itself:
+// gi_rope_cache_write's work for a decode step, inside the attention's launch.
+int gi_attn_decode_tc_rope(void* out, long ldo, float* part_o, float* part_ml, int* counters, int n_counters, const void* qkv,
+                           long ld, void* kcache, void* vcache, const int* block_table, int max_pages, const int* seq_slots,
+                           const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
+                           int own_tiles, int tile_keys, int stages, const float* table, int rot, gi_settle_t settle,
+                           void* stream);
 int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const float* part_ml, int n_seqs, int n_heads,
                     int hd, int n_splits, void* stream);
 

@@ -22,17 +22,30 @@
 #include "common.cuh"
 #include "mma_utils.cuh"
 
+//
+// The kernel can also take the rows as the q/k/v product left them (not rotated, tiles cut between the product's blocks
+// still as partial sums) together with the step's table of angles: every block then sums, rotates and rounds its own
+// query heads into shared memory, and the block that holds a sequence's newest position does the same for the kv
+// head's key and value, stores them in the cache (src/model.rs:1046-1048) and reads them back with the rest of its
+// last tile.  That is the rotary kernel's work (rope_cache.cu, the same roundings) without its launch.
 namespace {
 
 constexpr int WARPS = 4;
 
+// What the kernel needs to rotate and store by itself; table == nullptr: the queries come rotated, the cache is complete.
+struct RopeInside {
+  const float2* table;   // [sequences][rot / 2] (cos, sin) of each sequence's newest position; written by a kernel of this step
+  gi_settle_t st;        // partial sums that the q/k/v product left (partials == nullptr: none)
+  int rot;               // rotated part of a head, pairs (i, i + rot / 2)
+};
+
 template <int HD, int KT, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restrict__ part_o, float* __restrict__ part_ml,
-                      const __nv_bfloat16* q /* written by the kernel before: see gi::pdl_wait */, long ldq, const __nv_bfloat16* __restrict__ kcache,
-                      const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_pages,
+                      const __nv_bfloat16* q /* written by the kernel before: see gi::pdl_wait */, long ldq, __nv_bfloat16* kcache,
+                      __nv_bfloat16* vcache, const int* __restrict__ block_table, int max_pages,
                       const int* __restrict__ seq_slots, const int* __restrict__ seq_lens, int n_heads, int n_kv,
-                      float scale, int window, int n_splits, int own_tiles, int* __restrict__ counters) {
+                      float scale, int window, int n_splits, int own_tiles, int* __restrict__ counters, RopeInside rope) {
   constexpr int CH = HD / 8;                     // 16-byte chunks per row
   constexpr int TILE_BYTES = KT * HD * 2;        // one K or V tile
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;    // K then V
@@ -104,6 +117,25 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
 
+  // Rotating inside: which heads of the packed row this block works on (its query heads; with the newest position in
+  // its slice also the kv head's key and value) and, looked up before the wait, which of the product's blocks hold
+  // pieces of each (the tables of the product's cut are uploaded once and never written by a kernel).
+  __shared__ gi_settle_span s_span[18];
+  const bool inside = rope.table != nullptr;
+  const bool stores = inside && tile_hi == tiles;
+  const int n_items = gcount + (stores ? 2 : 0);
+  auto item_col = [&](int item) {
+    return (item < gcount ? h0 + item : (item == gcount ? n_heads + kvh : n_heads + n_kv + kvh)) * HD;
+  };
+  if (inside) {
+    if (tid < n_items) {
+      gi_settle_span none = {0, 0, 0};
+      s_span[tid] = rope.st.partials != nullptr ? gi_span_of(rope.st, item_col(tid)) : none;
+    }
+    for (int idx = tid; idx < 16 * CH; idx += WARPS * 32)
+      if (idx / CH >= gcount) *reinterpret_cast<uint4*>(q_s + gi::swz<CH>(idx / CH, idx % CH)) = make_uint4(0, 0, 0, 0);
+  }
+
   // prologue: STAGES - 1 tiles in flight; the tile with the sequence's last position only after the wait
   int next = tile_lo + warp;
   int late_stage = -1;
@@ -116,20 +148,72 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
     gi::cp_async_commit();
     next += WARPS;
   }
+  if (inside) __syncthreads();    // the spans are in shared memory
   gi::pdl_wait();
-  if (late_stage >= 0) {          // a short slice: its last tile is among the first ones; fetch it now and let it land
-    issue(tiles - 1, late_stage);
-    gi::cp_async_commit();
-    gi::cp_async_wait<0>();
+  if (!inside) {
+    if (late_stage >= 0) {        // a short slice: its last tile is among the first ones; fetch it now and let it land
+      issue(tiles - 1, late_stage);
+      gi::cp_async_commit();
+      gi::cp_async_wait<0>();
+    }
+    // queries of the group's heads as rows 0..gcount-1 of a 16-row tile (the others zero)
+    for (int idx = tid; idx < 16 * CH; idx += WARPS * 32) {
+      const int r = idx / CH, c = idx % CH;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < gcount) v = *reinterpret_cast<const uint4*>(q + (size_t)b * ldq + (size_t)(h0 + r) * HD + c * 8);
+      *reinterpret_cast<uint4*>(q_s + gi::swz<CH>(r, c)) = v;
+    }
+    __syncthreads();
+  } else {
+    // A thread takes two columns of a head at a time: a rotated pair (i, i + rot / 2), or two neighbours past the
+    // rotated part or of the value.  Each column is what the product stored or the sum of its pieces in the order of
+    // the K ranges, rounded to bfloat16 as the product would have stored it; rotated in 32-bit; rounded again.
+    const int half = rope.rot >> 1;
+    const __nv_bfloat16* row = q + (size_t)b * ldq;
+    const float2* cs = rope.table + (size_t)b * half;
+    size_t cache_row = 0;
+    if (stores) {
+      const int pos = max(len - 1, 0);
+      const int page = slot >= 0 ? gi::ld_step(block_table + (size_t)slot * max_pages + pos / PAGE_TOKENS) : 0;
+      cache_row = (((size_t)page * n_kv + kvh) * PAGE_TOKENS + (pos % PAGE_TOKENS)) * HD;
+    }
+    for (int idx = tid; idx < n_items * (HD / 2); idx += WARPS * 32) {
+      const int item = idx / (HD / 2), i = idx % (HD / 2);
+      const int col0 = item_col(item);
+      const bool is_v = item == gcount + 1;
+      const bool rotate = !is_v && i < half;
+      const int ea = is_v ? 2 * i : (rotate ? i : rope.rot + 2 * (i - half));
+      const int eb = rotate ? i + half : ea + 1;
+      const gi_settle_span spn = s_span[item];
+      float a, c;
+      if (spn.c_first != spn.c_last) {
+        const float2 sum = gi_sum_pieces2(rope.st, spn, b, col0 + ea, col0 + eb);
+        a = __bfloat162float(__float2bfloat16_rn(sum.x));
+        c = __bfloat162float(__float2bfloat16_rn(sum.y));
+      } else {
+        a = __bfloat162float(row[col0 + ea]);
+        c = __bfloat162float(row[col0 + eb]);
+      }
+      if (rotate) gi::rotate_pair(a, c, cs[i], &a, &c);
+      const __nv_bfloat16 va = __float2bfloat16_rn(a), vc = __float2bfloat16_rn(c);
+      if (item < gcount) {
+        *reinterpret_cast<__nv_bfloat16*>(q_s + gi::swz<CH>(item, ea >> 3) + (ea & 7) * 2) = va;
+        *reinterpret_cast<__nv_bfloat16*>(q_s + gi::swz<CH>(item, eb >> 3) + (eb & 7) * 2) = vc;
+      } else {
+        __nv_bfloat16* dst = (is_v ? vcache : kcache) + cache_row;
+        dst[ea] = va;
+        dst[eb] = vc;
+      }
+    }
+    // the newest key and value go through memory: stored here, fetched below like every other row of the last tile
+    if (stores) __threadfence();
+    __syncthreads();
+    if (late_stage >= 0) {
+      issue(tiles - 1, late_stage);
+      gi::cp_async_commit();
+      gi::cp_async_wait<0>();
+    }
   }
-  // queries of the group's heads as rows 0..gcount-1 of a 16-row tile (the others zero)
-  for (int idx = tid; idx < 16 * CH; idx += WARPS * 32) {
-    const int r = idx / CH, c = idx % CH;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < gcount) v = *reinterpret_cast<const uint4*>(q + (size_t)b * ldq + (size_t)(h0 + r) * HD + c * 8);
-    *reinterpret_cast<uint4*>(q_s + gi::swz<CH>(r, c)) = v;
-  }
-  __syncthreads();
   uint32_t qf[HD / 16][4];
 #pragma unroll
   for (int ks = 0; ks < HD / 16; ++ks) {
@@ -360,8 +444,8 @@ attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restri
 
 template <int HD, int KT, int STAGES>
 int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, float* pml, const __nv_bfloat16* q, long ldq,
-           const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int max_pages, const int* slots, const int* lens,
-           int H, int KV, float scale, int window, int n_splits, int own_tiles, int* counters) {
+           __nv_bfloat16* kc, __nv_bfloat16* vc, const int* bt, int max_pages, const int* slots, const int* lens,
+           int H, int KV, float scale, int window, int n_splits, int own_tiles, int* counters, RopeInside rope) {
   constexpr size_t ring = (size_t)WARPS * STAGES * 2 * KT * HD * 2;
   constexpr size_t merge = (size_t)(WARPS * 16 * (HD + 8) + 2 * WARPS * 16) * sizeof(float);
   constexpr size_t smem = 16 * HD * 2 + (ring > merge ? ring : merge);
@@ -374,7 +458,7 @@ int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, f
     if (dev >= 0) configured[dev] = true;
   }
   return gi::check(gi::launch(kern, grid, dim3(WARPS * 32), smem, s, out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV,
-                              scale, window, n_splits, own_tiles, counters), "attention decode (tensor cores)");
+                              scale, window, n_splits, own_tiles, counters, rope), "attention decode (tensor cores)");
 }
 
 }  // namespace
@@ -416,11 +500,11 @@ extern "C" int gi_attn_decode_tc_ex(void* out, long ldo, float* part_o, float* p
 // span, whatever n_splits is (which must cover the longest span); 0: each span is cut into n_splits equal slices.
 // stages: depth of each warp's ring of tiles (2, 3 or 4; 0: 3 at head size 128, 4 at head size 64).  Fewer stages
 // mean less shared memory per block and so more blocks per SM.
-extern "C" int gi_attn_decode_tc_merged(void* out, long ldo, float* part_o, float* part_ml, int* counters, int n_counters,
-                                        const void* q, long ldq, const void* kcache, const void* vcache,
-                                        const int* block_table, int max_pages, const int* seq_slots, const int* seq_lens,
-                                        int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
-                                        int own_tiles, int tile_keys, int stages, void* stream) {
+namespace {
+int decode_tc_impl(void* out, long ldo, float* part_o, float* part_ml, int* counters, int n_counters, const void* q, long ldq,
+                   void* kcache, void* vcache, const int* block_table, int max_pages, const int* seq_slots, const int* seq_lens,
+                   int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits, int own_tiles, int tile_keys,
+                   int stages, RopeInside rope, void* stream) {
   if (n_seqs <= 0) return GI_OK;
   if (own_tiles < 0) return gi::fail(GI_ERR_ARG, "attention: tiles per slice cannot be negative");
   if (tile_keys != 16 && tile_keys != 32) return gi::fail(GI_ERR_ARG, "attention decode (tensor cores): tiles of %d keys, 16 or 32", tile_keys);
@@ -441,8 +525,8 @@ extern "C" int gi_attn_decode_tc_merged(void* out, long ldo, float* part_o, floa
   int rc;
 #define GI_DECODE_TC(HD_, KT_, ST_)                                                                                          \
   rc = launch<HD_, KT_, ST_>(grid, s, (__nv_bfloat16*)out, ldo, part_o, part_ml, (const __nv_bfloat16*)q, ldq,               \
-                             (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table, max_pages, seq_slots, \
-                             seq_lens, n_heads, n_kv, scale, window, n_splits, own_tiles, counters)
+                             (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, block_table, max_pages, seq_slots,             \
+                             seq_lens, n_heads, n_kv, scale, window, n_splits, own_tiles, counters, rope)
   if (stages == 0) stages = hd == 128 ? 3 : 4;
   if (stages < 2 || stages > 4) return gi::fail(GI_ERR_ARG, "attention decode (tensor cores): rings of %d stages, 2 to 4", stages);
   if (hd == 128 && tile_keys == 32) GI_DECODE_TC(128, 32, 3);
@@ -456,6 +540,37 @@ extern "C" int gi_attn_decode_tc_merged(void* out, long ldo, float* part_o, floa
   if (rc != GI_OK) return rc;
   if (n_splits > 1 && counters == nullptr) return gi_attn_combine(out, ldo, GI_BF16, part_o, part_ml, n_seqs, n_heads, hd, n_splits, stream);
   return GI_OK;
+}
+}  // namespace
+
+extern "C" int gi_attn_decode_tc_merged(void* out, long ldo, float* part_o, float* part_ml, int* counters, int n_counters,
+                                        const void* q, long ldq, const void* kcache, const void* vcache,
+                                        const int* block_table, int max_pages, const int* seq_slots, const int* seq_lens,
+                                        int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
+                                        int own_tiles, int tile_keys, int stages, void* stream) {
+  const RopeInside none = {nullptr, {nullptr, nullptr, nullptr, nullptr, 0}, 0};
+  // without a table of angles the kernel only reads the cache
+  return decode_tc_impl(out, ldo, part_o, part_ml, counters, n_counters, q, ldq, const_cast<void*>(kcache), const_cast<void*>(vcache),
+                        block_table, max_pages, seq_slots, seq_lens, n_seqs, n_heads, n_kv, hd, scale, window, n_splits, own_tiles,
+                        tile_keys, stages, none, stream);
+}
+
+// The same for rows that are not rotated yet (one row per sequence: the packed [q | k | v] of its newest token, as the
+// q/k/v product left it; `settle`: that product's pending partial sums, partials == nullptr for none).  The kernel
+// rotates q and k by `table` ([sequences][rot / 2] (cos, sin)), pairs (i, i + rot / 2), and stores k and v at each
+// sequence's position (length - 1) itself: the work of gi_rope_cache_write for a decode step, without its launch.
+extern "C" int gi_attn_decode_tc_rope(void* out, long ldo, float* part_o, float* part_ml, int* counters, int n_counters,
+                                      const void* qkv, long ld, void* kcache, void* vcache, const int* block_table,
+                                      int max_pages, const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads,
+                                      int n_kv, int hd, float scale, int window, int n_splits, int own_tiles, int tile_keys,
+                                      int stages, const float* table, int rot, gi_settle_t settle, void* stream) {
+  if (!table) return gi::fail(GI_ERR_ARG, "attention decode with rotation: no table of angles");
+  if (rot < 0 || rot > hd || rot % 2 != 0) return gi::fail(GI_ERR_ARG, "attention decode with rotation: rotary size %d does not fit head size %d", rot, hd);
+  if (settle.partials != nullptr && settle.nt < n_seqs)
+    return gi::fail(GI_ERR_ARG, "attention decode with rotation: partial sums of a product of %d rows for %d sequences", settle.nt, n_seqs);
+  const RopeInside rope = {(const float2*)table, settle, rot};
+  return decode_tc_impl(out, ldo, part_o, part_ml, counters, n_counters, qkv, ld, kcache, vcache, block_table, max_pages, seq_slots,
+                        seq_lens, n_seqs, n_heads, n_kv, hd, scale, window, n_splits, own_tiles, tile_keys, stages, rope, stream);
 }
 
 // ------------------------------------------------------------------------------------------------------

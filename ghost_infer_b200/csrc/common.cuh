@@ -47,6 +47,14 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // read-only-path) load would return it.  These loads go to the L2 cache, which the upload went through.
 __device__ __forceinline__ int ld_step(const int* p) { return __ldcg(p); }
 
+// One rotary pair's rotation with its roundings spelled out, so that every kernel that rotates (the rotary kernels, the
+// decode attention that rotates its own rows) gives the same bits: (a cos - b sin, a sin + b cos), each as one product
+// rounded, then a fused multiply-add.  cs = (cos, sin).
+__device__ __forceinline__ void rotate_pair(float a, float b, float2 cs, float* ra, float* rb) {
+  *ra = __fmaf_rn(a, cs.x, -__fmul_rn(b, cs.y));
+  *rb = __fmaf_rn(a, cs.y, __fmul_rn(b, cs.x));
+}
+
 __device__ __forceinline__ float ldf(const float* p) { return *p; }
 __device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void stf(float* p, float v) { *p = v; }

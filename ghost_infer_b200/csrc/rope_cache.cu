@@ -24,12 +24,7 @@ __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restr
   table[idx] = make_float2(c, s);
 }
 
-// One pair's rotation with its roundings spelled out, so that both kernels below (and any other) give the same bits:
-// (a cos - b sin, a sin + b cos), each as one product rounded, then a fused multiply-add.
-__device__ __forceinline__ void rotate_pair(float a, float b, float2 cs, float* ra, float* rb) {
-  *ra = __fmaf_rn(a, cs.x, -__fmul_rn(b, cs.y));
-  *rb = __fmaf_rn(a, cs.y, __fmul_rn(b, cs.x));
-}
+using gi::rotate_pair;
 
 // The value of column f of token t's packed row: what the product stored, or, for a tile of 128 columns that was cut
 // between blocks of a deferred product (`sp`, looked up before the dependency wait), the sum of the partial sums in

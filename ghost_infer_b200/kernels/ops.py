@@ -12,7 +12,7 @@ import ctypes
 import os
 import weakref
 from ctypes import c_float, c_int, c_long, c_void_p
-from typing import Dict, Optional
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -64,6 +64,7 @@ def _bind():
         "gi_attn_decode_tc": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_attn_decode_tc_ex": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P],
         "gi_attn_decode_tc_merged": [P, L, P, P, P, I, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P],
+        "gi_attn_decode_tc_rope": [P, L, P, P, P, I, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P, I, SettleT, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
     }
     for name, argtypes in sigs.items():
@@ -464,7 +465,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 
 # Choices measured on a B200; benchmarks may override them to try alternatives.
 TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16,
-        "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3}
+        "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3, "attn_rope_inside": False}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -853,13 +854,16 @@ def attn_decode_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
                    head_dim: int, scale: float, window: Optional[int], n_splits: int, out: torch.Tensor,
                    part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
                    tile_keys: Optional[int] = None, own_tiles: int = 0, merge_inside: Optional[bool] = None,
-                   stages: Optional[int] = None) -> torch.Tensor:
+                   stages: Optional[int] = None, rope: Optional[Tuple[torch.Tensor, int]] = None) -> torch.Tensor:
     """`tile_keys`: 32 (one block per SM, deep rings) or 16 (two blocks per SM); default TUNE["attn_tile_keys"].
     `own_tiles` > 0: slices of that many tiles of each sequence's own span (`n_splits` must then cover the longest
     sequence); 0: every span is cut into `n_splits` equal slices.  `merge_inside`: the slices are merged by the block
-    that finishes last instead of by a second kernel (default TUNE["attn_merge_inside"])."""
+    that finishes last instead of by a second kernel (default TUNE["attn_merge_inside"]).
+    `rope` = (table of angles [sequences, pairs, 2], rotary size): `q` holds the packed [q | k | v] rows as the
+    product left them (partial sums may be pending); the kernel rotates q and k by the table, pairs (i, i + half),
+    and stores k and v at each sequence's newest position itself, instead of `rope_cache_write` before it."""
     lib = _bind()
-    _cuda(q, "queries")
+    _cuda(q, "queries", settles=rope is not None)
     ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
     if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("the tensor-core decode attention takes bfloat16 queries, cache and output")
@@ -878,15 +882,29 @@ def attn_decode_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
     counters = None
     if inside and n_splits > 1 and n_seqs * n_kv * chunks <= _ATTN_COUNTERS:
         counters = _attn_merge_counters(q.device)
-    _check(lib, lib.gi_attn_decode_tc_merged(
-        out.data_ptr(), ldo, part_o.data_ptr() if part_o is not None else None,
-        part_ml.data_ptr() if part_ml is not None else None,
-        counters.data_ptr() if counters is not None else None, counters.numel() if counters is not None else 0,
-        q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(),
-        _i32(block_table, "block table"), block_table.shape[1], _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"),
-        n_seqs, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(n_splits), int(own_tiles),
-        tile_keys, int(stages if stages is not None else attn_decode_stages(head_dim)), _stream()),
-        2 if (n_splits > 1 and counters is None) else 1)
+    args = (out.data_ptr(), ldo, part_o.data_ptr() if part_o is not None else None,
+            part_ml.data_ptr() if part_ml is not None else None,
+            counters.data_ptr() if counters is not None else None, counters.numel() if counters is not None else 0,
+            q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(),
+            _i32(block_table, "block table"), block_table.shape[1], _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"),
+            n_seqs, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(n_splits), int(own_tiles),
+            tile_keys, int(stages if stages is not None else attn_decode_stages(head_dim)))
+    n_launches = 2 if (n_splits > 1 and counters is None) else 1
+    if rope is None:
+        _check(lib, lib.gi_attn_decode_tc_merged(*args, _stream()), n_launches)
+        return out
+    table, rotary_dim = rope
+    if q.shape[0] < n_seqs or q.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError(f"q/k/v rows are {tuple(q.shape)}, wanted {n_seqs} rows of {(n_heads + 2 * n_kv) * head_dim}")
+    if table.dtype != torch.float32 or not table.is_contiguous() or table.numel() != q.shape[0] * (rotary_dim // 2) * 2:
+        raise KernelError("the table of angles must hold rows x rotary_dim / 2 float32 (cos, sin) pairs")
+    if tuple(kcache.shape[1:]) != (n_kv, 64, head_dim) or not kcache.is_contiguous() or not vcache.is_contiguous():
+        raise KernelError(f"cache pages must be contiguous [pages, {n_kv}, 64, {head_dim}], got {tuple(kcache.shape)}")
+    pending = _take_pending(q)
+    if pending is not None and not pending[1]:
+        raise KernelError("the decode attention met partial sums of an accumulating product")
+    settle_t = pending[0] if pending is not None else SettleT(None, None, None, None, 0)
+    _check(lib, lib.gi_attn_decode_tc_rope(*args, table.data_ptr(), int(rotary_dim), settle_t, _stream()), n_launches)
     return out
 
 
@@ -1004,13 +1022,24 @@ def attn_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, 
     return 1, 0
 
 
+def attn_rope_inside_ok(qkv: torch.Tensor, memory, step, head_dim: int) -> bool:
+    """Whether a step's rotation and cache write can be left to its attention kernel (`attention(..., rope=)`): a
+    decode step on the tensor-core kernel that writes its own cache."""
+    return bool(TUNE["attn_rope_inside"] and step.is_decode and memory.k is not None and memory.writes
+                and attn_decode_tc_ok(qkv, memory.k, head_dim) and qkv.shape[0] == step.n_seqs)
+
+
 def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim: int, scale: float,
-              window: Optional[int], out: torch.Tensor, plan=None) -> torch.Tensor:
+              window: Optional[int], out: torch.Tensor, plan=None, rope=None) -> torch.Tensor:
     """Attention of a step's tokens over the cache (which already holds the step's own keys and values).
     The queries are the first n_heads * head_dim columns of the packed rows `qkv`.  `plan`: what
-    `attn_decode_plan` gave for a decode step (worked out here when absent)."""
+    `attn_decode_plan` gave for a decode step (worked out here when absent).  `rope` = (table, rotary size), only
+    where `attn_rope_inside_ok` holds: the rows are not rotated and the cache lacks the step's keys and values;
+    the kernel does both."""
     if memory.k is None:
         raise KernelError("attention needs a cache to read from")
+    if rope is not None and not attn_rope_inside_ok(qkv, memory, step, head_dim):
+        raise KernelError("this step's attention cannot rotate and store by itself")
     if step.is_decode:
         fast = attn_decode_tc_ok(qkv, memory.k, head_dim)
         if plan is None:
@@ -1023,7 +1052,7 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
         if fast:
             return attn_decode_tc(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
                                   step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml,
-                                  own_tiles=own_tiles)
+                                  own_tiles=own_tiles, rope=rope)
         return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens,
                                    step.n_seqs, n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml,
                                    own_tiles=own_tiles)

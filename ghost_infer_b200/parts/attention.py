@@ -79,9 +79,12 @@ class GqaAttention(Mixer):
                     qkv = linear(h, self.w_qkv, out_dtype=self.rt.dtype)
             else:
                 qkv = linear(h, self.w_qkv, out_dtype=self.rt.dtype)
+        inside = None
         with ops.bucket("rope+cache"):
             if self.position is not None:
-                self.position.encode_and_store(qkv, step, memory, self.n_heads, self.n_kv, self.head_dim)
+                inside = self.position.left_to_attention(qkv, step, memory, self.n_heads, self.n_kv, self.head_dim)
+                if inside is None:
+                    self.position.encode_and_store(qkv, step, memory, self.n_heads, self.n_kv, self.head_dim)
             else:
                 ops.rope_cache_write(qkv, None, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
                                      self.n_heads, self.n_kv, self.head_dim, 0, False,
@@ -89,6 +92,6 @@ class GqaAttention(Mixer):
         with ops.bucket("attention"):
             att = torch.empty((h.shape[0], self.q_dim), dtype=self.rt.dtype, device=h.device)
             ops.attention(qkv, memory, step, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, att,
-                          plan=step.plan_of(self))
+                          plan=step.plan_of(self), rope=inside)
         with ops.bucket("out matmul"):
             linear(att, self.w_o, out=residual, accumulate=True)

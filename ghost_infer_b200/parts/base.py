@@ -92,6 +92,13 @@ class PositionEncoding(Part):
                          head_dim: int) -> None:
         raise NotImplementedError
 
+    def left_to_attention(self, qkv: torch.Tensor, step, memory: LayerMemory, n_heads: int, n_kv_heads: int,
+                          head_dim: int):
+        """An encoding whose work for this step the attention kernel can do on the way (a rotation by a table of
+        angles) returns what `ops.attention(..., rope=)` takes, and `encode_and_store` is then not called for the
+        step.  None (the default): the encoding runs as a step of its own."""
+        return None
+
 
 class Mixer(Part):
     def cache_request(self) -> Optional[CacheRequest]:

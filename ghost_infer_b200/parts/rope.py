@@ -68,13 +68,23 @@ class Rotary(PositionEncoding):
         sc = self.scaling
         self.table_key = ("rotary", self.rotary_dim, self.theta, repr(sorted(sc.items())) if sc else None)
 
-    def encode_and_store(self, qkv, step, memory, n_heads, n_kv_heads, head_dim) -> None:
+    def _table(self, step):
         # the angles depend on the step's positions and this encoding's constants only: one table per step
         # serves every layer that rotates the same way
         table = step.shared.get(self.table_key)
         if table is None:
             table = ops.rope_table(step.positions, self.inv_freq)
             step.shared[self.table_key] = table
+        return table
+
+    def left_to_attention(self, qkv, step, memory, n_heads, n_kv_heads, head_dim):
+        # one token per sequence: the decode attention's blocks rotate the heads they read and the newest key
+        if self.pairing != "half" or self.rotary_dim < 2 or not ops.attn_rope_inside_ok(qkv, memory, step, head_dim):
+            return None
+        return self._table(step), self.rotary_dim
+
+    def encode_and_store(self, qkv, step, memory, n_heads, n_kv_heads, head_dim) -> None:
+        table = self._table(step)
         ops.rope_cache_write(qkv, table, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
                              n_heads, n_kv_heads, head_dim, self.rotary_dim,
                              self.pairing == "adjacent", memory.writes and memory.k is not None)

@@ -800,11 +800,63 @@ def test_rope_and_cache_write_for_a_prompt(dtype, hd, rot):
     assert float(kc[0].abs().sum()) == 0
 
 
+@pytest.mark.parametrize("H,KV,hd,rot", [(32, 8, 128, 128), (6, 2, 64, 32), (5, 1, 64, 64), (40, 2, 128, 64), (8, 8, 128, 128)])
+@pytest.mark.parametrize("window,splits", [(None, 1), (None, 5), (100, 3)])
+@pytest.mark.parametrize("defer", [False, True])
+def test_decode_attention_rotates_and_stores_by_itself(H, KV, hd, rot, window, splits, defer):
+    """The decode attention given the rows as the q/k/v product left them (with partial sums pending or not) and the
+    table of angles, against the rotary kernel followed by the attention: the same bits in the output and in every
+    byte of the cache.  The cache rows of the newest positions hold NaN beforehand, so a block that reads its last tile
+    before the key and value are stored shows; lengths of 1, at page and tile edges, and long ones; a group of 20 heads
+    (two blocks per kv head, both of which store); a rotated part smaller than the head."""
+    lens = [1, 31, 64, 65, 700, 333, 96, 129, 16, 17]
+    B, S, d = len(lens), 704, 264
+    k = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=13)
+    v = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=14)
+    a, w = rnd(B, d, dtype=torch.bfloat16, seed=60), rnd((H + 2 * KV) * hd, d, dtype=torch.bfloat16, seed=61, scale=0.1)
+    slots, lens_t = torch.arange(B, dtype=torch.int32, device=DEV), torch.tensor(lens, dtype=torch.int32, device=DEV)
+    pos = lens_t - 1
+    table = ops.rope_table(pos, torch.from_numpy(pl.rotary_inv_freq(rot, 10000.0, None)).to(DEV))
+    results = []
+    for inside in (False, True, True):
+        kc, vc, bt = paged_from_dense(k, v, lens, seed=4)
+        for b, n in enumerate(lens):
+            page, off = int(bt[b, (n - 1) // 64]), (n - 1) % 64
+            kc[page, :, off] = float("nan")
+            vc[page, :, off] = float("nan")
+        if defer:
+            with ops.defer_store():
+                qkv = ops.linear(a, w, out_dtype=torch.bfloat16)
+            assert ops.has_pending(qkv)
+        else:
+            qkv = ops.linear(a, w, out_dtype=torch.bfloat16)
+        out = torch.full((B, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        part_o = torch.full((B * H * splits * hd,), float("nan"), device=DEV)
+        part_ml = torch.full((B * H * splits * 2,), float("nan"), device=DEV)
+        if not inside:
+            ops.rope_cache_write(qkv, table, pos, slots, bt, kc, vc, H, KV, hd, rot, False, True)
+        ops.attn_decode_tc(qkv, kc, vc, bt, slots, lens_t, B, H, KV, hd, 0.17, window, splits, out, part_o, part_ml,
+                           rope=(table, rot) if inside else None)
+        assert not ops.has_pending(qkv)
+        assert not bool(torch.isnan(out.float()).any())
+        results.append((out, kc, vc))
+    for out, kc, vc in results[1:]:
+        assert torch.equal(out, results[0][0])
+        # NaN poison fills the same unused rows in every run: compare the bits
+        assert torch.equal(kc.view(torch.int16), results[0][1].view(torch.int16))
+        assert torch.equal(vc.view(torch.int16), results[0][2].view(torch.int16))
+    # and the stored value is the product's
+    ref_v = (a.double() @ w.double().T)[:, (H + KV) * hd:]
+    got = torch.stack([results[1][2][int(bt[b, (n - 1) // 64]), :, (n - 1) % 64].reshape(KV * hd) for b, n in enumerate(lens)])
+    torch.testing.assert_close(got.double(), ref_v, rtol=1.6e-2, atol=1.6e-2)
+
+
+@pytest.mark.parametrize("inside", [False, True])
 @pytest.mark.parametrize("H,KV,hd,lens,hidden,splits", [(4, 2, 64, [102, 102], 192, 2), (4, 2, 64, [140, 111, 7], 192, 3),
                                                          (3, 1, 128, [102, 90], 264, 2), (32, 8, 64, [700] * 4, 2048, 4),
                                                          (32, 8, 128, [513] * 3, 4096, 3)])
-def test_a_replayed_step_reads_what_its_own_kernels_wrote(H, KV, hd, lens, hidden, splits):
-    """Product, rotation + cache write and decode attention recorded in a CUDA graph with dependent launch: each
+def test_a_replayed_step_reads_what_its_own_kernels_wrote(H, KV, hd, lens, hidden, splits, inside):
+    """Product, rotation + cache write (a kernel of its own, or inside the attention) and decode attention recorded in a CUDA graph with dependent launch: each
     kernel starts while the one before it still runs and must not read that kernel's results before its dependency
     wait.  The graph's buffers hold other values before the first replay (the queries' rows are filled with NaN, the
     cache rows of the new position with zeros), so a read that comes too early shows.  Compared bit for bit with the
@@ -826,11 +878,13 @@ def test_a_replayed_step_reads_what_its_own_kernels_wrote(H, KV, hd, lens, hidde
         with ops.defer_store():
             qkv = ops.linear(h, w, out_dtype=torch.bfloat16)
         table = ops.rope_table(pos, inv)
-        ops.rope_cache_write(qkv, table, pos, slots, bt, kc, vc, H, KV, hd, hd, False, True)
+        if not inside:
+            ops.rope_cache_write(qkv, table, pos, slots, bt, kc, vc, H, KV, hd, hd, False, True)
         out = torch.empty(B, H * hd, dtype=torch.bfloat16, device=DEV)
         po = torch.empty(B * H * splits * hd, device=DEV)
         pml = torch.empty(B * H * splits * 2, device=DEV)
-        ops.attn_decode_tc(qkv, kc, vc, bt, slots, lens_t, B, H, KV, hd, 0.125, None, splits, out, po, pml)
+        ops.attn_decode_tc(qkv, kc, vc, bt, slots, lens_t, B, H, KV, hd, 0.125, None, splits, out, po, pml,
+                           rope=(table, hd) if inside else None)
         kept.update(qkv=qkv, table=table, po=po, pml=pml)
         return out
 

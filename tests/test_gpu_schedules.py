@@ -242,6 +242,43 @@ def test_graph_runner_across_length_buckets(engines, tiny_configs, name, dtype):
         cache.close_slot(s)
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_decode_with_the_rotation_left_to_the_attention(model_dirs, tiny_configs, name):
+    """The position encoding may leave a decode step's rotation and cache write to the attention kernel
+    (`PositionEncoding.left_to_attention`, switched by `TUNE["attn_rope_inside"]`): through the runner that generation
+    uses, across a page edge and a bucket edge, the logits are those of the plain implementation and, bit for bit,
+    those of the step with the rotary kernel; one launch per layer fewer."""
+    from ghost_infer_b200.kernels import ops
+    cfg = tiny_configs[name]
+    d = model_dirs(name, "bfloat16")
+    starts, steps = [250, 61, 1], 70
+    seqs = [tokens_for(cfg, s + steps, 130 + i) for i, s in enumerate(starts)]
+    refs = [plain_logits(d, t) for t in seqs]
+    outs, launches = [], []
+    was = ops.TUNE["attn_rope_inside"]
+    try:
+        for inside in (False, True):
+            ops.TUNE["attn_rope_inside"] = inside
+            eng = make_engine(d, "bfloat16")            # a fresh engine: recorded steps keep the kernels they were recorded with
+            cache = eng.cache
+            slots = [cache.open_slot() for _ in seqs]
+            eng.step([gi.StepEntry(s, t[:n], []) for s, t, n in zip(slots, seqs, starts)])
+            runner = eng.decoder(slots)
+            got = []
+            for j in range(steps):
+                got.append(runner.forward(tokens=[t[n + j] for t, n in zip(seqs, starts)]).cpu().numpy().copy())
+            outs.append(np.stack(got))
+            launches.append(runner.launches_per_step())
+            for s in slots:
+                cache.close_slot(s)
+    finally:
+        ops.TUNE["attn_rope_inside"] = was
+    for i in range(3):
+        check_logits(outs[1][:, i], refs[i][starts[i]:], "bfloat16", f"{name} rotation inside the attention, request {i}")
+    assert np.array_equal(outs[0], outs[1])
+    assert launches[0] - launches[1] == cfg["num_hidden_layers"]
+
+
 # ---- (e) a model with a window, through the entry point ------------------------------------------------------
 def window_spec_for(window):
     def build(cfg):
