@@ -250,12 +250,32 @@ class SequenceCache:
     # ---- device side ------------------------------------------------------------------------
     def sync_tables(self) -> None:
         """Copies the changed stretches of the page tables to the device, on the stream of the kernels
-        that read them.  Only rows that gained pages since the last call are touched."""
+        that read them.  Only rows that gained pages since the last call are touched.
+
+        The host does not wait: the stretches are first copied into page-locked staging memory of this call's own
+        (a copy from ordinary memory would hold the host until everything queued on the stream has run, one whole step
+        in a decode loop that otherwise runs ahead of the device), and go to the device from there in stream order.
+        The staging memory is handed back to torch's allocator, which reuses it only after those copies ran; the
+        host's own table may change again at once (a slot closed, a page taken) without touching what is under way."""
+        on_gpu = self.device.type == "cuda"
         for g in self._groups:
             if not g.dirty:
                 continue
-            for slot, (lo, hi) in g.dirty.items():
-                g.table_dev[slot, lo:hi].copy_(torch.from_numpy(g.table_host[slot, lo:hi]))
+            if not on_gpu:
+                for slot, (lo, hi) in g.dirty.items():
+                    g.table_dev[slot, lo:hi].copy_(torch.from_numpy(g.table_host[slot, lo:hi]))
+                g.dirty.clear()
+                continue
+            stretches = [(slot, lo, hi) for slot, (lo, hi) in g.dirty.items() if hi > lo]
+            total = sum(hi - lo for _, lo, hi in stretches)
+            if total:
+                stage = torch.empty((total,), dtype=torch.int32, pin_memory=True)
+                view = stage.numpy()
+                at = 0
+                for slot, lo, hi in stretches:
+                    view[at:at + hi - lo] = g.table_host[slot, lo:hi]
+                    g.table_dev[slot, lo:hi].copy_(stage[at:at + hi - lo], non_blocking=True)
+                    at += hi - lo
             g.dirty.clear()
 
     def memory(self, entry: int) -> LayerMemory:

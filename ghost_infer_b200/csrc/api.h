@@ -136,6 +136,9 @@ int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const void* W, fl
                            int M, int N, int K, long lda, long ldw, long ldo, int use_pdl, const void* next_W, int next_N,
                            int next_K, long next_ldw, int next_mode, int units_ahead, void* stream);
 int gi_gemm_stream_status(int* status);
+// percent > 0: a product that finishes its own sums and has fewer 128-row tiles than SMs, but at least `percent` of
+// them, runs one block per tile, so that no tile is cut between blocks; 0: always one block per SM.  Returns the old value.
+int gi_gemm_stream_whole_tiles(int percent);
 // Time stamps of the streamed products' blocks, for a timeline of a decode step: see gemm_stream.cu.
 long gi_gemm_stream_timeline(unsigned long long* buf, int slots);
 int gi_gemm_stream_geometry(int M, int N, int K, int* n_ctas, int* kb_per_tile, int* nt);

@@ -403,6 +403,20 @@ int sm_count() {
   return n;
 }
 
+// How many blocks a launch takes.  Usually one per SM, the units cut evenly between them.  A product that finishes its
+// sums itself and has a few tiles fewer than there are SMs takes one block per tile instead (g_whole_percent: at least
+// that share of the SMs, 0: never): every tile is then whole, no block ends with an exchange of partial sums, and the
+// remaining SMs are fewer than the exchange costs.
+int g_whole_percent = 80;   // measured: from about 118 tiles on 148 SMs one block per tile is faster at every K tried, below that the cut is
+int grid_for(int N, int K, int mode) {
+  const int n_tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
+  const long units = (long)n_tiles * ((K + BK - 1) / BK);
+  const int sms = sm_count();
+  const bool deferred = mode == GI_SKINNY_ACCUM_DEFER || mode == GI_SKINNY_STORE_DEFER;
+  if (!deferred && g_whole_percent > 0 && n_tiles < sms && (long)n_tiles * 100 >= (long)sms * g_whole_percent) return n_tiles;
+  return (int)(units < sms ? units : sms);
+}
+
 template <int NT, int STAGES, int MODE>
 int launch(void* out, const CUtensorMap& mw, const CUtensorMap& ma, float* scratch, int* counters, int M, int N, int K, long ldo,
            int use_pdl, cudaStream_t s, const CUtensorMap& mn, Next next) {
@@ -415,8 +429,7 @@ int launch(void* out, const CUtensorMap& mw, const CUtensorMap& ma, float* scrat
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "streamed product: %s", cudaGetErrorString(e));
     if (dev >= 0) configured[dev] = true;
   }
-  const long units = (long)((N + TILE_ROWS - 1) / TILE_ROWS) * ((K + BK - 1) / BK);
-  const int grid = (int)(units < sm_count() ? units : sm_count());
+  const int grid = grid_for(N, K, MODE);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(THREADS);
@@ -487,8 +500,7 @@ extern "C" int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const 
   CUtensorMap mn = mw;
   if (next_W && units_ahead > 0 && next_N > 0 && next_K > 0 && next_K % 8 == 0 && next_ldw % 8 == 0 && !((uintptr_t)next_W & 15) &&
       gi::tensor_map_2d(&mn, next_W, next_N, next_K, next_ldw, TILE_ROWS) == GI_OK) {
-    const long units_n = (long)((next_N + TILE_ROWS - 1) / TILE_ROWS) * ((next_K + BK - 1) / BK);
-    next = {next_N, next_K, (int)(units_n < sm_count() ? units_n : sm_count()), units_ahead,
+    next = {next_N, next_K, grid_for(next_N, next_K, next_mode), units_ahead,
             (next_mode == GI_SKINNY_ACCUM_DEFER || next_mode == GI_SKINNY_STORE_DEFER) ? 1 : 0, nullptr};
   } else {
     mn = mw;
@@ -503,8 +515,7 @@ extern "C" int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const 
 // How a launch with these sizes cuts its work: blocks, units per tile, token-tile width.  The kernel that settles
 // deferred partial sums (gi_rmsnorm with a settle descriptor, gi_settle) needs exactly these numbers.
 extern "C" int gi_gemm_stream_geometry(int M, int N, int K, int* n_ctas, int* kb_per_tile, int* nt) {
-  const long units = (long)((N + TILE_ROWS - 1) / TILE_ROWS) * ((K + BK - 1) / BK);
-  *n_ctas = (int)(units < sm_count() ? units : sm_count());
+  *n_ctas = grid_for(N, K, GI_SKINNY_ACCUM_DEFER);
   *kb_per_tile = (K + BK - 1) / BK;
   *nt = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   return GI_OK;
@@ -519,6 +530,14 @@ extern "C" long gi_gemm_stream_timeline(unsigned long long* buf, int slots) {
   g_timeline_slots = slots > 0 ? slots : 1;
   g_timeline_launches = 0;
   return n;
+}
+
+// percent > 0: a product that finishes its own sums and has fewer tiles than SMs, but at least `percent` of them, runs
+// one block per tile (no tile is cut); 0: always one block per SM.  Returns the value before.
+extern "C" int gi_gemm_stream_whole_tiles(int percent) {
+  const int was = g_whole_percent;
+  g_whole_percent = percent < 0 ? 0 : (percent > 100 ? 100 : percent);
+  return was;
 }
 
 extern "C" int gi_gemm_stream_status(int* status) {

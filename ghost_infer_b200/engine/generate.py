@@ -200,7 +200,8 @@ class GenerationLoop:
                 tok_in = cur
             else:
                 pos = {i: r for r, i in enumerate(order)}
-                rows = torch.tensor([pos[i] for i in feed], dtype=torch.int64).to(cur.device, non_blocking=True)
+                # from page-locked memory: a copy from ordinary memory would hold the host until the device has caught up
+                rows = torch.tensor([pos[i] for i in feed], dtype=torch.int64, pin_memory=on_gpu).to(cur.device, non_blocking=True)
                 tok_in = cur.index_select(0, rows)
             want = [slots[i] for i in feed]
             if runner is None or runner.slots != want:

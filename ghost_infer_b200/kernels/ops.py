@@ -465,7 +465,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 
 # Choices measured on a B200; benchmarks may override them to try alternatives.
 TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16,
-        "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3, "attn_rope_inside": False}
+        "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3, "attn_rope_inside": False, "stream_whole_percent": 80}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -496,6 +496,9 @@ def _stream_buffers(device: torch.device):
     return _stream_scratch[key]
 
 
+_whole_percent = 80    # what the library was last told (its own default)
+
+
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch.Tensor] = None,
                 pdl: Optional[bool] = None) -> torch.Tensor:
     """out[M, N] (op)= a[M, K] @ w[N, K]^T for M <= 64: persistent, TMA-fed, tcgen05, stream-K balanced; the decode
@@ -522,6 +525,10 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
     scratch, counters = _stream_buffers(a.device)
     if (n + 127) // 128 > counters.numel():
         raise KernelError(f"the streamed product takes at most {counters.numel() * 128} rows of weights")
+    global _whole_percent
+    if _whole_percent != int(TUNE["stream_whole_percent"]):
+        _whole_percent = int(TUNE["stream_whole_percent"])
+        lib.gi_gemm_stream_whole_tiles(_whole_percent)
     _check(lib, lib.gi_gemm_stream_bf16_ex(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), scratch.data_ptr(),
                                            counters.data_ptr(), counters.numel(), m, n, k, lda, ldw, ldo,
                                            -1 if pdl is None else int(pdl), *_next_weights(w, mode), _stream()))

@@ -57,6 +57,8 @@ class DeviceSampler:
         self.device = torch.device(device)
         self.seed = params.seed if params.seed is not None else time.time_ns()
         self.states: Optional[torch.Tensor] = None
+        self._rows_of: Optional[tuple] = None          # the request ids whose device copy `_rows` holds
+        self._rows: Optional[torch.Tensor] = None
 
     def start(self, n_requests: int) -> None:
         if self.params.greedy:
@@ -72,7 +74,12 @@ class DeviceSampler:
         with ops.bucket("sampling"):
             if p.greedy:
                 return ops.sample(logits, 0.0, 0, 1.0)
-            idx = torch.tensor(list(request_ids), dtype=torch.int32).to(self.device, non_blocking=True)
+            ids = tuple(request_ids)
+            if self._rows_of != ids:        # the same rows step after step until a sequence leaves
+                pinned = self.device.type == "cuda"
+                self._rows = torch.tensor(ids, dtype=torch.int32, pin_memory=pinned).to(self.device, non_blocking=True)
+                self._rows_of = ids
+            idx = self._rows
             return ops.sample(logits, p.temperature, p.top_k, p.top_p, self.states, idx)
 
     def pick(self, logits: torch.Tensor, request_ids: Sequence[int]) -> List[int]:

@@ -554,6 +554,31 @@ def test_gemm_stream(pdl, m, n, k):
     assert ops.gemm_stream_status() == 0
 
 
+@pytest.mark.parametrize("mode", ["store", "f32", "swiglu"])
+@pytest.mark.parametrize("m,tiles,k", [(8, 120, 264), (64, 147, 512), (20, 119, 72), (5, 118, 264)])
+def test_gemm_stream_one_block_per_tile(mode, m, tiles, k):
+    """A product that finishes its own sums and has a few tiles fewer than there are SMs runs one block per tile (no
+    tile is cut between blocks): 119 tiles and more on 148 SMs.  Against the 64-bit product, with the rule on and
+    off, and with a last tile that is not full."""
+    n = tiles * 128 - (0 if mode == "swiglu" else 40)
+    a, w = rnd(m, k, dtype=torch.bfloat16, seed=80), rnd(n, k, dtype=torch.bfloat16, seed=81, scale=0.1)
+    ref = a.double() @ w.double().T
+    code = {"store": ops.SKINNY_STORE_BF16, "f32": ops.SKINNY_STORE_F32, "swiglu": ops.SKINNY_SWIGLU}[mode]
+    if mode == "swiglu":
+        r = ref.view(m, n // 16, 2, 8)
+        ref = (torch.nn.functional.silu(r[:, :, 0]) * r[:, :, 1]).reshape(m, n // 2)
+    was = ops.TUNE["stream_whole_percent"]
+    try:
+        for percent in (80, 0, 80):
+            ops.TUNE["stream_whole_percent"] = percent
+            out = ops.gemm_stream(a, w, code)
+            torch.testing.assert_close(out.double(), ref, **tol(torch.float32 if mode == "f32" else torch.bfloat16))
+    finally:
+        ops.TUNE["stream_whole_percent"] = was
+        ops.gemm_stream(a[:1], w[:128], ops.SKINNY_STORE_BF16)      # tells the library the old value again
+    assert ops.gemm_stream_status() == 0
+
+
 def test_gemm_stream_time_stamps():
     """With a buffer given, every block of a streamed product notes the clock along its life, in order; without
     one, nothing is written."""
