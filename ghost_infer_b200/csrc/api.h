@@ -223,6 +223,13 @@ int gi_attn_decode_tc_rope(void* out, long ldo, float* part_o, float* part_ml, i
                            const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
                            int own_tiles, int tile_keys, int stages, const float* table, int rot, gi_settle_t settle,
                            void* stream);
+// The decode attention with the keys on the rows of the tensor-core tile and up to 8 heads on its columns (half the
+// products per key for groups of up to 8 heads); slices are merged by gi_attn_combine.  warps: 4, 6 or 8 a block;
+// stages: 2 or 3 tiles deep per warp.
+int gi_attn_decode_kr(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, const void* kcache,
+                      const void* vcache, const int* block_table, int max_pages, const int* seq_slots, const int* seq_lens,
+                      int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits, int own_tiles,
+                      int warps, int stages, void* stream);
 int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const float* part_ml, int n_seqs, int n_heads,
                     int hd, int n_splits, void* stream);
 

@@ -64,6 +64,7 @@ def main() -> int:
     ap.add_argument("--merge-inside", type=int, default=-1, help="attn_decode: 1 = slices merged by the last block, 0 = by a second kernel")
     ap.add_argument("--tail", type=int, default=1, help="gemm_tc: 0 = full-width tiles only, 1 = narrower tiles in an unfilled last round")
     ap.add_argument("--stages", type=int, default=0, help="attn_decode: depth of each warp's ring of tiles (2 to 4)")
+    ap.add_argument("--keys-on-rows", type=int, default=-1, help="attn_decode: warps per block of the kernel with the keys on the tile's rows (0: the other kernel; default: the engine's choice)")
     ap.add_argument("--shortest", type=int, default=0, help="attn_decode: lengths uniform in [shortest, context] instead of all equal")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -71,6 +72,12 @@ def main() -> int:
     args = ap.parse_args()
     dev = "cuda:0"
     ops.set_pdl(args.pdl)
+    if args.keys_on_rows >= 0:
+        ops.TUNE["attn_keys_on_rows"] = args.keys_on_rows > 0
+        if args.keys_on_rows > 0:
+            ops.TUNE["attn_kr_warps"] = args.keys_on_rows
+            if args.stages:
+                ops.TUNE["attn_kr_stages"] = args.stages
     hbm, tflops, src = _peaks()
     bf = torch.bfloat16
     mode = {"store": ops.SKINNY_STORE_BF16, "accum": ops.SKINNY_ACCUM_F32, "swiglu": ops.SKINNY_SWIGLU, "f32": ops.SKINNY_STORE_F32}[args.mode]
@@ -121,7 +128,8 @@ def main() -> int:
                        n_sets, args.iters, args.warmup)
             nbytes = int(lens.sum()) * KV * hd * 2 * 2
             out.update(shape=[B, S, H, KV, hd], shortest=args.shortest, splits=splits, own_tiles=own, tile_keys=tile,
-                       merge_inside=inside, stages=args.stages, us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), frac_hbm=round(nbytes / us / 1e3 / hbm, 3))
+                       merge_inside=inside, stages=args.stages, keys_on_rows=int(ops.TUNE["attn_kr_warps"]) if ops.TUNE["attn_keys_on_rows"] else 0,
+                       us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), frac_hbm=round(nbytes / us / 1e3 / hbm, 3))
         else:
             q = torch.randn(B * S, (H + 2 * KV) * hd, device=dev, dtype=bf)
             cu = (torch.arange(B + 1, dtype=torch.int32, device=dev) * S)

@@ -65,6 +65,7 @@ def _bind():
         "gi_attn_decode_tc_ex": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P],
         "gi_attn_decode_tc_merged": [P, L, P, P, P, I, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P],
         "gi_attn_decode_tc_rope": [P, L, P, P, P, I, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P, I, SettleT, P],
+        "gi_attn_decode_kr": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
     }
     for name, argtypes in sigs.items():
@@ -465,7 +466,8 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 
 # Choices measured on a B200; benchmarks may override them to try alternatives.
 TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16,
-        "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3, "attn_rope_inside": False, "stream_whole_percent": 80}
+        "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3, "attn_rope_inside": False, "stream_whole_percent": 80,
+        "attn_keys_on_rows": True, "attn_kr_warps": 6, "attn_kr_stages": 2}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -897,6 +899,11 @@ def attn_decode_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
             n_seqs, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(n_splits), int(own_tiles),
             tile_keys, int(stages if stages is not None else attn_decode_stages(head_dim)))
     n_launches = 2 if (n_splits > 1 and counters is None) else 1
+    if rope is None and counters is None and TUNE["attn_keys_on_rows"] and n_heads // max(1, n_kv) <= 8:
+        # the keys of a tile on the rows of the products, up to 8 heads on their columns (a wider group would need
+        # two blocks that read the same keys: it keeps the kernel with 16 heads on the rows)
+        return attn_decode_kr(q, kcache, vcache, block_table, seq_slots, seq_lens, n_seqs, n_heads, n_kv, head_dim, scale,
+                              window, n_splits, out, part_o, part_ml, own_tiles=own_tiles)
     if rope is None:
         _check(lib, lib.gi_attn_decode_tc_merged(*args, _stream()), n_launches)
         return out
@@ -974,6 +981,13 @@ def attn_decode_blocks_per_sm(head_dim: int, fast: bool) -> float:
     the slice count fills that many places once."""
     if not fast:
         per_sm = 2
+    elif TUNE["attn_keys_on_rows"]:
+        # the kernel with a tile's keys on the rows of its products: 8 rows of queries, and each warp's ring of
+        # `stages` x (16 keys + 16 values); 80 registers a thread at head size 64, up to 127 at 128
+        warps, stages = int(TUNE["attn_kr_warps"]), int(TUNE["attn_kr_stages"])
+        smem = 8 * head_dim * 2 + warps * stages * 2 * 16 * head_dim * 2 + 1152
+        regs = 65536 // (warps * 32 * (80 if head_dim == 64 else 128))
+        per_sm = max(1, min(regs, (227 * 1024) // smem))
     elif TUNE["attn_tile_keys"] == 16:
         # a block's shared memory: 16 rows of queries, and four warps' rings of `stages` x (16 keys + 16 values)
         smem = 16 * head_dim * 2 + 4 * attn_decode_stages(head_dim) * 2 * 16 * head_dim * 2 + 1152
@@ -1005,7 +1019,9 @@ def attn_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, 
         tiles = (span + 31) // 32 + (1 if window else 0)
         return max(1, (tiles + OWN_LENGTH_TILES - 1) // OWN_LENGTH_TILES), OWN_LENGTH_TILES
     fast = dtype == torch.bfloat16 and head_dim in (64, 128)
-    rows_per_block = 16 if fast else 8            # the tensor-core kernel packs 16 heads of a group into a block
+    # heads of a group that one block takes: 16 in the tensor-core kernels (groups of more than 8 heads go to the one
+    # that has the heads on the rows of its tile), 8 in the plain kernel
+    rows_per_block = 16 if fast else 8
     group = n_heads // n_kv
     chunks = (group + rows_per_block - 1) // rows_per_block
     blocks = max(1, n_seqs * n_kv * chunks)
@@ -1027,6 +1043,35 @@ def attn_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, 
                 return max(1, (longest + own * tile - 1) // (own * tile)), own
             own += unit
     return 1, 0
+
+
+def attn_decode_kr(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                   seq_slots: torch.Tensor, seq_lens: torch.Tensor, n_seqs: int, n_heads: int, n_kv: int,
+                   head_dim: int, scale: float, window: Optional[int], n_splits: int, out: torch.Tensor,
+                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None, own_tiles: int = 0,
+                   warps: Optional[int] = None, stages: Optional[int] = None) -> torch.Tensor:
+    """The tensor-core decode attention with a tile's 16 keys on the rows of its products and up to 8 heads of a group on
+    their columns (wider groups take several blocks per kv head).  Same operands and scratch as `attn_decode_tc`;
+    `warps` per block (4, 6 or 8) and `stages` of each warp's ring (2 or 3) default to TUNE's."""
+    lib = _bind()
+    _cuda(q, "queries")
+    ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core decode attention takes bfloat16 queries, cache and output")
+    if n_splits > 1:
+        if part_o is None or part_ml is None:
+            raise KernelError("attention slices need scratch memory")
+        if part_o.dtype != torch.float32 or part_o.numel() < n_seqs * n_heads * n_splits * head_dim:
+            raise KernelError("attention scratch for outputs is too small")
+        if part_ml.dtype != torch.float32 or part_ml.numel() < n_seqs * n_heads * n_splits * 2:
+            raise KernelError("attention scratch for maxima and sums is too small")
+    _check(lib, lib.gi_attn_decode_kr(
+        out.data_ptr(), ldo, part_o.data_ptr() if part_o is not None else None,
+        part_ml.data_ptr() if part_ml is not None else None, q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(),
+        _i32(block_table, "block table"), block_table.shape[1], _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"),
+        n_seqs, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(n_splits), int(own_tiles),
+        int(warps or TUNE["attn_kr_warps"]), int(stages or TUNE["attn_kr_stages"]), _stream()), 2 if n_splits > 1 else 1)
+    return out
 
 
 def attn_rope_inside_ok(qkv: torch.Tensor, memory, step, head_dim: int) -> bool:

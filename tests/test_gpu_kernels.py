@@ -3,6 +3,8 @@ other than the tiny models': odd widths, head sizes 16..256, several group sizes
 import math
 
 import numpy as np
+import contextlib
+
 import pytest
 import torch
 
@@ -18,6 +20,29 @@ DTYPES = [torch.float32, torch.bfloat16]
 
 def tol(dtype):
     return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
+
+
+@contextlib.contextmanager
+def keys_on_rows(warps=4, stages=2):
+    """Inside, `ops.attn_decode_tc` runs the kernel that puts a tile's keys on the rows of its products."""
+    was = {k: ops.TUNE[k] for k in ("attn_keys_on_rows", "attn_kr_warps", "attn_kr_stages")}
+    ops.TUNE.update(attn_keys_on_rows=True, attn_kr_warps=warps, attn_kr_stages=stages)
+    try:
+        yield
+    finally:
+        ops.TUNE.update(was)
+
+
+@contextlib.contextmanager
+def heads_on_rows():
+    """Inside, `ops.attn_decode_tc` runs the kernel with the group's heads on the rows of its products whatever the
+    group's size (the kernel that can also merge its slices and rotate by itself)."""
+    was = ops.TUNE["attn_keys_on_rows"]
+    ops.TUNE["attn_keys_on_rows"] = False
+    try:
+        yield
+    finally:
+        ops.TUNE["attn_keys_on_rows"] = was
 
 
 def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
@@ -221,9 +246,33 @@ def test_attention_decode_tensor_cores(tile_keys, H, KV, hd, window, splits):
     part_o = torch.full((B * H * splits * hd,), float("nan"), device=DEV)
     part_ml = torch.full((B * H * splits * 2,), float("nan"), device=DEV)
     assert ops.attn_decode_tc_ok(q[:, 0], kc, hd)
-    ops.attn_decode_tc(q[:, 0], kc, vc, bt, torch.arange(B, dtype=torch.int32, device=DEV),
+    with heads_on_rows():
+        ops.attn_decode_tc(q[:, 0], kc, vc, bt, torch.arange(B, dtype=torch.int32, device=DEV),
+                           torch.tensor(lens, dtype=torch.int32, device=DEV), B, H, KV, hd, 0.17, window, splits, out,
+                           part_o, part_ml, tile_keys=tile_keys)
+    ref = attention_ref(q, k, v, [1] * B, [n - 1 for n in lens], H, KV, hd, 0.17, window)[:, 0]
+    torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("warps,stages", [(4, 2), (4, 3), (6, 2), (6, 3), (8, 2), (8, 3)])
+@pytest.mark.parametrize("H,KV,hd", [(8, 8, 64), (32, 8, 64), (32, 8, 128), (24, 8, 128), (5, 1, 64), (40, 2, 128), (16, 2, 64)])
+@pytest.mark.parametrize("window,splits,own_tiles", [(None, 1, 0), (None, 5, 0), (100, 1, 0), (100, 3, 0), (None, 13, 4)])
+def test_attention_decode_keys_on_rows(warps, stages, H, KV, hd, window, splits, own_tiles):
+    """The decode kernel with a tile's keys on the rows of its products and up to 8 heads on their columns: groups of 1,
+    3, 4, 5, 8 and 20 heads (one to three blocks per kv head), 4 to 8 warps, pages in shuffled order, rows past each
+    sequence's end poisoned with NaN, equal slices and slices of four tiles of each sequence's own span."""
+    lens = [1, 31, 64, 65, 700, 333, 96, 15, 16, 17]
+    B, S = len(lens), 704
+    k = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=13)
+    v = rnd(B, S, KV, hd, dtype=torch.bfloat16, seed=14)
+    q = rnd(B, 1, H * hd, dtype=torch.bfloat16, seed=15)
+    kc, vc, bt = paged_from_dense(k, v, lens, seed=4)
+    out = torch.full((B, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    part_o = torch.full((B * H * splits * hd,), float("nan"), device=DEV)
+    part_ml = torch.full((B * H * splits * 2,), float("nan"), device=DEV)
+    ops.attn_decode_kr(q[:, 0], kc, vc, bt, torch.arange(B, dtype=torch.int32, device=DEV),
                        torch.tensor(lens, dtype=torch.int32, device=DEV), B, H, KV, hd, 0.17, window, splits, out,
-                       part_o, part_ml, tile_keys=tile_keys)
+                       part_o, part_ml, own_tiles=own_tiles, warps=warps, stages=stages)
     ref = attention_ref(q, k, v, [1] * B, [n - 1 for n in lens], H, KV, hd, 0.17, window)[:, 0]
     torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
 
@@ -250,8 +299,9 @@ def test_attention_decode_merges_its_slices_itself(H, KV, hd, window, own_tiles,
         out = torch.full((B, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
         part_o = torch.full((B * H * splits * hd,), float("nan"), device=DEV)
         part_ml = torch.full((B * H * splits * 2,), float("nan"), device=DEV)
-        ops.attn_decode_tc(q[:, 0], kc, vc, bt, slots, lens_t, B, H, KV, hd, 0.17, window, splits, out, part_o, part_ml,
-                           tile_keys=tile_keys, own_tiles=own_tiles, merge_inside=inside)
+        with heads_on_rows():
+            ops.attn_decode_tc(q[:, 0], kc, vc, bt, slots, lens_t, B, H, KV, hd, 0.17, window, splits, out, part_o, part_ml,
+                               tile_keys=tile_keys, own_tiles=own_tiles, merge_inside=inside)
         torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
         outs.append(out)
     for o in outs[1:]:
@@ -291,8 +341,13 @@ def test_attention_finds_one_far_key(decode, window):
     one = torch.ones(1, dtype=torch.int32, device=DEV)
     if decode == "tc":
         po, pml = torch.zeros(H * 4 * hd, device=DEV), torch.zeros(H * 4 * 2, device=DEV)
-        ops.attn_decode_tc(q[:, 0], kc, vc, bt, 0 * one, n * one, 1, H, KV, hd, 1.0, window, 4, out, po, pml)
+        with heads_on_rows():
+            ops.attn_decode_tc(q[:, 0], kc, vc, bt, 0 * one, n * one, 1, H, KV, hd, 1.0, window, 4, out, po, pml)
         torch.testing.assert_close(out.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
+        out1 = torch.zeros_like(out)      # the decode kernel with the keys on the rows of its products
+        with keys_on_rows(8, 3):
+            ops.attn_decode_tc(q[:, 0], kc, vc, bt, 0 * one, n * one, 1, H, KV, hd, 1.0, window, 4, out1, po, pml)
+        torch.testing.assert_close(out1.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
         out2 = torch.zeros_like(out)      # and the prefill kernel: the last position as a one-token chunk
         ops.attn_prefill_tc(q[:, 0], kc, vc, bt, torch.tensor([0, 1], dtype=torch.int32, device=DEV), 0 * one,
                             pos * one, 1, 1, H, KV, hd, 1.0, window, out2)
@@ -357,7 +412,7 @@ def test_prompt_attention_edges_at_every_row(kernel, hd, window, edge):
         torch.testing.assert_close(out[:, h * hd + 1].double(), torch.ones(n, device=DEV, dtype=torch.float64), rtol=1e-2, atol=1e-2)
 
 
-@pytest.mark.parametrize("kernel,hd", [("generic", 32), ("mma", 64), ("mma", 128)])
+@pytest.mark.parametrize("kernel,hd", [("generic", 32), ("mma", 64), ("mma", 128), ("keys", 64), ("keys", 128)])
 @pytest.mark.parametrize("window,splits", [(None, 1), (None, 3), (37, 1), (64, 4), (100, 2)])
 @pytest.mark.parametrize("edge", ["newest", "oldest"])
 def test_decode_attention_edges_at_every_length(kernel, hd, window, splits, edge):
@@ -381,7 +436,8 @@ def test_decode_attention_edges_at_every_length(kernel, hd, window, splits, edge
     slots = torch.arange(B, dtype=torch.int32, device=DEV)
     dev_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
     fn = ops.attn_decode_generic if kernel == "generic" else ops.attn_decode_tc
-    fn(q, kc, vc, bt, slots, dev_lens, B, H, KV, hd, 1.0, window, splits, out, po, pml)
+    with (keys_on_rows() if kernel == "keys" else heads_on_rows()):
+        fn(q, kc, vc, bt, slots, dev_lens, B, H, KV, hd, 1.0, window, splits, out, po, pml)
     want = torch.tensor([float(n - 1 if edge == "newest" else (max(0, n - window) if window else 0)) for n in lens],
                         device=DEV, dtype=torch.float64)
     for h in range(H):
@@ -860,8 +916,9 @@ def test_decode_attention_rotates_and_stores_by_itself(H, KV, hd, rot, window, s
         part_ml = torch.full((B * H * splits * 2,), float("nan"), device=DEV)
         if not inside:
             ops.rope_cache_write(qkv, table, pos, slots, bt, kc, vc, H, KV, hd, rot, False, True)
-        ops.attn_decode_tc(qkv, kc, vc, bt, slots, lens_t, B, H, KV, hd, 0.17, window, splits, out, part_o, part_ml,
-                           rope=(table, rot) if inside else None)
+        with heads_on_rows():       # the same kernel in both arms
+            ops.attn_decode_tc(qkv, kc, vc, bt, slots, lens_t, B, H, KV, hd, 0.17, window, splits, out, part_o, part_ml,
+                               rope=(table, rot) if inside else None)
         assert not ops.has_pending(qkv)
         assert not bool(torch.isnan(out.float()).any())
         results.append((out, kc, vc))

@@ -255,8 +255,9 @@ def test_decode_with_the_rotation_left_to_the_attention(model_dirs, tiny_configs
     seqs = [tokens_for(cfg, s + steps, 130 + i) for i, s in enumerate(starts)]
     refs = [plain_logits(d, t) for t in seqs]
     outs, launches = [], []
-    was = ops.TUNE["attn_rope_inside"]
+    was = ops.TUNE["attn_rope_inside"], ops.TUNE["attn_keys_on_rows"]
     try:
+        ops.TUNE["attn_keys_on_rows"] = False           # the kernel that can rotate by itself, in both runs
         for inside in (False, True):
             ops.TUNE["attn_rope_inside"] = inside
             eng = make_engine(d, "bfloat16")            # a fresh engine: recorded steps keep the kernels they were recorded with
@@ -272,7 +273,7 @@ def test_decode_with_the_rotation_left_to_the_attention(model_dirs, tiny_configs
             for s in slots:
                 cache.close_slot(s)
     finally:
-        ops.TUNE["attn_rope_inside"] = was
+        ops.TUNE["attn_rope_inside"], ops.TUNE["attn_keys_on_rows"] = was
     for i in range(3):
         check_logits(outs[1][:, i], refs[i][starts[i]:], "bfloat16", f"{name} rotation inside the attention, request {i}")
     assert np.array_equal(outs[0], outs[1])

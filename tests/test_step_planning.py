@@ -62,6 +62,15 @@ def test_wide_groups_take_several_blocks_per_kv_head():
     assert plan(4, 4096, 40, 1, 128) == ((2 * 148) // (4 * 3), 0)
 
 
+def test_both_tensor_core_kernels_hold_the_same_number_of_blocks(monkeypatch):
+    # keys on the rows, six warps with rings of two stages: 98 KB and up to 127 registers at head size 128, 50 KB and
+    # 80 registers at 64; heads on the rows, four warps: the shared memory decides at 128, the registers at 64
+    for on in (True, False):
+        monkeypatch.setitem(ops.TUNE, "attn_keys_on_rows", on)
+        assert ops.attn_decode_blocks_per_sm(128, True) == 2 * ops.TUNE["attn_waves"]
+        assert ops.attn_decode_blocks_per_sm(64, True) == 4 * ops.TUNE["attn_waves"]
+
+
 def test_head_sizes_the_tensor_core_kernel_declines_count_eight_rows_a_block():
     # head size 48 in bfloat16 runs the plain kernel: 8 heads a block (two blocks for a group of 16), two blocks per SM
     assert plan(4, 1 << 20, 32, 2, 48) == ((2 * 148) // (4 * 2 * 2), 0)
