@@ -151,9 +151,15 @@ int gi_settle(float* x, gi_settle_t settle, const int* rows, int n_rows, int d, 
 #define GI_TC_STORE_F32 1
 #define GI_TC_ACCUM_F32 2
 #define GI_TC_SWIGLU 3
+#define GI_TC_QKV_ROPE 4        // gi_gemm_tc_qkv_rope only: queries rotated and stored, keys and values into the cache
 // tcgen05 / TMA product for many rows of activations; tile_n is 128 or 256
 int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
                     long ldo, int tile_n, void* stream);
+// The q/k/v product of a prompt step that rotates and stores in its epilogue (the work of gi_rope_cache_write, the same
+// bits): out [M, N] packed rows of which the queries' columns are written; N = (n_heads + 2 n_kv) * hd, hd 64 or 128.
+int gi_gemm_tc_qkv_rope(void* out, const void* A, const void* W, int M, int N, int K, long lda, long ldw, long ldo,
+                        const float* table, const int* positions, const int* slots, const int* block_table, int max_pages,
+                        void* kcache, void* vcache, int n_heads, int n_kv, int hd, int write_cache, void* stream);
 // narrower tiles for the columns of an unfilled last round of blocks: on (default) or off
 int gi_gemm_tc_tail_tiles(int on);
 int gi_gemm_tc_status(int* status);

@@ -47,18 +47,34 @@ struct TilePlan {
   int n_tiles;       // all tiles
 };
 
+// What the q/k/v product's epilogue needs to rotate and store by itself (mode GI_TC_QKV_ROPE): the output's columns are
+// heads of `hd` values, first n_heads of queries, then n_kv of keys, then n_kv of values.  Queries are rotated and
+// stored in the packed rows, keys rotated into the cache, values copied into the cache (src/model.rs:1046-1048);
+// the keys' and values' columns of the packed rows are not written at all.
+struct RopeEpilogue {
+  const float2* table;        // [M][hd / 2] (cos, sin) of each token's position
+  const int* positions;       // [M]
+  const int* slots;           // [M] the sequence's slot, -1: a padding row (the trash page)
+  const int* block_table;
+  int max_pages;
+  __nv_bfloat16* kcache;
+  __nv_bfloat16* vcache;
+  int n_heads, n_kv, hd;      // hd 64 or 128, all of it rotated, pairs (i, i + hd / 2)
+  int write_cache;
+};
+
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_o, int M, int N, int K,
-               const TilePlan plan) {
+               const TilePlan plan, const RopeEpilogue rope) {
   constexpr uint32_t A_BYTES = BM * BK * 2, W_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
   constexpr uint32_t STG_BYTES = BM * 128;     // a staging tile: 128 rows of 128 bytes
   // instruction descriptor: float accumulator (bits 4-5 = 1), bfloat16 A and B (bits 7-9, 10-12 = 1), both K-major,
   // N / 8 in bits 17-22, M / 16 in bits 24-28
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   // accumulator columns that make one 128-byte row of output: 32 floats, 64 bfloat16, or 128 gate/up values -> 64 activations
-  constexpr int CW = (MODE == GI_TC_SWIGLU) ? 128 : (MODE == GI_TC_STORE_BF16 ? 64 : 32);
+  constexpr int CW = (MODE == GI_TC_SWIGLU) ? 128 : ((MODE == GI_TC_STORE_BF16 || MODE == GI_TC_QKV_ROPE) ? 64 : 32);
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* staging = smem + STAGES * STAGE_BYTES;                 // two staging tiles
@@ -164,12 +180,103 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++seg) {
       int m0, n0, width;
       geometry(tile, m0, n0, width);
-      const int chunks = width / CW;
+      const int chunks = MODE == GI_TC_QKV_ROPE ? 0 : width / CW;      // that mode has its own loop over the columns
       const int buf = seg & 1;
       ok = mbar_wait(accf0 + 8 * buf, ((uint32_t)(seg >> 1)) & 1, 3, &g_status);
       if (!ok) break;
       tc_fence_after();
       const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+      if (MODE == GI_TC_QKV_ROPE) {
+        // This thread's row is one token.  The tile is worked through in groups of 128 columns: one head of 128
+        // values (its first half goes to staging tile A, its second to B) or two heads of 64 (one to each tile).
+        // A value is rounded to bfloat16 as the plain store would round it, rotated in 32-bit with the token's
+        // angles (the same function as the rotary kernels: the same bits), and rounded again.
+        const int tok = m0 + row;
+        const bool live = tok < M;
+        const int hd = rope.hd, half = hd >> 1;
+        size_t cache_tok = 0;       // this token's row of kv head 0 in the cache, in elements
+        if (live && rope.write_cache) {
+          const int pos = rope.positions[tok], slot = rope.slots[tok];
+          const int page = slot >= 0 ? rope.block_table[(size_t)slot * rope.max_pages + pos / PAGE_TOKENS] : 0;
+          cache_tok = ((size_t)page * rope.n_kv * PAGE_TOKENS + (pos % PAGE_TOKENS)) * hd;
+        }
+        const float2* cs = rope.table + (size_t)(live ? tok : 0) * half;
+        const int heads_all = rope.n_heads + 2 * rope.n_kv;
+        auto kind_of = [&](int head) { return head < rope.n_heads ? 0 : (head < rope.n_heads + rope.n_kv ? 1 : (head < heads_all ? 2 : 3)); };
+        const int groups = width / 128;
+#pragma unroll 1
+        for (int gi_ = 0; gi_ < groups; ++gi_) {
+          const int gcol = n0 + gi_ * 128;
+          if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // both staging tiles are free again
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll 1
+          for (int pass = 0; pass < 2; ++pass) {
+            // head size 128: the head's pairs 32 pass .. 32 pass + 31; head size 64: head `pass` of the group
+            const int lo_col = hd == 128 ? 32 * pass : 64 * pass, hi_col = lo_col + half;
+            const int lo_dim = hd == 128 ? 32 * pass : 0;
+            const int head = (gcol + lo_col) / hd;
+            const int kind = kind_of(head);
+            if (kind == 3) continue;                          // past the last head (the same for every thread)
+            uint32_t lo[32], hi[32];
+            tc_ld32(tbase + (uint32_t)(gi_ * 128 + lo_col), lo);
+            tc_ld32(tbase + (uint32_t)(gi_ * 128 + hi_col), hi);
+            tc_wait_ld();
+            uint32_t plo[16], phi[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float a0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[j]))), a1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[j + 1])));
+              float b0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[j]))), b1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[j + 1])));
+              if (kind != 2 && live) {
+                const float4 c2 = *reinterpret_cast<const float4*>(cs + lo_dim + j);    // two pairs' (cos, sin)
+                gi::rotate_pair(a0, b0, make_float2(c2.x, c2.y), &a0, &b0);
+                gi::rotate_pair(a1, b1, make_float2(c2.z, c2.w), &a1, &b1);
+              }
+              __nv_bfloat162 v = __floats2bfloat162_rn(a0, a1);
+              plo[j / 2] = *reinterpret_cast<uint32_t*>(&v);
+              v = __floats2bfloat162_rn(b0, b1);
+              phi[j / 2] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            if (kind == 0) {
+              // head size 128: the first half's chunks 4 pass .. in tile A, the second half's in tile B;
+              // head size 64: the head's eight chunks in tile A (pass 0) or B (pass 1)
+              unsigned char* stg_lo = (hd == 128 || pass == 0) ? staging : staging + STG_BYTES;
+              unsigned char* stg_hi = hd == 128 ? staging + STG_BYTES : stg_lo;
+              const int c_lo = hd == 128 ? 4 * pass : 0, c_hi = hd == 128 ? 4 * pass : 4;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                stage_chunk(stg_lo, row, c_lo + e, make_uint4(plo[4 * e], plo[4 * e + 1], plo[4 * e + 2], plo[4 * e + 3]));
+                stage_chunk(stg_hi, row, c_hi + e, make_uint4(phi[4 * e], phi[4 * e + 1], phi[4 * e + 2], phi[4 * e + 3]));
+              }
+            } else if (live && rope.write_cache) {
+              const int kvh = head - rope.n_heads - (kind == 2 ? rope.n_kv : 0);
+              __nv_bfloat16* dst = (kind == 1 ? rope.kcache : rope.vcache) + cache_tok + (size_t)kvh * PAGE_TOKENS * hd;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                *reinterpret_cast<uint4*>(dst + lo_dim + 8 * e) = make_uint4(plo[4 * e], plo[4 * e + 1], plo[4 * e + 2], plo[4 * e + 3]);
+                *reinterpret_cast<uint4*>(dst + lo_dim + half + 8 * e) = make_uint4(phi[4 * e], phi[4 * e + 1], phi[4 * e + 2], phi[4 * e + 3]);
+              }
+            }
+          }
+          if (gi_ == groups - 1) {
+            // the whole accumulator is in registers, staged or stored: hand the buffer back to the MMA thread
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // staged rows become visible to the TMA engine
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (issuer) {
+            // tile A holds columns gcol .. gcol + 63, tile B the next 64: stored where they are queries
+            if (kind_of(gcol / hd) == 0)
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&map_o), "r"(smem_u32(staging)), "r"(gcol), "r"(m0) : "memory");
+            if (kind_of((gcol + 64) / hd) == 0)
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&map_o), "r"(smem_u32(staging + STG_BYTES)), "r"(gcol + 64), "r"(m0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < chunks; ++c, ++chunk_no) {
         unsigned char* stg = staging + (chunk_no & 1) * STG_BYTES;
@@ -333,7 +440,7 @@ TilePlan plan_tiles(int M, int N, int bn, int gran, int sms) {
 
 template <int BN, int STAGES, int MODE>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mo, int M, int N, int K,
-           const TilePlan& plan, cudaStream_t s) {
+           const TilePlan& plan, const RopeEpilogue& rope, cudaStream_t s) {
   constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 2 * BM * 128 + (2 * STAGES + 4) * 8 + 16 + 1024;
   auto kern = gemm_tc_kernel<BN, STAGES, MODE>;
   static bool configured[gi::MAX_DEVICES_SEEN] = {false};
@@ -345,17 +452,18 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mw2,
   }
   const long tiles = plan.n_tiles;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  return gi::check(gi::launch(kern, dim3(grid), dim3(THREADS), smem, s, ma, mw, mw2, mo, M, N, K, plan), "tensor-core product");
+  return gi::check(gi::launch(kern, dim3(grid), dim3(THREADS), smem, s, ma, mw, mw2, mo, M, N, K, plan, rope), "tensor-core product");
 }
 
 template <int BN, int STAGES>
 int launch_mode(int mode, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mo, int M, int N,
                 int K, const TilePlan& plan, cudaStream_t s) {
+  const RopeEpilogue none = {nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0};
   switch (mode) {
-    case GI_TC_STORE_BF16: return launch<BN, STAGES, GI_TC_STORE_BF16>(ma, mw, mw2, mo, M, N, K, plan, s);
-    case GI_TC_STORE_F32: return launch<BN, STAGES, GI_TC_STORE_F32>(ma, mw, mw2, mo, M, N, K, plan, s);
-    case GI_TC_ACCUM_F32: return launch<BN, STAGES, GI_TC_ACCUM_F32>(ma, mw, mw2, mo, M, N, K, plan, s);
-    case GI_TC_SWIGLU: return launch<BN, STAGES, GI_TC_SWIGLU>(ma, mw, mw2, mo, M, N, K, plan, s);
+    case GI_TC_STORE_BF16: return launch<BN, STAGES, GI_TC_STORE_BF16>(ma, mw, mw2, mo, M, N, K, plan, none, s);
+    case GI_TC_STORE_F32: return launch<BN, STAGES, GI_TC_STORE_F32>(ma, mw, mw2, mo, M, N, K, plan, none, s);
+    case GI_TC_ACCUM_F32: return launch<BN, STAGES, GI_TC_ACCUM_F32>(ma, mw, mw2, mo, M, N, K, plan, none, s);
+    case GI_TC_SWIGLU: return launch<BN, STAGES, GI_TC_SWIGLU>(ma, mw, mw2, mo, M, N, K, plan, none, s);
   }
   return gi::fail(GI_ERR_ARG, "tensor-core product: unknown mode %d", mode);
 }
@@ -393,6 +501,39 @@ extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W
   }
   if (tile_n == 128) return launch_mode<128, 6>(mode, ma, mw, mw2, mo, M, N, K, plan, s);
   return launch_mode<256, 4>(mode, ma, mw, mw2, mo, M, N, K, plan, s);
+}
+
+// The q/k/v product of a prompt step with rotation and cache write in its epilogue: out[M, N] holds the packed rows,
+// of which only the queries' columns are written (rotated); keys (rotated) and values go to the cache pages of each
+// token's slot and position.  N = (n_heads + 2 n_kv) * hd, hd 64 or 128, all of a head rotated, pairs (i, i + hd / 2);
+// table [M][hd / 2] (cos, sin).  The same bits as gi_gemm_tc_bf16 (GI_TC_STORE_BF16) followed by gi_rope_cache_write.
+extern "C" int gi_gemm_tc_qkv_rope(void* out, const void* A, const void* W, int M, int N, int K, long lda, long ldw, long ldo,
+                                   const float* table, const int* positions, const int* slots, const int* block_table,
+                                   int max_pages, void* kcache, void* vcache, int n_heads, int n_kv, int hd, int write_cache,
+                                   void* stream) {
+  if (M <= 0 || N <= 0) return GI_OK;
+  if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ldo % 8 != 0)
+    return gi::fail(GI_ERR_UNSUPPORTED, "q/k/v product: K (%d) and the row strides (%ld, %ld, %ld) must be multiples of 8", K, lda, ldw, ldo);
+  if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out | (uintptr_t)table | (uintptr_t)kcache | (uintptr_t)vcache) & 15)
+    return gi::fail(GI_ERR_UNSUPPORTED, "q/k/v product: operands must be 16-byte aligned");
+  if (hd != 64 && hd != 128) return gi::fail(GI_ERR_UNSUPPORTED, "q/k/v product with rotation: head size %d, only 64 and 128", hd);
+  if (n_heads <= 0 || n_kv <= 0 || N != (n_heads + 2 * n_kv) * hd)
+    return gi::fail(GI_ERR_ARG, "q/k/v product with rotation: %d columns are not (%d + 2 x %d) heads of %d", N, n_heads, n_kv, hd);
+  if (!table || !positions) return gi::fail(GI_ERR_ARG, "q/k/v product with rotation: no table of angles or no positions");
+  if (write_cache && (!kcache || !vcache || !block_table || !slots)) return gi::fail(GI_ERR_ARG, "q/k/v product with rotation: cache write without a cache");
+  if ((N + 255) / 256 > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "q/k/v product: too many tiles");
+  CUtensorMap ma, mw, mo;
+  int rc = gi::tensor_map_2d(&ma, A, M, K, lda, BM);
+  if (rc != GI_OK) return rc;
+  rc = gi::tensor_map_2d(&mw, W, N, K, ldw, 256);
+  if (rc != GI_OK) return rc;
+  rc = gi::tensor_map_2d_ex(&mo, out, M, N, ldo, GI_BF16, 64, BM);
+  if (rc != GI_OK) return rc;
+  // full-width tiles only: a narrower tile would cut a head
+  const TilePlan plan = plan_tiles(M, N, 256, 64, 0);
+  const RopeEpilogue rope = {(const float2*)table, positions, slots, block_table, max_pages, (__nv_bfloat16*)kcache,
+                             (__nv_bfloat16*)vcache, n_heads, n_kv, hd, write_cache};
+  return launch<256, 4, GI_TC_QKV_ROPE>(ma, mw, mw, mo, M, N, K, plan, rope, (cudaStream_t)stream);
 }
 
 // Switches the narrower tiles of an unfilled last round on (the default) or off; for measurements.

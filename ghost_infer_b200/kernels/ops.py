@@ -66,6 +66,7 @@ def _bind():
         "gi_attn_decode_tc_merged": [P, L, P, P, P, I, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P],
         "gi_attn_decode_tc_rope": [P, L, P, P, P, I, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P, I, SettleT, P],
         "gi_attn_decode_kr": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P],
+        "gi_gemm_tc_qkv_rope": [P, P, P, I, I, I, L, L, L, P, P, P, P, I, P, P, I, I, I, I, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
     }
     for name, argtypes in sigs.items():
@@ -467,7 +468,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 # Choices measured on a B200; benchmarks may override them to try alternatives.
 TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16,
         "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3, "attn_rope_inside": False, "stream_whole_percent": 80,
-        "attn_keys_on_rows": True, "attn_kr_warps": 6, "attn_kr_stages": 2}
+        "attn_keys_on_rows": True, "attn_kr_warps": 6, "attn_kr_stages": 2, "qkv_rope_epilogue": True}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -653,6 +654,54 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch.Ten
     ldo = _rows(out, "output")
     _check(lib, lib.gi_gemm_tc_bf16(out.data_ptr(), mode, a.data_ptr(), w.data_ptr(), m, n, k, lda, ldw, ldo,
                                     int(tile_n or TC_TILE_N), _stream()))
+    return out
+
+
+def qkv_rope_ok(h: torch.Tensor, w: torch.Tensor, memory, head_dim: int, rotary_dim: int) -> bool:
+    """Whether the prompt step's q/k/v product can rotate and store in its epilogue (`gemm_tc_qkv_rope`): the
+    tensor-core product takes the operands, heads of 64 or 128 values rotated whole, a bfloat16 cache or none to write."""
+    if not (TUNE["qkv_rope_epilogue"] and tc_ok(h, w) and h.shape[0] > SKINNY_MAX_ROWS and head_dim in (64, 128)
+            and rotary_dim == head_dim):
+        return False
+    if memory.writes and memory.k is not None:
+        return memory.k.dtype == torch.bfloat16 and memory.k.is_contiguous() and memory.v.is_contiguous()
+    return True
+
+
+def gemm_tc_qkv_rope(h: torch.Tensor, w: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                     block_table: Optional[torch.Tensor], kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
+                     n_heads: int, n_kv: int, head_dim: int, write_cache: bool) -> torch.Tensor:
+    """The packed [q | k | v] rows of a prompt step, h @ w^T, with the rotation by `table` (pairs (i, i + half), the
+    whole head) and the cache write in the product's epilogue: the queries' columns of the result are rotated, the
+    keys' and values' columns are not written (they went to the cache; with `write_cache` false, nowhere).  The same
+    bits as the plain product followed by `rope_cache_write`."""
+    lib = _bind()
+    _cuda(h, "activations")
+    _cuda(w, "weights")
+    if h.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core product takes bfloat16 operands")
+    lda, ldw = _rows(h, "activations"), _rows(w, "weights")
+    m, k = h.shape
+    n, kw = w.shape
+    if k != kw or n != (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError(f"q/k/v product: activations {tuple(h.shape)}, weights {tuple(w.shape)}, wanted {(n_heads + 2 * n_kv) * head_dim} rows of weights")
+    if table.dtype != torch.float32 or not table.is_contiguous() or table.numel() != m * (head_dim // 2) * 2:
+        raise KernelError("the table of angles must hold tokens x head_dim / 2 float32 (cos, sin) pairs")
+    if write_cache:
+        if kcache is None or vcache is None or block_table is None:
+            raise KernelError("cache write without a cache")
+        if kcache.dtype != torch.bfloat16 or vcache.dtype != torch.bfloat16:
+            raise KernelError(f"the cache is {kcache.dtype}, the step runs in bfloat16")
+        if tuple(kcache.shape[1:]) != (n_kv, 64, head_dim) or not kcache.is_contiguous() or not vcache.is_contiguous():
+            raise KernelError(f"cache pages must be contiguous [pages, {n_kv}, 64, {head_dim}], got {tuple(kcache.shape)}")
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=h.device)
+    _check(lib, lib.gi_gemm_tc_qkv_rope(
+        out.data_ptr(), h.data_ptr(), w.data_ptr(), m, n, k, lda, ldw, _rows(out, "output"), table.data_ptr(),
+        _i32(positions, "positions"), _i32(slots, "slots"), _i32(block_table, "block table"),
+        block_table.shape[1] if block_table is not None else 0,
+        kcache.data_ptr() if (write_cache and kcache is not None) else None,
+        vcache.data_ptr() if (write_cache and vcache is not None) else None,
+        n_heads, n_kv, head_dim, int(write_cache), _stream()))
     return out
 
 

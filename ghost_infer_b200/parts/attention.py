@@ -73,6 +73,12 @@ class GqaAttention(Mixer):
     def forward(self, h, residual, step, memory) -> None:
         # in a decode step the product may leave partial sums for the kernel that rotates and stores (it reads
         # every value anyway); an encoding that does not go through that kernel gets plain rows
+        qkv = None
+        if self.position is not None:
+            with ops.bucket("qkv matmul"):
+                qkv = self.position.project_and_store(h, self.w_qkv, step, memory, self.n_heads, self.n_kv, self.head_dim)
+        if qkv is not None:
+            return self._attend(qkv, None, residual, step, memory)
         with ops.bucket("qkv matmul"):
             if self.position is None or getattr(self.position, "settles_pending", False):
                 with ops.defer_store():
@@ -89,8 +95,11 @@ class GqaAttention(Mixer):
                 ops.rope_cache_write(qkv, None, step.positions, step.token_slots, memory.block_table, memory.k, memory.v,
                                      self.n_heads, self.n_kv, self.head_dim, 0, False,
                                      memory.writes and memory.k is not None)
+        self._attend(qkv, inside, residual, step, memory)
+
+    def _attend(self, qkv, inside, residual, step, memory) -> None:
         with ops.bucket("attention"):
-            att = torch.empty((h.shape[0], self.q_dim), dtype=self.rt.dtype, device=h.device)
+            att = torch.empty((qkv.shape[0], self.q_dim), dtype=self.rt.dtype, device=qkv.device)
             ops.attention(qkv, memory, step, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, att,
                           plan=step.plan_of(self), rope=inside)
         with ops.bucket("out matmul"):

@@ -92,6 +92,14 @@ class PositionEncoding(Part):
                          head_dim: int) -> None:
         raise NotImplementedError
 
+    def project_and_store(self, h: torch.Tensor, w_qkv: torch.Tensor, step, memory: LayerMemory, n_heads: int,
+                          n_kv_heads: int, head_dim: int) -> Optional[torch.Tensor]:
+        """An encoding that can ride in the epilogue of the q/k/v product itself returns the packed rows of
+        `h @ w_qkv^T` with its work and the cache write done (queries encoded in place; the keys' and values' columns
+        need not hold anything afterwards), and neither the product nor `encode_and_store` is then run for the
+        step.  None (the default): product and encoding run as steps of their own."""
+        return None
+
     def left_to_attention(self, qkv: torch.Tensor, step, memory: LayerMemory, n_heads: int, n_kv_heads: int,
                           head_dim: int):
         """An encoding whose work for this step the attention kernel can do on the way (a rotation by a table of

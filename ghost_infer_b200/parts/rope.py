@@ -77,6 +77,14 @@ class Rotary(PositionEncoding):
             step.shared[self.table_key] = table
         return table
 
+    def project_and_store(self, h, w_qkv, step, memory, n_heads, n_kv_heads, head_dim):
+        # a prompt step's product on the tensor cores rotates its own rows: every thread of its epilogue holds one token's row
+        if step.is_decode or self.pairing != "half" or not ops.qkv_rope_ok(h, w_qkv, memory, head_dim, self.rotary_dim):
+            return None
+        writes = bool(memory.writes and memory.k is not None)
+        return ops.gemm_tc_qkv_rope(h, w_qkv, self._table(step), step.positions, step.token_slots, memory.block_table,
+                                    memory.k, memory.v, n_heads, n_kv_heads, head_dim, writes)
+
     def left_to_attention(self, qkv, step, memory, n_heads, n_kv_heads, head_dim):
         # one token per sequence: the decode attention's blocks rotate the heads they read and the newest key
         if self.pairing != "half" or self.rotary_dim < 2 or not ops.attn_rope_inside_ok(qkv, memory, step, head_dim):

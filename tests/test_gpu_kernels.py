@@ -933,6 +933,47 @@ def test_decode_attention_rotates_and_stores_by_itself(H, KV, hd, rot, window, s
     torch.testing.assert_close(got.double(), ref_v, rtol=1.6e-2, atol=1.6e-2)
 
 
+@pytest.mark.parametrize("H,KV,hd", [(32, 8, 128), (3, 1, 128), (5, 1, 64), (4, 2, 64), (6, 3, 64)])
+@pytest.mark.parametrize("m,k", [(200, 264), (65, 64), (1000, 512)])
+@pytest.mark.parametrize("write_cache", [True, False])
+def test_prompt_product_rotates_and_stores_in_its_epilogue(H, KV, hd, m, k, write_cache):
+    """The q/k/v product of a prompt step with the rotation and the cache write in its epilogue, against the plain
+    product followed by the rotary kernel: the same bits in the queries' columns and in every byte of the cache.
+    Three sequences of unequal lengths that start inside pages, one of them a padding row's slot (-1, the trash page);
+    head counts that make a group of 128 columns straddle queries and keys, or end half-way (7 heads of 64); a last
+    row tile that is not full."""
+    n = (H + 2 * KV) * hd
+    a, w = rnd(m, k, dtype=torch.bfloat16, seed=90), rnd(n, k, dtype=torch.bfloat16, seed=91, scale=0.1)
+    cuts = [0, m // 3, m // 3 + 1, m]                       # tokens of sequence i: cuts[i] .. cuts[i + 1]
+    starts = [37, 64, 5]
+    positions = torch.cat([torch.arange(s0, s0 + (cuts[i + 1] - cuts[i])) for i, s0 in enumerate(starts)]).to(torch.int32).to(DEV)
+    slots = torch.cat([torch.full((cuts[i + 1] - cuts[i],), sl, dtype=torch.int32) for i, sl in enumerate([1, -1, 0])]).to(DEV)
+    pages = (max(starts) + m + 63) // 64 + 1
+    bt = (torch.randperm(2 * pages, generator=torch.Generator().manual_seed(3)) + 1).to(torch.int32).reshape(2, pages).to(DEV)
+    table = ops.rope_table(positions, torch.from_numpy(pl.rotary_inv_freq(hd, 10000.0, None)).to(DEV))
+    results = []
+    for fused in (False, True):
+        kc = torch.full((2 * pages + 1, KV, 64, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        vc = torch.full_like(kc, float("nan"))
+        if fused:
+            qkv = ops.gemm_tc_qkv_rope(a, w, table, positions, slots, bt, kc, vc, H, KV, hd, write_cache)
+        else:
+            qkv = ops.gemm_tc(a, w, ops.SKINNY_STORE_BF16)
+            ops.rope_cache_write(qkv, table, positions, slots, bt, kc, vc, H, KV, hd, hd, False, write_cache)
+        results.append((qkv[:, :H * hd].clone(), kc, vc))
+    assert ops.gemm_tc_status() == 0
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.equal(results[0][1].view(torch.int16), results[1][1].view(torch.int16))
+    assert torch.equal(results[0][2].view(torch.int16), results[1][2].view(torch.int16))
+    assert not bool(torch.isnan(results[1][0].float()).any())
+    if write_cache:       # the value rows are the product's
+        ref_v = (a.double() @ w.double().T)[:cuts[1], (H + KV) * hd:]
+        got = torch.stack([results[1][2][int(bt[1, (37 + t) // 64]), :, (37 + t) % 64].reshape(KV * hd) for t in range(cuts[1])])
+        torch.testing.assert_close(got.double(), ref_v, rtol=1.6e-2, atol=1.6e-2)
+    else:
+        assert bool(torch.isnan(results[1][1].float()).all())
+
+
 @pytest.mark.parametrize("inside", [False, True])
 @pytest.mark.parametrize("H,KV,hd,lens,hidden,splits", [(4, 2, 64, [102, 102], 192, 2), (4, 2, 64, [140, 111, 7], 192, 3),
                                                          (3, 1, 128, [102, 90], 264, 2), (32, 8, 64, [700] * 4, 2048, 4),
