@@ -468,7 +468,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 # Choices measured on a B200; benchmarks may override them to try alternatives.
 TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16,
         "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3, "attn_rope_inside": False, "stream_whole_percent": 80,
-        "attn_keys_on_rows": True, "attn_kr_warps": 6, "attn_kr_stages": 2, "qkv_rope_epilogue": True}
+        "attn_keys_on_rows": True, "attn_kr_warps": 6, "attn_kr_stages": 2, "qkv_rope_epilogue": True, "attn_min_slice": 256}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -1055,7 +1055,9 @@ def attn_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, 
     """How the decode attention cuts contexts into slices, as (slices in the launch, tiles per slice).
 
     bfloat16, few sequences: tiles per slice 0 = every sequence is cut into the same number of slices, as many as
-    fill the GPU once (blocks that wait for a second round cost more than longer slices), at least 128 positions each.
+    fill the GPU once (blocks that wait for a second round cost more than longer slices), at least 256 positions of the
+    longest sequence's present length each (measured at batch 1 to 4 of the 8B shape with 2,048 cached positions: 8
+    slices beat 16 and 4, and 32, which the length bucket's upper end alone would allow, cost 3.5 % of the step).
     bfloat16, so many sequences that one slice each fills more than half the GPU, and their lengths (`kv_lens`) known:
     slices of a fixed number of tiles of each sequence's own span, the shortest for which all blocks still find a
     place at once; long sequences are then cut and short ones are not, so that no block is much longer than the rest.
@@ -1076,7 +1078,10 @@ def attn_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, 
     blocks = max(1, n_seqs * n_kv * chunks)
     places = int(attn_decode_blocks_per_sm(head_dim, fast) * sm_count)
     if 2 * blocks <= places or not fast:
-        return int(max(1, min(places // blocks, 32, max_kv_len // 128))), 0
+        # slices of at least TUNE["attn_min_slice"] positions of the longest sequence as it is now (a plan is kept while
+        # the sequences grow to the end of their length bucket, up to twice as long)
+        longest = max_kv_len if not kv_lens else min(max_kv_len, max(int(n) for n in kv_lens))
+        return int(max(1, min(places // blocks, 32, longest // int(TUNE["attn_min_slice"])))), 0
     if kv_lens is not None and TUNE["attn_own_slices"] and blocks < places:
         tile = int(TUNE["attn_tile_keys"])
         span = (lambda n: n) if not window else (lambda n: min(n, int(window) + 2 * tile))

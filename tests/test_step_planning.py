@@ -15,13 +15,19 @@ def test_slices_fill_the_blocks_an_sm_holds():
     assert ops.attn_decode_blocks_per_sm(128, True) == 2 * ops.TUNE["attn_waves"]
     assert ops.attn_decode_blocks_per_sm(64, True) == 4 * ops.TUNE["attn_waves"]
     assert plan(8, 2048, 32, 8, 128) == (4, 0)
-    assert plan(8, 2048, 32, 8, 64) == (9, 0)
+    assert plan(8, 4096, 32, 8, 64) == (9, 0)
 
 
-def test_slices_are_never_shorter_than_128_positions_nor_more_than_32():
+def test_slices_are_never_shorter_than_256_positions_nor_more_than_32():
     assert plan(1, 100, 32, 8, 128) == (1, 0)
-    assert plan(1, 300, 32, 8, 128) == (2, 0)
+    assert plan(1, 300, 32, 8, 128) == (1, 0)
+    assert plan(1, 600, 32, 8, 128) == (2, 0)
     assert plan(1, 1 << 20, 4, 1, 128) == (32, 0)
+    # the length that counts is the longest sequence's now, not the end of its length bucket (which the plan must
+    # still cover: it is kept until a sequence outgrows the bucket)
+    assert plan(1, 4096, 32, 8, 128) == (16, 0)
+    assert plan(1, 4096, 32, 8, 128, kv_lens=[2049]) == (8, 0)
+    assert plan(2, 4096, 32, 8, 128, kv_lens=[300, 1100]) == (4, 0)
 
 
 def test_many_equal_sequences_take_one_slice_each():
@@ -59,7 +65,7 @@ def test_many_unequal_sequences_can_be_cut_so_that_all_blocks_find_a_place_at_on
 
 def test_wide_groups_take_several_blocks_per_kv_head():
     # 40 heads on one kv head: three blocks of 16 rows per sequence and slice
-    assert plan(4, 4096, 40, 1, 128) == ((2 * 148) // (4 * 3), 0)
+    assert plan(4, 8192, 40, 1, 128) == ((2 * 148) // (4 * 3), 0)
 
 
 def test_both_tensor_core_kernels_hold_the_same_number_of_blocks(monkeypatch):
