@@ -276,6 +276,34 @@ __global__ void attn_combine_kernel(T* __restrict__ out, long ldo, const float* 
   const int b = blockIdx.y, h = blockIdx.x;
   const size_t p0 = ((size_t)b * n_heads + h) * n_splits;
   const float2* ml = reinterpret_cast<const float2*>(part_ml) + p0;
+  if (n_splits <= 8) {
+    // the usual case: the maxima, the sums and this thread's values of all slices in one round of loads
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+      float2 m8[8];
+      float o8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool in = j < n_splits;
+        m8[j] = in ? __ldcg(ml + j) : make_float2(-INFINITY, 0.f);
+        o8[j] = in ? __ldcg(part_o + (p0 + j) * hd + d) : 0.f;
+      }
+      float mm = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mm = fmaxf(mm, m8[j].x);
+      float tot = 0.f, val = 0.f;
+      if (mm != -INFINITY) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (m8[j].x == -INFINITY) continue;
+          const float w = expf(m8[j].x - mm);
+          tot += m8[j].y * w;
+          val += o8[j] * w;
+        }
+      }
+      gi::stf(out + (size_t)b * ldo + (size_t)h * hd + d, tot > 0.f ? val / tot : 0.f);
+    }
+    return;
+  }
   float mm = -INFINITY;
   for (int s0 = 0; s0 < n_splits; s0 += 8) {
     float m8[8];
@@ -375,7 +403,7 @@ extern "C" int gi_attn_combine(void* out, long ldo, int dtype, const float* part
   dim3 cgrid(n_heads, n_seqs);
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T,
-      e = gi::launch(attn_combine_kernel<T>, cgrid, dim3(64), 0, (cudaStream_t)stream, (T*)out, ldo, part_o, part_ml, n_heads, hd, n_splits));
+      e = gi::launch(attn_combine_kernel<T>, cgrid, dim3(hd <= 64 ? 64 : (hd <= 128 ? 128 : 256)), 0, (cudaStream_t)stream, (T*)out, ldo, part_o, part_ml, n_heads, hd, n_splits));
   return gi::check(e, "attention combine");
 }
 
