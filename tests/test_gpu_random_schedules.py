@@ -5,7 +5,7 @@ tokens; either every step takes some of the live requests and gives each a chunk
 step holds fresh prompts, chunks in mid-sequence and single tokens side by side, some requests sit a step out, and the
 places whose logits are wanted are drawn too), or the prompts are read in one step and the rest goes one token at a
 time through the runner that generation uses, which is rebuilt whenever a request ends.  Every row of logits that
-comes back is compared.  The seeds are fixed: a failure names seed and round and can be run again."""
+comes back is compared.  The seeds are fixed: a failure names configuration and draw and can be run again."""
 import numpy as np
 import pytest
 
@@ -87,7 +87,7 @@ def test_drawn_schedules(model_dirs, tiny_configs, name, dtype):
     rng = np.random.default_rng(sum(map(ord, name + dtype)))
     rows = 0
     for rnd in range(12):
-        rows += _chunks(rng, eng, d, cfg, dtype, f"{name} {dtype} round {rnd} in chunks")
-        rows += _runner(rng, eng, d, cfg, dtype, f"{name} {dtype} round {rnd} through the runner")
+        rows += _chunks(rng, eng, d, cfg, dtype, f"{name} {dtype} draw {rnd} in chunks")
+        rows += _runner(rng, eng, d, cfg, dtype, f"{name} {dtype} draw {rnd} through the runner")
     assert rows > 200
     assert eng.cache.slots.free_slots == eng.cache.max_slots          # every slot came back
