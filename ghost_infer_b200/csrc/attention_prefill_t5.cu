@@ -363,7 +363,15 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full0 + 8 * s);
     }
-    if (ok) ok = mbar_wait(o_full, (uint32_t)((n_tiles - 1) & 1), 3, &g_attn_status);
+    // The last output product is done when the barrier that frees its stage of values says so.  That barrier belongs
+    // to one stage: it completes a phase every second tile, and the phase before the awaited one (tile n - 3's) is known
+    // to be complete, since the scores of tile n - 1 were not issued before it.  `o_full`, which completes a phase
+    // at every tile, cannot be asked here: a warp that has finished its last tile while another is still two tiles back
+    // finds it two phases behind, and a wait by parity takes that for the awaited phase: the warp then read its rows
+    // of the output before the last two products had added to them (seen as one warp's rows wrong, once in some
+    // dozens of launches with few tiles per block).  During the loop `o_full` is safe: at tile j the product of tile
+    // j - 2 is known to be done, so the barrier is at most one phase behind.
+    if (ok) ok = mbar_wait(kv_empty0 + 8 * ((n_tiles - 1) & 1), (uint32_t)(((n_tiles - 1) >> 1) & 1), 3, &g_attn_status);
     tc_fence_after();
     if (ok) {
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
