@@ -798,13 +798,16 @@ def test_attention_prefill_tcgen05(H, KV, window, hd, pairing, request):
     flat = torch.cat([q[b, :lens_q[b]] for b in range(B)])
     cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
     slots = torch.arange(B, dtype=torch.int32, device=DEV)
-    out = torch.full((flat.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.attn_prefill_t5(flat, kc, vc, bt, cu, slots, torch.tensor(pos0, dtype=torch.int32, device=DEV), B,
-                        max(lens_q), H, KV, hd, 0.21, window, out)
-    assert ops.attn_prefill_t5_status() == 0
     ref = attention_ref(q[:, :, :H * hd], k, v, lens_q, pos0, H, KV, hd, 0.21, window)
     ref = torch.cat([ref[b, :lens_q[b]] for b in range(B)])
-    torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
+    pos0_t = torch.tensor(pos0, dtype=torch.int32, device=DEV)
+    # Many launches of the same case: what goes wrong in this kernel goes wrong by timing (a warp of a block that falls
+    # behind the others), most easily where a block has few key tiles (a window), and then in one launch of dozens.
+    for _ in range(16 if window else 4):
+        out = torch.full((flat.shape[0], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.attn_prefill_t5(flat, kc, vc, bt, cu, slots, pos0_t, B, max(lens_q), H, KV, hd, 0.21, window, out)
+        assert ops.attn_prefill_t5_status() == 0
+        torch.testing.assert_close(out.double(), ref, **tol(torch.bfloat16))
 
 
 def test_prefill_kernels_chain_under_dependent_launch():
