@@ -250,8 +250,11 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk)      // 16 keys of the probabilities = 8 columns of the tile's score buffer
           tc_mma_a_tmem(tmem_o, tmem_s + (uint32_t)(s * 64 + kk * 8), s ? dv[1][kk] : dv[0][kk], IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(kv_empty0 + 8 * s);
+        // `o_full` first: the barrier asked last by the row warps (the stage's, at the end of the tile loop) is then the
+        // one whose arrival is issued last, and no arrival can still be on its way when the barriers are made anew
+        // for the block's second query tile
         tc_commit(o_full);
+        tc_commit(kv_empty0 + 8 * s);
         // values two tiles ahead go into this tile's stage once this product no longer reads it
         if (j + 2 < n_tiles) {
           ok = mbar_wait(kv_empty0 + 8 * s, (uint32_t)((j >> 1) & 1), 1, &g_attn_status);
